@@ -1,0 +1,60 @@
+// Kernel-level extern "C" entry points (declared in include/pi05_b200.h).
+#include <string>
+
+#include "../../include/pi05_b200.h"
+#include "gemm.h"
+
+namespace pi05 {
+
+thread_local std::string g_last_cuda_error;
+
+int record_cuda(cudaError_t error) {
+  if (error == cudaSuccess) return kPi05Ok;
+  g_last_cuda_error = cudaGetErrorString(error);
+  return kPi05ErrCuda;
+}
+
+}  // namespace pi05
+
+extern "C" const char* pi05_last_cuda_error(void) { return pi05::g_last_cuda_error.c_str(); }
+
+extern "C" const char* pi05_version(void) { return "pi05_b200 sm_100a " __DATE__; }
+
+extern "C" int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream) {
+  using namespace pi05;
+  if (args == nullptr) return kPi05ErrInvalidValue;
+  GemmProblem q;
+  q.op = args->op;
+  q.M = args->m;
+  q.N = args->n;
+  q.K = args->k;
+  q.nb0 = args->nb0;
+  q.nb1 = args->nb1;
+  q.a = GemmOperand{args->a, args->m, args->lda, args->a_sb0, args->a_sb1};
+  q.b = GemmOperand{args->b, args->b_mn_major ? args->k : args->n, args->ldb, args->b_sb0,
+                    args->b_sb1};
+  q.b_mn_major = args->b_mn_major != 0;
+  q.out = args->out;
+  q.ldc = args->ldc;
+  q.out_sb0 = args->out_sb0;
+  q.out_sb1 = args->out_sb1;
+  q.out_type = args->out_type;
+  q.mode = args->mode;
+  q.residual = args->residual;
+  q.bias = args->bias;
+  q.col_scale = args->col_scale;
+  q.row_scale = args->row_scale;
+  q.pos = args->pos;
+  q.pos_rows = args->pos_rows;
+  q.pos_ld = args->pos_ld;
+  q.gate = args->gate;
+  q.alpha = args->alpha;
+  q.out_inv_scale = args->out_inv_scale;
+  q.status = args->status;
+  q.force_swap = args->force_swap;
+  q.force_block_n = args->force_block_n;
+  GemmPlan plan;
+  const int rc = gemm_plan_build(q, &plan);
+  if (rc != kPi05Ok) return rc;
+  return record_cuda(gemm_plan_launch(plan, static_cast<cudaStream_t>(cuda_stream)));
+}

@@ -1,0 +1,202 @@
+// Host side of the tcgen05 GEMM family: tensor-map encoding, tile-shape
+// selection and launch. Nothing here allocates device memory.
+#include "gemm.h"
+
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+namespace pi05 {
+namespace {
+
+using EncodeTiledFn = PFN_cuTensorMapEncodeTiled_v12000;
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query) ==
+            cudaSuccess &&
+        query == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+int elem_bytes(int op) { return op == kOpBf16 ? 2 : 1; }
+
+// Rank-4 tiled map {inner, rows, b0, b1}, 128-byte swizzle, zero fill outside.
+int encode_map(CUtensorMap* map, int op, const void* ptr, uint64_t inner, uint64_t rows,
+               uint64_t nb0, uint64_t nb1, long long ld, long long sb0, long long sb1,
+               uint32_t box_inner, uint32_t box_rows) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return kPi05ErrDriver;
+  const uint64_t es = elem_bytes(op);
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return kPi05ErrInvalidValue;
+  if ((ld * es) % 16 != 0) return kPi05ErrInvalidValue;
+  uint64_t row_bytes = static_cast<uint64_t>(ld) * es;
+  uint64_t s0 = static_cast<uint64_t>(sb0) * es;
+  uint64_t s1 = static_cast<uint64_t>(sb1) * es;
+  // singleton batch dimensions still need a legal (16-byte multiple) stride
+  if (nb0 <= 1) s0 = row_bytes * rows;
+  if (nb1 <= 1) s1 = (nb0 <= 1 ? row_bytes * rows : s0 * nb0);
+  if (s0 % 16 != 0 || s1 % 16 != 0) return kPi05ErrInvalidValue;
+  cuuint64_t dims[4] = {inner, rows, nb0 < 1 ? 1 : nb0, nb1 < 1 ? 1 : nb1};
+  cuuint64_t strides[3] = {row_bytes, s0, s1};
+  cuuint32_t box[4] = {box_inner, box_rows, 1, 1};
+  cuuint32_t estrides[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dtype =
+      op == kOpBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult result = encode(map, dtype, 4, const_cast<void*>(ptr), dims, strides, box, estrides,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return result == CUDA_SUCCESS ? kPi05Ok : kPi05ErrDriver;
+}
+
+template <int OP, int BLOCK_N, int STAGES, bool SWAP, bool B_MN>
+const void* kernel_ptr(int* smem) {
+  auto kernel = &gemm_umma_kernel<OP, BLOCK_N, STAGES, SWAP, B_MN>;
+  *smem = gemm_smem_bytes(BLOCK_N, STAGES);
+  // per device, idempotent and cheap: set on every plan build
+  cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       gemm_smem_bytes(BLOCK_N, STAGES));
+  return reinterpret_cast<const void*>(kernel);
+}
+
+template <int OP>
+const void* select_kernel(int block_n, bool swap, bool b_mn, int* smem) {
+  if (b_mn) {
+    if constexpr (OP == kOpBf16) {
+      if (block_n == 128) return kernel_ptr<OP, 128, 6, false, true>(smem);
+      if (block_n == 256) return kernel_ptr<OP, 256, 4, false, true>(smem);
+    }
+    return nullptr;
+  }
+  if (swap) {
+    if (block_n == 16) return kernel_ptr<OP, 16, 8, true, false>(smem);
+    if (block_n == 32) return kernel_ptr<OP, 32, 8, true, false>(smem);
+    if (block_n == 64) return kernel_ptr<OP, 64, 8, true, false>(smem);
+    return nullptr;
+  }
+  if (block_n == 64) return kernel_ptr<OP, 64, 8, false, false>(smem);
+  if (block_n == 128) return kernel_ptr<OP, 128, 6, false, false>(smem);
+  if (block_n == 256) return kernel_ptr<OP, 256, 4, false, false>(smem);
+  return nullptr;
+}
+
+}  // namespace
+
+int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
+  if (plan == nullptr || q.a.ptr == nullptr || q.b.ptr == nullptr || q.out == nullptr ||
+      q.M <= 0 || q.N <= 0 || q.K <= 0 || q.nb0 <= 0 || q.nb1 <= 0 || q.status == nullptr) {
+    return kPi05ErrInvalidValue;
+  }
+  if (q.op != kOpBf16 && q.op != kOpE4m3 && q.op != kOpS8) return kPi05ErrInvalidValue;
+  if (q.out_type == kOutS32 && q.op != kOpS8) return kPi05ErrInvalidValue;
+  if (q.mode == kEpiGeglu && (q.N % 128 != 0 || q.b_mn_major)) return kPi05ErrInvalidValue;
+  if ((q.mode == kEpiBiasResidual || q.mode == kEpiGateResidual) && q.residual == nullptr)
+    return kPi05ErrInvalidValue;
+  if (q.mode == kEpiGateResidual && q.gate == nullptr) return kPi05ErrInvalidValue;
+  if (q.mode == kEpiBiasPos && (q.pos == nullptr || q.pos_rows <= 0)) return kPi05ErrInvalidValue;
+  if (q.b_mn_major && q.op != kOpBf16) return kPi05ErrUnsupported;
+
+  const int es = elem_bytes(q.op);
+  const int block_k = 128 / es;
+  bool swap = q.force_swap >= 0 ? q.force_swap != 0 : (q.M <= 64 && !q.b_mn_major);
+  if (q.b_mn_major) swap = false;
+  int block_n = q.force_block_n;
+  if (block_n == 0) {
+    if (swap) {
+      block_n = q.M <= 16 ? 16 : q.M <= 32 ? 32 : 64;
+    } else if (q.b_mn_major) {
+      block_n = q.N > 128 ? 256 : 128;
+    } else {
+      const long long tiles_m = (q.M + 127) / 128;
+      const long long batches = (long long)q.nb0 * q.nb1;
+      const long long tiles256 = tiles_m * ((q.N + 255) / 256) * batches;
+      const long long tiles128 = tiles_m * ((q.N + 127) / 128) * batches;
+      if (tiles256 >= 2 * 148 || (q.mode == kEpiGeglu && tiles256 >= 148)) {
+        block_n = 256;
+      } else if (tiles128 >= 120 || q.mode == kEpiGeglu || q.N < 128) {
+        block_n = 128;
+      } else {
+        block_n = 64;
+      }
+      if (q.mode == kEpiGeglu && block_n < 128) block_n = 128;
+      if (q.N % 256 != 0 && q.mode == kEpiGeglu) block_n = 128;
+    }
+  }
+  if (swap && q.M > block_n) return kPi05ErrInvalidValue;
+
+  int smem = 0;
+  const void* kernel = nullptr;
+  if (q.op == kOpBf16) kernel = select_kernel<kOpBf16>(block_n, swap, q.b_mn_major, &smem);
+  if (q.op == kOpE4m3) kernel = select_kernel<kOpE4m3>(block_n, swap, q.b_mn_major, &smem);
+  if (q.op == kOpS8) kernel = select_kernel<kOpS8>(block_n, swap, q.b_mn_major, &smem);
+  if (kernel == nullptr) return kPi05ErrUnsupported;
+
+  // A-side map = the operand with 128-row tiles.
+  int rc;
+  if (!swap) {
+    rc = encode_map(&plan->tmap_a, q.op, q.a.ptr, q.K, q.M, q.nb0, q.nb1, q.a.ld, q.a.sb0, q.a.sb1,
+                    block_k, 128);
+    if (rc != kPi05Ok) return rc;
+    if (q.b_mn_major) {
+      rc = encode_map(&plan->tmap_b, q.op, q.b.ptr, q.N, q.K, q.nb0, q.nb1, q.b.ld, q.b.sb0,
+                      q.b.sb1, 64, 64);
+    } else {
+      rc = encode_map(&plan->tmap_b, q.op, q.b.ptr, q.K, q.N, q.nb0, q.nb1, q.b.ld, q.b.sb0,
+                      q.b.sb1, block_k, block_n);
+    }
+    if (rc != kPi05Ok) return rc;
+  } else {
+    rc = encode_map(&plan->tmap_a, q.op, q.b.ptr, q.K, q.N, q.nb0, q.nb1, q.b.ld, q.b.sb0, q.b.sb1,
+                    block_k, 128);
+    if (rc != kPi05Ok) return rc;
+    rc = encode_map(&plan->tmap_b, q.op, q.a.ptr, q.K, q.M, q.nb0, q.nb1, q.a.ld, q.a.sb0, q.a.sb1,
+                    block_k, block_n);
+    if (rc != kPi05Ok) return rc;
+  }
+
+  GemmParams& p = plan->params;
+  p.rows_a = swap ? q.N : q.M;
+  p.rows_b = swap ? q.M : q.N;
+  p.num_kb = (q.K + block_k - 1) / block_k;
+  p.nb0 = q.nb0;
+  p.out = q.out;
+  p.ldc = q.ldc;
+  p.out_sb0 = q.out_sb0;
+  p.out_sb1 = q.out_sb1;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(q.residual);
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(q.bias);
+  p.col_scale = q.col_scale;
+  p.row_scale = q.row_scale;
+  p.pos = reinterpret_cast<const __nv_bfloat16*>(q.pos);
+  p.gate = reinterpret_cast<const __nv_bfloat16*>(q.gate);
+  p.alpha = q.alpha;
+  p.out_inv_scale = q.out_inv_scale;
+  p.pos_rows = q.pos_rows;
+  p.pos_ld = q.pos_ld;
+  p.mode = q.mode;
+  p.out_type = q.out_type;
+  p.status = q.status;
+
+  plan->grid = dim3((p.rows_a + 127) / 128, (p.rows_b + block_n - 1) / block_n, q.nb0 * q.nb1);
+  plan->smem_bytes = smem;
+  plan->kernel = kernel;
+  plan->swap = swap;
+  plan->block_n = block_n;
+  return kPi05Ok;
+}
+
+cudaError_t gemm_plan_launch(const GemmPlan& plan, cudaStream_t stream) {
+  void* args[3] = {const_cast<CUtensorMap*>(&plan.tmap_a), const_cast<CUtensorMap*>(&plan.tmap_b),
+                   const_cast<GemmParams*>(&plan.params)};
+  return cudaLaunchKernel(plan.kernel, plan.grid, dim3(kGemmThreads), args, plan.smem_bytes,
+                          stream);
+}
+
+}  // namespace pi05

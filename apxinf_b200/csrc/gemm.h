@@ -1,0 +1,77 @@
+// Host-side description, planning and launch of one tcgen05 GEMM.
+// A plan (two TMA tensor maps + kernel parameters + launch geometry) is built
+// once, on the host, with no device allocation, and can then be launched any
+// number of times, also inside a CUDA-graph capture.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gemm_umma.cuh"
+
+namespace pi05 {
+
+// A K-major operand: `rows` rows of `k` contiguous elements, leading dimension
+// `ld`, optionally batched over two outer indices. All strides in elements.
+struct GemmOperand {
+  const void* ptr = nullptr;
+  int rows = 0;
+  long long ld = 0;
+  long long sb0 = 0, sb1 = 0;
+};
+
+struct GemmProblem {
+  int op = kOpBf16;  // OperandType of both operands
+  int M = 0, N = 0, K = 0;
+  int nb0 = 1, nb1 = 1;  // batch extents
+  GemmOperand a;         // activations [M, K]
+  GemmOperand b;         // weights [N, K]; with b_mn_major: [K, N] row-major, rows = K
+  bool b_mn_major = false;
+  // output / epilogue (logical [M, N_out]); N_out = N/2 for kEpiGeglu
+  void* out = nullptr;
+  long long ldc = 0, out_sb0 = 0, out_sb1 = 0;
+  int out_type = kOutBf16;
+  int mode = kEpiStore;
+  const void* residual = nullptr;
+  const void* bias = nullptr;
+  const float* col_scale = nullptr;
+  const float* row_scale = nullptr;
+  const void* pos = nullptr;
+  int pos_rows = 1;
+  long long pos_ld = 0;
+  const void* gate = nullptr;
+  float alpha = 1.0f;
+  float out_inv_scale = 1.0f;
+  int* status = nullptr;
+  // tuning overrides (0 / -1 = automatic)
+  int force_swap = -1;
+  int force_block_n = 0;
+};
+
+struct GemmPlan {
+  CUtensorMap tmap_a;
+  CUtensorMap tmap_b;
+  GemmParams params;
+  dim3 grid;
+  int smem_bytes = 0;
+  const void* kernel = nullptr;
+  bool swap = false;
+  int block_n = 0;
+};
+
+// Error codes of this library's C ABI (negative = rejected before launch).
+enum Pi05Error : int {
+  kPi05Ok = 0,
+  kPi05ErrInvalidValue = -1,
+  kPi05ErrUnsupported = -2,
+  kPi05ErrDriver = -3,
+  kPi05ErrCuda = -4,
+  kPi05ErrDeviceTimeout = -5,
+  kPi05ErrNotBuilt = -6,
+};
+
+int gemm_plan_build(const GemmProblem& problem, GemmPlan* plan);
+cudaError_t gemm_plan_launch(const GemmPlan& plan, cudaStream_t stream);
+
+}  // namespace pi05

@@ -1,0 +1,481 @@
+// Dense linear layers of the PI0.5 forward as tcgen05 (UMMA) GEMMs with TMEM
+// accumulators fed by TMA, for sm_100a only.
+//
+//   D[i, j] = sum_k A[i, k] * B[j, k]        A: 128-row tile, B: BLOCK_N-row tile
+//
+// Both operands are K-major in global memory (row = one output index, K
+// contiguous) and land in shared memory through 128-byte-swizzled TMA boxes;
+// optionally B is "MN-major" (a [K, N] row-major matrix such as an attention
+// value matrix). One CTA computes one 128 x BLOCK_N tile:
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocator + single-thread tcgen05.mma issuer
+//   warps 2..5  epilogue: tcgen05.ld the accumulator, apply the fused
+//               epilogue, store with 16/32-byte accesses
+// "Swap" launches put the weight matrix on the 128-row side and the (few)
+// activation rows on the BLOCK_N side, so a 10- or 50-row action-expert GEMM
+// still fills the 128-lane MMA; the epilogue then writes the transpose.
+//
+// Replaces, for the PI0.5 path, the reference's cuBLAS / cuBLASLt / CUTLASS
+// GEMM dispatch (crates/apxinf-cuda/src/kernels/gemm/{bf16,fp8,w8a8}.rs) and
+// the elementwise kernels that follow each GEMM there
+// (crates/apxinf-cuda/kernels/custom/{activation,elementwise,fused}.cuh); the
+// rounding points of those separate kernels are kept inside the epilogue.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "ptx.cuh"
+
+namespace pi05 {
+
+enum OperandType : int { kOpBf16 = 0, kOpE4m3 = 1, kOpS8 = 2 };
+
+// Fused epilogues. "rb" = round to bf16 and back (the reference stores every
+// GEMM result as a 16-bit tensor before the next elementwise kernel reads it).
+enum EpilogueMode : int {
+  kEpiStore = 0,        // o = rb(v); if bias: o = rb(o + bias[c])
+  kEpiBiasGelu = 1,     // o = gelu_tanh(rb(v) + bias[c])
+  kEpiBiasSilu = 2,     // o = silu(rb(v) + bias[c])
+  kEpiBiasResidual = 3, // o = rb(v) + residual[r, c] (+ bias[c])
+  kEpiBiasPos = 4,      // o = rb(v) + pos[r % pos_rows, c] (+ bias[c])
+  kEpiGateResidual = 5, // o = residual[r, c] + rb(v) * gate[c]
+  kEpiGeglu = 6,        // weight rows interleaved 64 gate / 64 up: o = gelu_tanh(rb(g)) * rb(u)
+};
+
+enum OutType : int {
+  kOutBf16 = 0,  // round-to-nearest-even bf16
+  kOutE4m3 = 1,  // e4m3(clamp(o * out_inv_scale, +-448))
+  kOutF32 = 2,   // raw scaled accumulator (no epilogue rounding), for tests / partial sums
+  kOutS32 = 3,   // raw int32 accumulator (kOpS8 only), for bit-exact checks
+};
+
+enum GemmStatus : int {
+  kGemmOk = 0,
+  kGemmTimeoutProducer = 101,
+  kGemmTimeoutMma = 102,
+  kGemmTimeoutEpilogue = 103,
+};
+
+struct GemmParams {
+  int rows_a;   // valid rows of the 128-row-side operand
+  int rows_b;   // valid rows of the BLOCK_N-side operand
+  int num_kb;   // K blocks of 128 bytes
+  int nb0;      // blockIdx.z = b0 + nb0 * b1
+  // logical output [M, N] (after un-swapping), element strides
+  void* out;
+  long long ldc, out_sb0, out_sb1;
+  const __nv_bfloat16* residual;  // same geometry as out
+  const __nv_bfloat16* bias;      // [N]
+  const float* col_scale;         // [N] or null (per-output-channel weight scale)
+  const float* row_scale;         // [M] or null (per-row activation scale)
+  const __nv_bfloat16* pos;       // [pos_rows, N]
+  const __nv_bfloat16* gate;      // [N]
+  float alpha;                    // scalar scale applied with row_scale
+  float out_inv_scale;            // for kOutE4m3
+  int pos_rows;
+  long long pos_ld;
+  int mode;
+  int out_type;
+  int* status;                    // device status word, 0 = ok
+};
+
+__device__ __forceinline__ float round_bf16(float x) {
+  return __bfloat162float(__float2bfloat16(x));
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float value) {
+  constexpr float kAlpha = 0.7978845608028654f;
+  return 0.5f * value * (1.0f + tanhf(kAlpha * (value + 0.044715f * value * value * value)));
+}
+
+__device__ __forceinline__ float silu_f(float value) { return value / (1.0f + expf(-value)); }
+
+__device__ __forceinline__ uint8_t to_e4m3(float scaled) {
+  const float clamped = fminf(448.0f, fmaxf(-448.0f, scaled));
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(clamped, __NV_SATFINITE, __NV_E4M3));
+}
+
+template <int OP>
+struct OpTraits;
+template <>
+struct OpTraits<kOpBf16> {
+  static constexpr int kElemBytes = 2;
+  static constexpr ptx::MmaKind kKind = ptx::MmaKind::kF16;
+  static constexpr uint32_t kFormat = 1;   // bf16
+  static constexpr uint32_t kCFormat = 1;  // f32
+};
+template <>
+struct OpTraits<kOpE4m3> {
+  static constexpr int kElemBytes = 1;
+  static constexpr ptx::MmaKind kKind = ptx::MmaKind::kF8F6F4;
+  static constexpr uint32_t kFormat = 0;   // e4m3
+  static constexpr uint32_t kCFormat = 1;  // f32
+};
+template <>
+struct OpTraits<kOpS8> {
+  static constexpr int kElemBytes = 1;
+  static constexpr ptx::MmaKind kKind = ptx::MmaKind::kI8;
+  static constexpr uint32_t kFormat = 1;   // s8
+  static constexpr uint32_t kCFormat = 2;  // s32
+};
+
+constexpr int kGemmThreads = 192;
+constexpr int kTileRowsA = 128;
+constexpr int kStageABytes = kTileRowsA * 128;
+
+__host__ __device__ constexpr int gemm_stage_bytes(int block_n) { return kStageABytes + block_n * 128; }
+__host__ __device__ constexpr int gemm_smem_bytes(int block_n, int stages) {
+  return stages * gemm_stage_bytes(block_n) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+}
+__host__ __device__ constexpr uint32_t tmem_cols_for(int block_n) {
+  return block_n <= 32 ? 32u : block_n <= 64 ? 64u : block_n <= 128 ? 128u : 256u;
+}
+
+// One output element through the fused epilogue. `v` is the scaled
+// accumulator; (r, c) are logical output coordinates.
+struct EpilogueCtx {
+  const GemmParams& p;
+  long long out_base;  // batch offset in elements
+};
+
+__device__ __forceinline__ float epilogue_value(const GemmParams& p, long long out_base, int r,
+                                                int c, float v) {
+  switch (p.mode) {
+    case kEpiStore: {
+      float o = round_bf16(v);
+      if (p.bias != nullptr) o = round_bf16(o + __bfloat162float(p.bias[c]));
+      return o;
+    }
+    case kEpiBiasGelu: {
+      float x = round_bf16(v);
+      if (p.bias != nullptr) x += __bfloat162float(p.bias[c]);
+      return gelu_tanh_f(x);
+    }
+    case kEpiBiasSilu: {
+      float x = round_bf16(v);
+      if (p.bias != nullptr) x += __bfloat162float(p.bias[c]);
+      return silu_f(x);
+    }
+    case kEpiBiasResidual: {
+      float o = round_bf16(v) + __bfloat162float(p.residual[out_base + (long long)r * p.ldc + c]);
+      if (p.bias != nullptr) o += __bfloat162float(p.bias[c]);
+      return o;
+    }
+    case kEpiBiasPos: {
+      float o = round_bf16(v) + __bfloat162float(p.pos[(long long)(r % p.pos_rows) * p.pos_ld + c]);
+      if (p.bias != nullptr) o += __bfloat162float(p.bias[c]);
+      return o;
+    }
+    case kEpiGateResidual: {
+      return __bfloat162float(p.residual[out_base + (long long)r * p.ldc + c]) +
+             round_bf16(v) * __bfloat162float(p.gate[c]);
+    }
+    default:
+      return v;
+  }
+}
+
+__device__ __forceinline__ void store_one(const GemmParams& p, long long index, float o) {
+  if (p.out_type == kOutBf16) {
+    reinterpret_cast<__nv_bfloat16*>(p.out)[index] = __float2bfloat16(o);
+  } else if (p.out_type == kOutE4m3) {
+    reinterpret_cast<uint8_t*>(p.out)[index] = to_e4m3(o * p.out_inv_scale);
+  } else {
+    reinterpret_cast<float*>(p.out)[index] = o;
+  }
+}
+
+// Store 16 consecutive columns of one row; vectorised when the destination is
+// 16-byte aligned and the whole chunk is in range.
+__device__ __forceinline__ void store_chunk16(const GemmParams& p, long long index, int valid,
+                                              const float (&o)[16]) {
+  if (p.out_type == kOutBf16) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + index;
+    if (valid == 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+      uint32_t w[8];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        __nv_bfloat162 pair = __floats2bfloat162_rn(o[2 * t], o[2 * t + 1]);
+        w[t] = *reinterpret_cast<uint32_t*>(&pair);
+      }
+      reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    } else {
+      for (int t = 0; t < valid; ++t) dst[t] = __float2bfloat16(o[t]);
+    }
+  } else if (p.out_type == kOutE4m3) {
+    uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + index;
+    if (valid == 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+      uint32_t w[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        w[t] = (uint32_t)to_e4m3(o[4 * t] * p.out_inv_scale) |
+               ((uint32_t)to_e4m3(o[4 * t + 1] * p.out_inv_scale) << 8) |
+               ((uint32_t)to_e4m3(o[4 * t + 2] * p.out_inv_scale) << 16) |
+               ((uint32_t)to_e4m3(o[4 * t + 3] * p.out_inv_scale) << 24);
+      }
+      *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      for (int t = 0; t < valid; ++t) dst[t] = to_e4m3(o[t] * p.out_inv_scale);
+    }
+  } else {
+    float* dst = reinterpret_cast<float*>(p.out) + index;
+    for (int t = 0; t < valid; ++t) dst[t] = o[t];
+  }
+}
+
+template <int OP, int BLOCK_N, int STAGES, bool SWAP, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                 const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  using T = OpTraits<OP>;
+  static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 256, "bad BLOCK_N");
+  static_assert(!B_MN || (OP == kOpBf16 && BLOCK_N % 64 == 0 && !SWAP), "MN-major B: bf16 only");
+  constexpr int kBlockK = 128 / T::kElemBytes;  // elements per 128-byte K block
+  constexpr int kStageBBytes = BLOCK_N * 128;
+  constexpr int kStageBytes = kStageABytes + kStageBBytes;
+  constexpr uint32_t kTmemCols = tmem_cols_for(BLOCK_N);
+  constexpr uint32_t kIdesc =
+      ptx::make_idesc(T::kCFormat, T::kFormat, T::kFormat, 0, B_MN ? 1 : 0, 128, BLOCK_N);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* accum_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tile_a = blockIdx.x;
+  const int tile_b = blockIdx.y;
+  const int b0 = blockIdx.z % p.nb0;
+  const int b1 = blockIdx.z / p.nb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    ptx::mbar_init(accum_bar, 1);
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tmap_a);
+      ptx::prefetch_tensormap(&tmap_b);
+      bool ok = true;
+      int issued = 0;
+      for (int kb = 0; kb < p.num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t round = kb / STAGES;
+        if (round > 0) ok = ptx::mbar_wait(&empty_bar[s], (round - 1) & 1);
+        if (!ok) break;
+        uint8_t* sa = smem + s * kStageBytes;
+        uint8_t* sb = sa + kStageABytes;
+        ptx::mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+        ptx::tma_load_4d(sa, &tmap_a, &full_bar[s], kb * kBlockK, tile_a * kTileRowsA, b0, b1);
+        if constexpr (B_MN) {
+#pragma unroll
+          for (int chunk = 0; chunk < BLOCK_N / 64; ++chunk) {
+            ptx::tma_load_4d(sb + chunk * 8192, &tmap_b, &full_bar[s],
+                             tile_b * BLOCK_N + chunk * 64, kb * kBlockK, b0, b1);
+          }
+        } else {
+          ptx::tma_load_4d(sb, &tmap_b, &full_bar[s], kb * kBlockK, tile_b * BLOCK_N, b0, b1);
+        }
+        ++issued;
+      }
+      if (!ok) {
+        atomicCAS(p.status, 0, kGemmTimeoutProducer);
+        // let copies already in flight land before the CTA retires
+        const int first = issued > STAGES ? issued - STAGES : 0;
+        for (int kb = first; kb < issued; ++kb) {
+          ptx::mbar_wait(&full_bar[kb % STAGES], (kb / STAGES) & 1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        const int s = kb % STAGES;
+        ok = ptx::mbar_wait(&full_bar[s], (kb / STAGES) & 1);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const uint32_t a_addr = ptx::smem_u32(smem + s * kStageBytes);
+        const uint32_t b_addr = a_addr + kStageABytes;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t adesc = ptx::make_smem_desc(a_addr + k * 32, 16, 1024);
+          const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b_addr + k * 2048, 8192, 1024)
+                                      : ptx::make_smem_desc(b_addr + k * 32, 16, 1024);
+          ptx::umma<T::kKind>(tmem_base, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+        }
+        ptx::umma_commit(&empty_bar[s]);
+      }
+      if (!ok) atomicCAS(p.status, 0, kGemmTimeoutMma);
+      // Always signal the epilogue so that it never waits on a dead pipeline.
+      ptx::umma_commit(accum_bar);
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int row_in_tile = quarter * 32 + lane;
+    const int gi = tile_a * kTileRowsA + row_in_tile;  // index on the 128-row side
+    const bool ok = ptx::mbar_wait(accum_bar, 0);
+    if (!ok && lane == 0) atomicCAS(p.status, 0, kGemmTimeoutEpilogue);
+    ptx::tc_fence_after();
+    const long long out_base = (long long)b0 * p.out_sb0 + (long long)b1 * p.out_sb1;
+    const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+
+    auto to_float = [](uint32_t raw) -> float {
+      if constexpr (OP == kOpS8) return static_cast<float>(static_cast<int>(raw));
+      return __uint_as_float(raw);
+    };
+
+    if (p.mode == kEpiGeglu) {
+      if constexpr (!SWAP) {
+        // columns [128t, 128t+64) gate, [128t+64, 128t+128) up; thread-local.
+        const float sr = p.alpha * (p.row_scale != nullptr && gi < p.rows_a ? p.row_scale[gi] : 1.0f);
+#pragma unroll 1
+        for (int pair = 0; pair < BLOCK_N / 128; ++pair) {
+#pragma unroll 1
+          for (int sub = 0; sub < 4; ++sub) {
+            uint32_t rg[16], ru[16];
+            ptx::tmem_ld_16(taddr_row + pair * 128 + sub * 16, rg);
+            ptx::tmem_ld_16(taddr_row + pair * 128 + 64 + sub * 16, ru);
+            ptx::tmem_ld_wait();
+            const int cg = tile_b * BLOCK_N + pair * 128 + sub * 16;  // packed gate column
+            const int oc = (cg / 128) * 64 + (cg % 128);              // output column
+            float o[16];
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+              const float sg = p.col_scale != nullptr ? p.col_scale[min(cg + t, p.rows_b - 1)] : 1.0f;
+              const float su =
+                  p.col_scale != nullptr ? p.col_scale[min(cg + 64 + t, p.rows_b - 1)] : 1.0f;
+              const float g = round_bf16(to_float(rg[t]) * sr * sg);
+              const float u = round_bf16(to_float(ru[t]) * sr * su);
+              o[t] = gelu_tanh_f(g) * u;
+            }
+            if (gi < p.rows_a && cg < p.rows_b) {
+              store_chunk16(p, out_base + (long long)gi * p.ldc + oc, 16, o);
+            }
+          }
+        }
+      } else {
+        // lanes [0,64) hold gate features, lanes [64,128) the matching up
+        // features; the up half goes through shared memory (stage 0 is idle
+        // once the accumulator barrier has fired).
+        float* xchg = reinterpret_cast<float*>(smem);  // [64][BLOCK_N]
+        const float sc = p.col_scale != nullptr && gi < p.rows_a ? p.col_scale[gi] : 1.0f;
+        float vals[BLOCK_N];
+#pragma unroll
+        for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
+          uint32_t raw[16];
+          ptx::tmem_ld_16(taddr_row + cc * 16, raw);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            const int r = tile_b * BLOCK_N + cc * 16 + t;
+            const float sr =
+                p.alpha * (p.row_scale != nullptr && r < p.rows_b ? p.row_scale[r] : 1.0f);
+            vals[cc * 16 + t] = round_bf16(to_float(raw[t]) * sr * sc);
+          }
+        }
+        if (row_in_tile >= 64) {
+#pragma unroll
+          for (int j = 0; j < BLOCK_N; ++j) xchg[j * 64 + (row_in_tile - 64)] = vals[j];
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (row_in_tile < 64) {
+          const int oc = tile_a * 64 + row_in_tile;
+          if (gi < p.rows_a) {
+#pragma unroll
+            for (int j = 0; j < BLOCK_N; ++j) {
+              const int r = tile_b * BLOCK_N + j;
+              if (r < p.rows_b) {
+                const float o = gelu_tanh_f(vals[j]) * xchg[j * 64 + row_in_tile];
+                store_one(p, out_base + (long long)r * p.ldc + oc, o);
+              }
+            }
+          }
+        }
+      }
+    } else if constexpr (!SWAP) {
+      const int r = gi;
+      const float sr = p.alpha * (p.row_scale != nullptr && r < p.rows_a ? p.row_scale[r] : 1.0f);
+#pragma unroll 1
+      for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
+        uint32_t raw[16];
+        ptx::tmem_ld_16(taddr_row + cc * 16, raw);
+        ptx::tmem_ld_wait();
+        const int c0 = tile_b * BLOCK_N + cc * 16;
+        if (r >= p.rows_a || c0 >= p.rows_b) continue;
+        const int valid = min(16, p.rows_b - c0);
+        if (p.out_type == kOutS32) {
+          int* dst = reinterpret_cast<int*>(p.out) + out_base + (long long)r * p.ldc + c0;
+          for (int t = 0; t < valid; ++t) dst[t] = static_cast<int>(raw[t]);
+          continue;
+        }
+        float o[16];
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+          const int c = min(c0 + t, p.rows_b - 1);
+          const float sc = p.col_scale != nullptr ? p.col_scale[c] : 1.0f;
+          const float v = to_float(raw[t]) * sr * sc;
+          o[t] = p.out_type == kOutF32 ? v : epilogue_value(p, out_base, r, c, v);
+        }
+        store_chunk16(p, out_base + (long long)r * p.ldc + c0, valid, o);
+      }
+    } else {
+      // swapped: lane index = logical column, TMEM column = logical row
+      const int c = gi;
+      const float sc = p.col_scale != nullptr && c < p.rows_a ? p.col_scale[c] : 1.0f;
+#pragma unroll 1
+      for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
+        uint32_t raw[16];
+        ptx::tmem_ld_16(taddr_row + cc * 16, raw);
+        ptx::tmem_ld_wait();
+        if (c >= p.rows_a) continue;
+#pragma unroll 1
+        for (int t = 0; t < 16; ++t) {
+          const int r = tile_b * BLOCK_N + cc * 16 + t;
+          if (r >= p.rows_b) break;
+          const long long index = out_base + (long long)r * p.ldc + c;
+          if (p.out_type == kOutS32) {
+            reinterpret_cast<int*>(p.out)[index] = static_cast<int>(raw[t]);
+            continue;
+          }
+          const float sr = p.alpha * (p.row_scale != nullptr ? p.row_scale[r] : 1.0f);
+          const float v = to_float(raw[t]) * sr * sc;
+          const float o = p.out_type == kOutF32 ? v : epilogue_value(p, out_base, r, c, v);
+          store_one(p, index, o);
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace pi05

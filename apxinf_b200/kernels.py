@@ -1,0 +1,68 @@
+"""Kernel-level operators over the C ABI, taking torch CUDA tensors as device memory.
+
+torch only supplies memory and the stream handle here; every operator is a
+hand-written CUDA kernel in libpi05_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import GemmArgs, check, lib
+
+
+def _stream_ptr(stream=None) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return int(s.cuda_stream)
+
+
+def _ptr(t) -> int | None:
+    return None if t is None else int(t.data_ptr())
+
+
+def _operand(t: torch.Tensor):
+    """(rows, k, ld, nb0, nb1, sb0, sb1) of a [.., rows, k] tensor (innermost contiguous)."""
+    assert t.stride(-1) == 1, "innermost dimension must be contiguous"
+    rows, k = t.shape[-2], t.shape[-1]
+    ld = t.stride(-2)
+    nb0 = t.shape[-3] if t.dim() >= 3 else 1
+    sb0 = t.stride(-3) if t.dim() >= 3 else 0
+    nb1 = t.shape[-4] if t.dim() >= 4 else 1
+    sb1 = t.stride(-4) if t.dim() >= 4 else 0
+    return rows, k, ld, nb0, nb1, sb0, sb1
+
+
+def new_status(device="cuda") -> torch.Tensor:
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def gemm(a, b, out, *, op, mode=_lib.EPI_STORE, out_type=_lib.OUT_BF16, bias=None,
+         residual=None, col_scale=None, row_scale=None, pos=None, gate=None, alpha=1.0,
+         out_inv_scale=1.0, b_mn_major=False, status=None, stream=None, force_swap=-1,
+         force_block_n=0):
+    """out[.., M, N'] = epilogue(a[.., M, K] @ b[.., N, K]^T); see Pi05GemmArgs."""
+    m, k, lda, nb0, nb1, a_sb0, a_sb1 = _operand(a)
+    if b_mn_major:
+        kb, n, ldb, _, _, b_sb0, b_sb1 = _operand(b)
+    else:
+        n, kb, ldb, _, _, b_sb0, b_sb1 = _operand(b)
+    assert kb == k, (kb, k)
+    _, _, ldc, _, _, o_sb0, o_sb1 = _operand(out)
+    if status is None:
+        status = new_status(a.device)
+    args = GemmArgs(
+        op=op, m=m, n=n, k=k, nb0=nb0, nb1=nb1,
+        a=_ptr(a), lda=lda, a_sb0=a_sb0, a_sb1=a_sb1,
+        b=_ptr(b), ldb=ldb, b_sb0=b_sb0, b_sb1=b_sb1, b_mn_major=int(b_mn_major),
+        out=_ptr(out), ldc=ldc, out_sb0=o_sb0, out_sb1=o_sb1,
+        out_type=out_type, mode=mode,
+        residual=_ptr(residual), bias=_ptr(bias), col_scale=_ptr(col_scale),
+        row_scale=_ptr(row_scale), pos=_ptr(pos),
+        pos_rows=(pos.shape[0] if pos is not None else 1),
+        pos_ld=(pos.stride(0) if pos is not None else 0),
+        gate=_ptr(gate), alpha=alpha, out_inv_scale=out_inv_scale, status=_ptr(status),
+        force_swap=force_swap, force_block_n=force_block_n)
+    check(lib().pi05_gemm(C.byref(args), _stream_ptr(stream)), "pi05_gemm")
+    return status

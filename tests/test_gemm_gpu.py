@@ -1,0 +1,253 @@
+"""tcgen05 GEMM family through the C ABI (pi05_gemm) against an fp32 CPU reference.
+
+Integer (s8 x s8 -> s32) results must be bit-exact; floating-point results are
+compared after the same rounding points the epilogue applies.
+"""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _lib():
+    from apxinf_b200 import _lib as L, kernels as K
+    return L, K
+
+
+def rb(x):
+    return x.to(torch.bfloat16).to(torch.float32)
+
+
+def gelu_tanh(x):
+    return 0.5 * x * (1.0 + torch.tanh(0.7978845608028654 * (x + 0.044715 * x * x * x)))
+
+
+def make_operand(rows, k, op, gen, scale=1.0):
+    L, _ = _lib()
+    if op == L.OP_BF16:
+        t = (torch.randn(rows, k, generator=gen) * scale).to(torch.bfloat16)
+        return t, t.float()
+    if op == L.OP_E4M3:
+        t = (torch.randn(rows, k, generator=gen) * scale * 4).clamp(-448, 448).to(torch.float8_e4m3fn)
+        return t, t.float()
+    t = torch.randint(-128, 128, (rows, k), generator=gen, dtype=torch.int8)
+    return t, t.float()
+
+
+def check_close(got, want, atol, rtol, what):
+    got = got.float().cpu()
+    err = (got - want).abs()
+    tol = atol + rtol * want.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{what}: {bad} mismatches, max err {err.max().item():.5f}, max ref {want.abs().max().item():.3f}"
+
+
+SHAPES_NORMAL = [
+    # (M, N, K, block_n)
+    (128, 128, 64, 128),
+    (256, 256, 256, 128),
+    (522, 1152, 592, 128),
+    (522, 2560, 2048, 64),
+    (300, 512, 4304, 256),
+    (130, 72, 256, 128),
+    (522, 4304, 1152, 0),
+]
+
+
+@pytest.mark.parametrize("op", [0, 1, 2])
+@pytest.mark.parametrize("shape", SHAPES_NORMAL)
+def test_gemm_raw_accumulator(op, shape):
+    L, K = _lib()
+    M, N, Kd, bn = shape
+    gen = torch.Generator().manual_seed(1000 + M + N + Kd + op)
+    a, af = make_operand(M, Kd, op, gen)
+    b, bf = make_operand(N, Kd, op, gen)
+    want = af.double() @ bf.double().t()
+    ad, bd = a.cuda(), b.cuda()
+    if op == L.OP_S8:
+        out = torch.full((M, N), -7, dtype=torch.int32, device="cuda")
+        st = K.gemm(ad, bd, out, op=op, out_type=L.OUT_S32, force_swap=0, force_block_n=bn)
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        assert torch.equal(out.cpu().double(), want), "s32 accumulators must be bit-exact"
+    else:
+        out = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+        st = K.gemm(ad, bd, out, op=op, out_type=L.OUT_F32, force_swap=0, force_block_n=bn)
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        scale = math.sqrt(Kd) * (16 if op == L.OP_E4M3 else 1)
+        check_close(out, want.float(), 2e-3 * scale, 1e-3, f"raw {shape}")
+
+
+@pytest.mark.parametrize("op", [0, 1, 2])
+@pytest.mark.parametrize("shape", [(10, 2560, 1024, 16), (10, 1024, 4096, 16), (1, 3072, 1024, 16),
+                                   (50, 8192, 1024, 64), (21, 1024, 2048, 32), (10, 32, 1024, 16),
+                                   (10, 1024, 32, 16)])
+def test_gemm_swapped_skinny(op, shape):
+    L, K = _lib()
+    M, N, Kd, bn = shape
+    gen = torch.Generator().manual_seed(2000 + M + N + Kd + op)
+    a, af = make_operand(M, Kd, op, gen)
+    b, bf = make_operand(N, Kd, op, gen)
+    want = af.double() @ bf.double().t()
+    if op == L.OP_S8:
+        out = torch.full((M, N), -7, dtype=torch.int32, device="cuda")
+        st = K.gemm(a.cuda(), b.cuda(), out, op=op, out_type=L.OUT_S32, force_swap=1, force_block_n=bn)
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        assert torch.equal(out.cpu().double(), want)
+    else:
+        out = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+        st = K.gemm(a.cuda(), b.cuda(), out, op=op, out_type=L.OUT_F32, force_swap=1, force_block_n=bn)
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        scale = math.sqrt(Kd) * (16 if op == L.OP_E4M3 else 1)
+        check_close(out, want.float(), 2e-3 * scale, 1e-3, f"swap {shape}")
+
+
+def test_gemm_batched_strided_views():
+    """Per-(view, head) attention logits out of a packed QKV buffer, as the vision tower uses."""
+    L, K = _lib()
+    views, heads, tokens, hd = 2, 4, 256, 72
+    width = heads * hd
+    gen = torch.Generator().manual_seed(7)
+    qkv = (torch.randn(views * tokens, 3 * width, generator=gen)).to(torch.bfloat16)
+    qkvd = qkv.cuda()
+    q4 = qkvd.view(views, tokens, 3, heads, hd)
+    qv = q4[:, :, 0].permute(0, 2, 1, 3)  # [views, heads, tokens, hd] strided view
+    kv = q4[:, :, 1].permute(0, 2, 1, 3)
+    out = torch.zeros(views, heads, tokens, tokens, dtype=torch.bfloat16, device="cuda")
+    alpha = 1.0 / math.sqrt(hd)
+    st = K.gemm(qv, kv, out, op=L.OP_BF16, alpha=alpha)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    qf = qkv.float().view(views, tokens, 3, heads, hd)
+    want = torch.einsum("vthd,vshd->vhts", qf[:, :, 0], qf[:, :, 1]) * alpha
+    check_close(out, rb(want), 2e-2, 1e-2, "batched logits")
+
+
+@pytest.mark.parametrize("block_n", [128, 256])
+def test_gemm_mn_major_b(block_n):
+    """P[M, keys] . V[keys, d] with V left row-major (MN-major B operand)."""
+    L, K = _lib()
+    M, keys, d = 200, 532, 256 if block_n == 256 else 72
+    gen = torch.Generator().manual_seed(11)
+    ld = 536
+    p = torch.zeros(M, ld, dtype=torch.bfloat16)
+    p[:, :keys] = torch.rand(M, keys, generator=gen).to(torch.bfloat16)
+    v = torch.randn(keys, d, generator=gen).to(torch.bfloat16)
+    out = torch.zeros(M, d, dtype=torch.float32, device="cuda")
+    pd = p.cuda()[:, :keys]
+    st = K.gemm(pd, v.cuda(), out, op=L.OP_BF16, out_type=L.OUT_F32, b_mn_major=True,
+                force_block_n=block_n)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    want = p[:, :keys].float() @ v.float()
+    check_close(out, want, 2e-2, 1e-3, "mn-major")
+
+
+def _epilogue_reference(mode, v, bias, residual, pos, gate, L):
+    M, N = v.shape
+    if mode == L.EPI_STORE:
+        o = rb(v)
+        if bias is not None:
+            o = rb(o + bias)
+        return o
+    if mode == L.EPI_BIAS_GELU:
+        return gelu_tanh(rb(v) + bias)
+    if mode == L.EPI_BIAS_SILU:
+        x = rb(v) + bias
+        return x / (1.0 + torch.exp(-x))
+    if mode == L.EPI_BIAS_RESIDUAL:
+        return rb(v) + residual + bias
+    if mode == L.EPI_BIAS_POS:
+        reps = (M + pos.shape[0] - 1) // pos.shape[0]
+        return rb(v) + pos.repeat(reps, 1)[:M] + bias
+    if mode == L.EPI_GATE_RESIDUAL:
+        return residual + rb(v) * gate
+    raise AssertionError(mode)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2, 3, 4, 5])
+@pytest.mark.parametrize("M,swap", [(300, 0), (10, 1), (50, 1)])
+@pytest.mark.parametrize("out_type", [0, 1])
+def test_gemm_epilogues(mode, M, swap, out_type):
+    L, K = _lib()
+    N, Kd = 384, 256
+    gen = torch.Generator().manual_seed(31 + mode * 7 + M)
+    a, af = make_operand(M, Kd, L.OP_BF16, gen)
+    b, bf = make_operand(N, Kd, L.OP_BF16, gen, 0.05)
+    bias = (torch.randn(N, generator=gen) * 0.1).to(torch.bfloat16)
+    residual = torch.randn(M, N, generator=gen).to(torch.bfloat16)
+    pos = torch.randn(64, N, generator=gen).to(torch.bfloat16)
+    gate = torch.randn(N, generator=gen).to(torch.bfloat16)
+    col_scale = torch.rand(N, generator=gen) + 0.5
+    v = (af.double() @ bf.double().t()).float() * 0.5 * col_scale
+    ref = _epilogue_reference(mode, v, bias.float(), residual.float(), pos.float(), gate.float(), L)
+    inv = 8.0
+    if out_type == L.OUT_BF16:
+        want = rb(ref)
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    else:
+        want = (ref * inv).clamp(-448, 448).to(torch.float8_e4m3fn).float()
+        out = torch.zeros(M, N, dtype=torch.float8_e4m3fn, device="cuda")
+    res_d = residual.cuda()
+    if mode in (L.EPI_BIAS_RESIDUAL, L.EPI_GATE_RESIDUAL) and out_type == L.OUT_BF16:
+        out.copy_(res_d)  # in-place residual update, as the engine does
+        res_arg = out
+    else:
+        res_arg = res_d
+    st = K.gemm(a.cuda(), b.cuda(), out, op=L.OP_BF16, mode=mode, out_type=out_type,
+                bias=bias.cuda(), residual=res_arg, pos=pos.cuda(), gate=gate.cuda(),
+                col_scale=col_scale.cuda(), alpha=0.5, out_inv_scale=inv, force_swap=swap)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    got = out.float().cpu()
+    # one bf16 / e4m3 ulp of slack for accumulation-order differences
+    ulp = want.abs() * (2 ** -7 if out_type == L.OUT_BF16 else 2 ** -2) + (1e-2 if out_type == L.OUT_BF16 else 0.3)
+    err = (got - want).abs()
+    frac_exact = (err == 0).float().mean().item()
+    assert (err <= ulp).all(), f"mode {mode}: max err {err.max().item()}"
+    assert frac_exact > 0.97, f"mode {mode}: only {frac_exact:.3f} bit-identical"
+
+
+@pytest.mark.parametrize("op", [0, 1, 2])
+@pytest.mark.parametrize("M,swap,bn", [(300, 0, 128), (300, 0, 256), (10, 1, 16), (50, 1, 64)])
+def test_gemm_geglu(op, M, swap, bn):
+    """gate|up interleaved in blocks of 64 weight rows; out = gelu(rb(g)) * rb(u)."""
+    L, K = _lib()
+    inner, Kd = 512, 256
+    gen = torch.Generator().manual_seed(77 + op + M)
+    a, af = make_operand(M, Kd, op, gen, 0.5 if op != L.OP_S8 else 1.0)
+    wg, wgf = make_operand(inner, Kd, op, gen, 0.05 if op != L.OP_S8 else 1.0)
+    wu, wuf = make_operand(inner, Kd, op, gen, 0.05 if op != L.OP_S8 else 1.0)
+    packed = torch.empty(2 * inner, Kd, dtype=wg.dtype)
+    pv = packed.view(inner // 64, 2, 64, Kd)
+    pv[:, 0] = wg.view(inner // 64, 64, Kd)
+    pv[:, 1] = wu.view(inner // 64, 64, Kd)
+    alpha = {0: 1.0, 1: 1.0 / 16, 2: 1e-3}[op]
+    g = rb((af.double() @ wgf.double().t()).float() * alpha)
+    u = rb((af.double() @ wuf.double().t()).float() * alpha)
+    want = rb(gelu_tanh(g) * u)
+    out = torch.zeros(M, inner, dtype=torch.bfloat16, device="cuda")
+    st = K.gemm(a.cuda(), packed.cuda(), out, op=op, mode=L.EPI_GEGLU, alpha=alpha,
+                force_swap=swap, force_block_n=bn)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    got = out.float().cpu()
+    err = (got - want).abs()
+    assert (err <= want.abs() * 2 ** -6 + 2e-2).all(), f"max err {err.max().item()}"
+    assert (err == 0).float().mean().item() > 0.95
+
+
+def test_gemm_rejects_bad_arguments():
+    L, K = _lib()
+    from apxinf_b200 import Pi05Error
+    a = torch.zeros(16, 64, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(16, 16, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(Pi05Error):  # leading dimension not a multiple of 16 bytes
+        K.gemm(a[:, :60][:, :60].contiguous()[:, :52], a[:, :52], out, op=L.OP_BF16)
+    with pytest.raises(Pi05Error):  # s32 output only for int8 operands
+        K.gemm(a, a, out, op=L.OP_BF16, out_type=L.OUT_S32)
