@@ -1,0 +1,173 @@
+// Engine-level extern "C" entry points (declared in include/pi05_b200.h).
+#include <new>
+
+#include "../../include/pi05_b200.h"
+#include "engine.h"
+
+struct Pi05Engine {
+  pi05::Engine* impl;
+};
+struct Pi05Graph {
+  pi05::PreparedGraph* impl;
+};
+
+namespace {
+
+pi05::ModelConfig to_internal(const Pi05ModelConfig& c) {
+  pi05::ModelConfig m;
+  m.action_dim = c.action_dim;
+  m.action_horizon = c.action_horizon;
+  m.max_token_len = c.max_token_len;
+  m.num_flow_steps = c.num_flow_steps;
+  m.num_views = c.num_views;
+  m.image_size = c.image_size;
+  m.patch_size = c.patch_size;
+  m.vision_width = c.vision_width;
+  m.vision_depth = c.vision_depth;
+  m.vision_mlp_dim = c.vision_mlp_dim;
+  m.vision_heads = c.vision_heads;
+  m.vision_head_dim = c.vision_head_dim;
+  m.vocab_size = c.vocab_size;
+  m.rms_norm_eps = c.rms_norm_eps;
+  m.layer_norm_eps = c.layer_norm_eps;
+  m.rope_theta = c.rope_theta;
+  m.time_min_period = c.time_min_period;
+  m.time_max_period = c.time_max_period;
+  auto gemma = [](const Pi05Gemma& g) {
+    return pi05::GemmaDims{g.width, g.depth, g.mlp_dim, g.num_heads, g.num_kv_heads, g.head_dim};
+  };
+  m.language = gemma(c.language);
+  m.action = gemma(c.action_expert);
+  return m;
+}
+
+}  // namespace
+
+extern "C" void pi05_default_config(Pi05ModelConfig* c) {
+  if (c == nullptr) return;
+  const pi05::ModelConfig m;
+  c->action_dim = m.action_dim;
+  c->action_horizon = m.action_horizon;
+  c->max_token_len = m.max_token_len;
+  c->num_flow_steps = m.num_flow_steps;
+  c->num_views = m.num_views;
+  c->image_size = m.image_size;
+  c->patch_size = m.patch_size;
+  c->vision_width = m.vision_width;
+  c->vision_depth = m.vision_depth;
+  c->vision_mlp_dim = m.vision_mlp_dim;
+  c->vision_heads = m.vision_heads;
+  c->vision_head_dim = m.vision_head_dim;
+  c->vocab_size = m.vocab_size;
+  c->rms_norm_eps = m.rms_norm_eps;
+  c->layer_norm_eps = m.layer_norm_eps;
+  c->rope_theta = m.rope_theta;
+  c->time_min_period = m.time_min_period;
+  c->time_max_period = m.time_max_period;
+  auto gemma = [](const pi05::GemmaDims& g) {
+    return Pi05Gemma{g.width, g.depth, g.mlp_dim, g.num_heads, g.num_kv_heads, g.head_dim};
+  };
+  c->language = gemma(m.language);
+  c->action_expert = gemma(m.action);
+}
+
+extern "C" int pi05_engine_create(const Pi05ModelConfig* config, int32_t dtype, int32_t device,
+                                  uint64_t seed, float fp8_act_scale, Pi05Engine** out) {
+  if (config == nullptr || out == nullptr || device < 0) return pi05::kPi05ErrInvalidValue;
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || device >= count) {
+    return pi05::record_cuda(cudaErrorNoDevice);
+  }
+  auto* impl = new (std::nothrow) pi05::Engine(to_internal(*config), dtype, device, seed,
+                                               dtype == PI05_DTYPE_FP8 ? fp8_act_scale : 1.0f);
+  if (impl == nullptr) return pi05::kPi05ErrInvalidValue;
+  const int rc = impl->init();
+  if (rc != pi05::kPi05Ok) {
+    delete impl;
+    return rc;
+  }
+  *out = new Pi05Engine{impl};
+  return pi05::kPi05Ok;
+}
+
+extern "C" void pi05_engine_destroy(Pi05Engine* engine) {
+  if (engine == nullptr) return;
+  delete engine->impl;
+  delete engine;
+}
+
+extern "C" size_t pi05_engine_weight_bytes(const Pi05Engine* engine) {
+  return engine == nullptr ? 0 : engine->impl->weight_bytes();
+}
+
+extern "C" int pi05_engine_read_weight(Pi05Engine* engine, const char* name, void* host,
+                                       size_t capacity, size_t* actual) {
+  if (engine == nullptr || name == nullptr) return pi05::kPi05ErrInvalidValue;
+  return engine->impl->read_weight(name, host, capacity, actual);
+}
+
+extern "C" int pi05_engine_capture(Pi05Engine* engine, int32_t token_count, int32_t image_layout,
+                                   int32_t batch, Pi05Graph** out) {
+  if (engine == nullptr || out == nullptr) return pi05::kPi05ErrInvalidValue;
+  *out = nullptr;
+  if (image_layout != PI05_IMAGE_NHWC && image_layout != PI05_IMAGE_NCHW) {
+    return pi05::kPi05ErrInvalidValue;
+  }
+  auto* impl = new (std::nothrow) pi05::PreparedGraph(engine->impl, token_count, image_layout, batch);
+  if (impl == nullptr) return pi05::kPi05ErrInvalidValue;
+  int rc = impl->prepare();
+  if (rc == pi05::kPi05Ok) rc = impl->run_eager();  // warm pass before recording
+  if (rc == pi05::kPi05Ok) rc = impl->sync();
+  if (rc == pi05::kPi05Ok) rc = impl->capture();
+  if (rc != pi05::kPi05Ok) {
+    delete impl;
+    return rc;
+  }
+  *out = new Pi05Graph{impl};
+  return pi05::kPi05Ok;
+}
+
+extern "C" void pi05_graph_destroy(Pi05Graph* graph) {
+  if (graph == nullptr) return;
+  delete graph->impl;
+  delete graph;
+}
+
+#define PI05_GRAPH_CALL(expr) (graph == nullptr ? pi05::kPi05ErrInvalidValue : graph->impl->expr)
+
+extern "C" int pi05_graph_update_raw_image_inputs(Pi05Graph* graph, const uint8_t* images,
+                                                  const uint32_t* token_ids,
+                                                  const uint16_t* noise_bf16) {
+  return PI05_GRAPH_CALL(update_inputs(images, token_ids, noise_bf16));
+}
+extern "C" int pi05_graph_replay(Pi05Graph* graph) { return PI05_GRAPH_CALL(replay()); }
+extern "C" int pi05_graph_run_eager(Pi05Graph* graph) { return PI05_GRAPH_CALL(run_eager()); }
+extern "C" int pi05_graph_sync(Pi05Graph* graph) { return PI05_GRAPH_CALL(sync()); }
+extern "C" int pi05_graph_output(Pi05Graph* graph, float* host_out) {
+  return PI05_GRAPH_CALL(output(host_out));
+}
+extern "C" int pi05_graph_time_replays(Pi05Graph* graph, int32_t iterations, float* ms_each) {
+  return PI05_GRAPH_CALL(time_replays(iterations, ms_each));
+}
+extern "C" int pi05_graph_stage_times(Pi05Graph* graph, float* ms3) {
+  return PI05_GRAPH_CALL(stage_times(ms3));
+}
+extern "C" size_t pi05_graph_workspace_bytes(const Pi05Graph* graph) {
+  return graph == nullptr ? 0 : graph->impl->workspace_bytes();
+}
+extern "C" size_t pi05_graph_workspace_used_bytes(const Pi05Graph* graph) {
+  return graph == nullptr ? 0 : graph->impl->workspace_used();
+}
+extern "C" int32_t pi05_graph_num_launches(const Pi05Graph* graph) {
+  return graph == nullptr ? 0 : graph->impl->num_launches();
+}
+extern "C" const char* pi05_graph_launch_name(const Pi05Graph* graph, int32_t index) {
+  if (graph == nullptr || index < 0 || index >= graph->impl->num_launches()) return nullptr;
+  return graph->impl->ops()[index].name.c_str();
+}
+extern "C" int pi05_graph_read_tensor(Pi05Graph* graph, const char* name, void* host,
+                                      size_t capacity, size_t* actual) {
+  if (name == nullptr) return pi05::kPi05ErrInvalidValue;
+  return PI05_GRAPH_CALL(read_tensor(name, host, capacity, actual));
+}

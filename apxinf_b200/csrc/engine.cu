@@ -1,0 +1,874 @@
+#include "engine.h"
+
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+#include "row_kernels.cuh"
+#include "weights.cuh"
+
+namespace pi05 {
+
+#define PI05_CUDA(expr)                                  \
+  do {                                                   \
+    const cudaError_t pi05_err_ = (expr);                \
+    if (pi05_err_ != cudaSuccess) return record_cuda(pi05_err_); \
+  } while (0)
+
+#define PI05_TRY(expr)                     \
+  do {                                     \
+    const int pi05_rc_ = (expr);           \
+    if (pi05_rc_ != kPi05Ok) return pi05_rc_; \
+  } while (0)
+
+namespace {
+
+uint16_t bf16_bits(float value) {
+  uint32_t bits;
+  std::memcpy(&bits, &value, 4);
+  if ((bits & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>((bits >> 16) | 0x40u);
+  const uint32_t rounding = ((bits >> 16) & 1u) + 0x7fffu;
+  return static_cast<uint16_t>((bits + rounding) >> 16);
+}
+
+float bf16_to_float(uint16_t bits) {
+  const uint32_t wide = static_cast<uint32_t>(bits) << 16;
+  float value;
+  std::memcpy(&value, &wide, 4);
+  return value;
+}
+
+int elem_size(int prec) { return prec == kPrecBf16 ? 2 : 1; }
+int op_of(int prec) { return prec == kPrecBf16 ? kOpBf16 : prec == kPrecFp8 ? kOpE4m3 : kOpS8; }
+long long round_up(long long v, long long m) { return (v + m - 1) / m * m; }
+
+}  // namespace
+
+int ModelConfig::validate() const {
+  const bool ok =
+      action_dim > 0 && action_dim % 8 == 0 && action_horizon > 0 && action_horizon <= 64 &&
+      num_flow_steps > 0 && num_views > 0 && image_size > 0 && patch_size > 0 &&
+      image_size % patch_size == 0 && vision_width == vision_heads * vision_head_dim &&
+      vision_width % 16 == 0 && vision_head_dim % 8 == 0 && vision_mlp_dim % 16 == 0 &&
+      vocab_size > 0 && language.width % 16 == 0 && action.width % 16 == 0 &&
+      language.mlp_dim % 64 == 0 && action.mlp_dim % 64 == 0 && language.num_kv_heads == 1 &&
+      action.num_kv_heads == 1 && language.head_dim == action.head_dim &&
+      language.num_heads == action.num_heads && language.depth == action.depth &&
+      language.head_dim % 16 == 0 && max_token_len > 0 &&
+      num_views * patches_per_view() + max_token_len + action_horizon <= 1024 &&
+      patches_per_view() % 8 == 0;
+  return ok ? kPi05Ok : kPi05ErrInvalidValue;
+}
+
+// ---------------------------------------------------------------------------
+// Engine: weights
+// ---------------------------------------------------------------------------
+
+Engine::Engine(const ModelConfig& cfg, int precision, int device, uint64_t seed, float act_scale)
+    : cfg_(cfg), prec_(precision), device_(device), seed_(seed), act_scale_(act_scale) {}
+
+Engine::~Engine() {
+  cudaSetDevice(device_);
+  if (stream_ != nullptr) cudaStreamSynchronize(stream_);
+  for (void* p : allocations_) cudaFree(p);
+  if (stream_ != nullptr) cudaStreamDestroy(stream_);
+}
+
+void* Engine::dmalloc(size_t bytes) {
+  void* p = nullptr;
+  if (cudaMalloc(&p, std::max<size_t>(bytes, 256)) != cudaSuccess) return nullptr;
+  allocations_.push_back(p);
+  weight_bytes_ += bytes;
+  return p;
+}
+
+int Engine::make_linear(const std::string& prefix, const std::vector<std::string>& parts, int k,
+                        const std::vector<int>& ns, bool bias, bool interleave, Linear* out) {
+  int n_total = 0;
+  for (int n : ns) n_total += n;
+  const int es = elem_size(prec_);
+  const long long ldk = round_up(k, 16);
+  out->n = n_total;
+  out->k = k;
+  out->ldk = ldk;
+  out->w = dmalloc(static_cast<size_t>(n_total) * ldk * es);
+  if (out->w == nullptr) return record_cuda(cudaErrorMemoryAllocation);
+  if (bias) {
+    out->bias = dmalloc(static_cast<size_t>(n_total) * 2);
+    if (out->bias == nullptr) return record_cuda(cudaErrorMemoryAllocation);
+  }
+  void* stage = prec_ == kPrecBf16 ? out->w : tmp_stage_;
+  const size_t stage_bytes = static_cast<size_t>(n_total) * ldk * 2;
+  if (prec_ != kPrecBf16 && stage_bytes > tmp_stage_bytes_) return kPi05ErrInvalidValue;
+  PI05_CUDA(cudaMemsetAsync(stage, 0, stage_bytes, stream_));
+  int row_offset = 0;
+  for (size_t i = 0; i < parts.size(); ++i) {
+    const long long count = static_cast<long long>(k) * ns[i];
+    if (static_cast<size_t>(count) * 2 > tmp_src_bytes_) return kPi05ErrInvalidValue;
+    PI05_CUDA(launch_lcg_fill(tmp_src_, seed_, cursor_, count, stream_));
+    cursor_ += static_cast<uint64_t>(count);
+    PI05_CUDA(launch_transpose_pack(tmp_src_, stage, k, ns[i], ldk, row_offset,
+                                    interleave ? 1 : 0, static_cast<int>(i), stream_));
+    if (bias) {
+      PI05_CUDA(launch_lcg_fill(static_cast<uint16_t*>(out->bias) + row_offset, seed_, cursor_,
+                                ns[i], stream_));
+      cursor_ += static_cast<uint64_t>(ns[i]);
+    }
+    row_offset += ns[i];
+  }
+  if (prec_ != kPrecBf16) {
+    out->col_scale = static_cast<float*>(dmalloc(static_cast<size_t>(n_total) * 4));
+    if (out->col_scale == nullptr) return record_cuda(cudaErrorMemoryAllocation);
+    PI05_CUDA(launch_quantize_weight_rows(stage, out->w, out->col_scale, n_total, k, ldk,
+                                          prec_ == kPrecInt8 ? 1 : 0, stream_));
+  }
+  named_[prefix + ".weight"] = {out->w, static_cast<size_t>(n_total) * ldk * es};
+  if (out->col_scale != nullptr) named_[prefix + ".scale"] = {out->col_scale, (size_t)n_total * 4};
+  if (out->bias != nullptr) named_[prefix + ".bias"] = {out->bias, (size_t)n_total * 2};
+  return kPi05Ok;
+}
+
+int Engine::init() {
+  PI05_TRY(cfg_.validate());
+  if (prec_ < kPrecBf16 || prec_ > kPrecInt8 || !(act_scale_ > 0.0f)) return kPi05ErrInvalidValue;
+  PI05_CUDA(cudaSetDevice(device_));
+  PI05_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+  status_ = static_cast<int*>(dmalloc(256));
+  if (status_ == nullptr) return record_cuda(cudaErrorMemoryAllocation);
+  PI05_CUDA(cudaMemsetAsync(status_, 0, 256, stream_));
+
+  // RoPE tables: float frequency and angle, as the reference's powf / sincosf path computes
+  // them (crates/apxinf-cuda/kernels/custom/fused.cuh:471-490), evaluated in double.
+  const int half = cfg_.language.head_dim / 2;
+  rope_positions = cfg_.num_views * cfg_.patches_per_view() + cfg_.max_token_len + cfg_.action_horizon;
+  std::vector<float> host_cos(static_cast<size_t>(rope_positions) * half), host_sin(host_cos.size());
+  for (int i = 0; i < half; ++i) {
+    const float freq = static_cast<float>(
+        std::pow(static_cast<double>(cfg_.rope_theta), -static_cast<double>(i) / half));
+    for (int pos = 0; pos < rope_positions; ++pos) {
+      const float angle = static_cast<float>(pos) * freq;
+      host_cos[static_cast<size_t>(pos) * half + i] = static_cast<float>(std::cos((double)angle));
+      host_sin[static_cast<size_t>(pos) * half + i] = static_cast<float>(std::sin((double)angle));
+    }
+  }
+  rope_cos = static_cast<float*>(dmalloc(host_cos.size() * 4));
+  rope_sin = static_cast<float*>(dmalloc(host_sin.size() * 4));
+  if (rope_cos == nullptr || rope_sin == nullptr) return record_cuda(cudaErrorMemoryAllocation);
+  PI05_CUDA(cudaMemcpyAsync(rope_cos, host_cos.data(), host_cos.size() * 4, cudaMemcpyHostToDevice, stream_));
+  PI05_CUDA(cudaMemcpyAsync(rope_sin, host_sin.data(), host_sin.size() * 4, cudaMemcpyHostToDevice, stream_));
+  PI05_CUDA(cudaStreamSynchronize(stream_));
+
+  // scratch for generation: largest [in, out] source and largest packed staging matrix
+  const GemmaDims& lg = cfg_.language;
+  const GemmaDims& ac = cfg_.action;
+  size_t max_src = 0, max_stage = 0;
+  auto consider = [&](long long k, long long n_part, long long n_total) {
+    max_src = std::max(max_src, static_cast<size_t>(k * n_part * 2));
+    max_stage = std::max(max_stage, static_cast<size_t>(round_up(k, 16) * n_total * 2));
+  };
+  const int vw = cfg_.vision_width;
+  consider(vw, vw, 3 * vw);
+  consider(vw, cfg_.vision_mlp_dim, cfg_.vision_mlp_dim);
+  consider(cfg_.vision_mlp_dim, vw, vw);
+  consider(cfg_.patch_width(), vw, vw);
+  consider(vw, lg.width, lg.width);
+  for (const GemmaDims* g : {&lg, &ac}) {
+    const int qw = g->num_heads * g->head_dim;
+    consider(g->width, qw, qw + 2 * g->head_dim);
+    consider(qw, g->width, g->width);
+    consider(g->width, g->mlp_dim, 2 * g->mlp_dim);
+    consider(g->mlp_dim, g->width, g->width);
+  }
+  consider(ac.width, 3 * ac.width, 3 * ac.width);
+  consider(cfg_.action_dim, ac.width, ac.width);
+  consider(ac.width, cfg_.action_dim, cfg_.action_dim);
+  PI05_CUDA(cudaMalloc(&tmp_src_, max_src));
+  tmp_src_bytes_ = max_src;
+  if (prec_ != kPrecBf16) {
+    PI05_CUDA(cudaMalloc(&tmp_stage_, max_stage));
+    tmp_stage_bytes_ = max_stage;
+  }
+
+  // Generation order = Pi05Weights::synthetic (crates/apxinf-model/src/pi05/weights.rs:255-330).
+  cursor_ = 0;
+  vision.resize(cfg_.vision_depth);
+  for (int i = 0; i < cfg_.vision_depth; ++i) {
+    const std::string p = "vision." + std::to_string(i);
+    PI05_TRY(make_linear(p + ".qkv", {"q", "k", "v"}, vw, {vw, vw, vw}, true, false, &vision[i].qkv));
+    PI05_TRY(make_linear(p + ".o", {"o"}, vw, {vw}, true, false, &vision[i].o));
+    PI05_TRY(make_linear(p + ".fc1", {"fc1"}, vw, {cfg_.vision_mlp_dim}, true, false, &vision[i].fc1));
+    PI05_TRY(make_linear(p + ".fc2", {"fc2"}, cfg_.vision_mlp_dim, {vw}, true, false, &vision[i].fc2));
+  }
+  PI05_TRY(make_linear("vision.patch_embedding", {"w"}, cfg_.patch_width(), {vw}, true, false, &patch));
+  {
+    const long long count = static_cast<long long>(cfg_.patches_per_view()) * vw;
+    position_embedding = dmalloc(count * 2);
+    if (position_embedding == nullptr) return record_cuda(cudaErrorMemoryAllocation);
+    PI05_CUDA(launch_lcg_fill(position_embedding, seed_, cursor_, count, stream_));
+    cursor_ += count;
+    named_["vision.position_embedding"] = {position_embedding, (size_t)count * 2};
+  }
+  PI05_TRY(make_linear("vision.projector", {"w"}, vw, {lg.width}, true, false, &projector));
+  {
+    const long long count = static_cast<long long>(cfg_.vocab_size) * lg.width;
+    token_embedding = dmalloc(count * 2);
+    if (token_embedding == nullptr) return record_cuda(cudaErrorMemoryAllocation);
+    PI05_CUDA(launch_lcg_fill(token_embedding, seed_, cursor_, count, stream_));
+    cursor_ += count;
+    named_["token_embedding"] = {token_embedding, (size_t)count * 2};
+  }
+  language.resize(lg.depth);
+  for (int i = 0; i < lg.depth; ++i) {
+    const std::string p = "language." + std::to_string(i);
+    const int qw = lg.num_heads * lg.head_dim;
+    PI05_TRY(make_linear(p + ".qkv", {"q", "k", "v"}, lg.width, {qw, lg.head_dim, lg.head_dim}, false, false, &language[i].qkv));
+    PI05_TRY(make_linear(p + ".o", {"o"}, qw, {lg.width}, false, false, &language[i].o));
+    PI05_TRY(make_linear(p + ".gate_up", {"gate", "up"}, lg.width, {lg.mlp_dim, lg.mlp_dim}, false, true, &language[i].gate_up));
+    PI05_TRY(make_linear(p + ".down", {"down"}, lg.mlp_dim, {lg.width}, false, false, &language[i].down));
+  }
+  action.resize(ac.depth);
+  for (int i = 0; i < ac.depth; ++i) {
+    const std::string p = "action." + std::to_string(i);
+    const int qw = ac.num_heads * ac.head_dim;
+    PI05_TRY(make_linear(p + ".input_style", {"w"}, ac.width, {3 * ac.width}, true, false, &action[i].input_style));
+    PI05_TRY(make_linear(p + ".qkv", {"q", "k", "v"}, ac.width, {qw, ac.head_dim, ac.head_dim}, false, false, &action[i].qkv));
+    PI05_TRY(make_linear(p + ".o", {"o"}, qw, {ac.width}, false, false, &action[i].o));
+    PI05_TRY(make_linear(p + ".post_style", {"w"}, ac.width, {3 * ac.width}, true, false, &action[i].post_style));
+    PI05_TRY(make_linear(p + ".gate_up", {"gate", "up"}, ac.width, {ac.mlp_dim, ac.mlp_dim}, false, true, &action[i].gate_up));
+    PI05_TRY(make_linear(p + ".down", {"down"}, ac.mlp_dim, {ac.width}, false, false, &action[i].down));
+  }
+  PI05_TRY(make_linear("action.final_style", {"w"}, ac.width, {3 * ac.width}, true, false, &final_style));
+  PI05_TRY(make_linear("action_in", {"w"}, cfg_.action_dim, {ac.width}, true, false, &action_in));
+  PI05_TRY(make_linear("action_out", {"w"}, ac.width, {cfg_.action_dim}, true, false, &action_out));
+  PI05_TRY(make_linear("time_mlp_in", {"w"}, ac.width, {ac.width}, true, false, &time_in));
+  PI05_TRY(make_linear("time_mlp_out", {"w"}, ac.width, {ac.width}, true, false, &time_out));
+  PI05_CUDA(cudaStreamSynchronize(stream_));
+  cudaFree(tmp_src_);
+  tmp_src_ = nullptr;
+  if (tmp_stage_ != nullptr) cudaFree(tmp_stage_);
+  tmp_stage_ = nullptr;
+  return kPi05Ok;
+}
+
+int Engine::read_weight(const char* name, void* host, size_t capacity, size_t* actual) {
+  auto it = named_.find(name);
+  if (it == named_.end()) return kPi05ErrInvalidValue;
+  if (actual != nullptr) *actual = it->second.second;
+  if (host == nullptr) return kPi05Ok;
+  if (capacity < it->second.second) return kPi05ErrInvalidValue;
+  PI05_CUDA(cudaSetDevice(device_));
+  PI05_CUDA(cudaMemcpy(host, it->second.first, it->second.second, cudaMemcpyDeviceToHost));
+  return kPi05Ok;
+}
+
+// ---------------------------------------------------------------------------
+// PreparedGraph
+// ---------------------------------------------------------------------------
+
+PreparedGraph::PreparedGraph(Engine* engine, int token_count, int nchw, int batch)
+    : e_(engine), T_(token_count), nchw_(nchw), B_(batch) {
+  const ModelConfig& c = e_->cfg();
+  V_ = c.num_views * c.patches_per_view();
+  P_ = V_ + T_;
+  H_ = c.action_horizon;
+  S_ = c.num_flow_steps;
+}
+
+PreparedGraph::~PreparedGraph() {
+  cudaSetDevice(e_->device());
+  cudaStreamSynchronize(e_->stream());
+  if (exec_ != nullptr) cudaGraphExecDestroy(exec_);
+  if (graph_ != nullptr) cudaGraphDestroy(graph_);
+  if (arena_base_ != nullptr) cudaFree(arena_base_);
+  if (h_out_ != nullptr) cudaFreeHost(h_out_);
+}
+
+void PreparedGraph::add_kernel(const char* name, std::function<cudaError_t(cudaStream_t)> fn) {
+  if (measuring_) return;
+  Op op;
+  op.name = name;
+  op.stage = stage_;
+  op.launch = std::move(fn);
+  ops_.push_back(std::move(op));
+}
+
+int PreparedGraph::add_gemm(const char* name, const GemmProblem& problem) {
+  if (measuring_) return kPi05Ok;
+  Op op;
+  op.name = name;
+  op.stage = stage_;
+  op.is_gemm = true;
+  PI05_TRY(gemm_plan_build(problem, &op.plan));
+  ops_.push_back(std::move(op));
+  return kPi05Ok;
+}
+
+Act PreparedGraph::make_act(int rows, long long ld) {
+  Act a;
+  a.rows = rows;
+  a.ld = ld;
+  const int prec = e_->precision();
+  a.data = arena_.alloc(static_cast<size_t>(rows) * ld * elem_size(prec));
+  if (prec == kPrecInt8) {
+    a.row_scale = static_cast<float*>(arena_.alloc(static_cast<size_t>(rows) * 4));
+    a.wide = arena_.alloc(static_cast<size_t>(rows) * ld * 2);
+  }
+  return a;
+}
+
+// out = epilogue(in . w^T) with the precision's operand type and scales.
+int PreparedGraph::linear(const char* name, const Act& in, int rows, const Linear& w, int mode,
+                          void* out, long long ldc, int out_type, const void* residual,
+                          const void* gate, const void* pos, int pos_rows, float out_inv_scale,
+                          int nb0, long long a_sb0, long long out_sb0) {
+  GemmProblem q;
+  const int prec = e_->precision();
+  q.op = op_of(prec);
+  q.M = rows;
+  q.N = w.n;
+  q.K = static_cast<int>(std::min<long long>(w.ldk, in.ld));
+  q.nb0 = nb0;
+  q.a = GemmOperand{in.data, rows, in.ld, a_sb0, 0};
+  q.b = GemmOperand{w.w, w.n, w.ldk, 0, 0};
+  q.out = out;
+  q.ldc = ldc;
+  q.out_sb0 = out_sb0;
+  q.out_type = out_type;
+  q.mode = mode;
+  q.residual = residual;
+  q.bias = w.bias;
+  q.col_scale = w.col_scale;
+  q.row_scale = prec == kPrecInt8 ? in.row_scale : nullptr;
+  q.row_scale_sb0 = nb0 > 1 ? rows : 0;
+  q.pos = pos;
+  q.pos_rows = pos_rows;
+  q.pos_ld = w.n;
+  q.gate = gate;
+  q.alpha = prec == kPrecFp8 ? e_->act_scale() : 1.0f;
+  q.out_inv_scale = out_inv_scale;
+  q.status = e_->status();
+  return add_gemm(name, q);
+}
+
+// GEMM whose result feeds another GEMM: written in the precision's operand form.
+int PreparedGraph::linear_to_act(const char* name, const Act& in, int rows, const Linear& w,
+                                 int mode, Act* out) {
+  const int prec = e_->precision();
+  const float inv = 1.0f / e_->act_scale();
+  if (prec == kPrecBf16) {
+    return linear(name, in, rows, w, mode, out->data, out->ld, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f);
+  }
+  if (prec == kPrecFp8) {
+    return linear(name, in, rows, w, mode, out->data, out->ld, kOutE4m3, nullptr, nullptr, nullptr, 1, inv);
+  }
+  PI05_TRY(linear(name, in, rows, w, mode, out->wide, out->ld, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
+  const void* wide = out->wide;
+  int8_t* data = static_cast<int8_t*>(out->data);
+  float* scale = out->row_scale;
+  const int cols = static_cast<int>(out->ld);
+  add_kernel("quantize_rows_int8", [=](cudaStream_t s) {
+    return launch_quantize_rows_int8(wide, data, scale, rows, cols, cols, cols, s);
+  });
+  return kPi05Ok;
+}
+
+int PreparedGraph::norm_to_act(const char* name, const void* x, int rows, int cols, int kind,
+                               const void* style, float eps, Act* out) {
+  NormArgs a{};
+  a.input = x;
+  a.output = out->data;
+  a.row_scale = out->row_scale;
+  a.style = style;
+  a.rows = rows;
+  a.cols = cols;
+  a.eps = eps;
+  a.inv_scale = 1.0f / e_->act_scale();
+  a.kind = kind;
+  const int prec = e_->precision();
+  a.out = prec == kPrecBf16 ? kRowBf16 : prec == kPrecFp8 ? kRowE4m3 : kRowInt8;
+  add_kernel(name, [a](cudaStream_t s) { return launch_norm(a, s); });
+  return kPi05Ok;
+}
+
+// softmax(scale * q k^T) v as two tensor-core GEMMs around a row softmax, the
+// logits and probabilities held as bf16 like the reference's MQA
+// (crates/apxinf-cuda/adapters/cublas_adapter.cu:89-132). v is consumed in its
+// natural [keys, head_dim] layout as an MN-major operand.
+int PreparedGraph::attention(const char* name, const void* q, long long q_ld, long long q_sb0,
+                             long long q_sb1, const void* k, long long k_ld, long long k_sb0,
+                             long long k_sb1, const void* v, long long v_ld, long long v_sb0,
+                             long long v_sb1, int q_rows, int keys, int head_dim, int nb0, int nb1,
+                             float scale, void* logits, Act* out, long long out_ld,
+                             long long out_sb0, long long out_sb1) {
+  const long long ld_s = round_up(keys, 8);
+  const long long s_sb0 = static_cast<long long>(q_rows) * ld_s;
+  const long long s_sb1 = s_sb0 * nb0;
+  GemmProblem s;
+  s.op = kOpBf16;
+  s.M = q_rows;
+  s.N = keys;
+  s.K = head_dim;
+  s.nb0 = nb0;
+  s.nb1 = nb1;
+  s.a = GemmOperand{q, q_rows, q_ld, q_sb0, q_sb1};
+  s.b = GemmOperand{k, keys, k_ld, k_sb0, k_sb1};
+  s.out = logits;
+  s.ldc = ld_s;
+  s.out_sb0 = s_sb0;
+  s.out_sb1 = s_sb1;
+  s.alpha = scale;
+  s.status = e_->status();
+  PI05_TRY(add_gemm((std::string(name) + ".qk").c_str(), s));
+  const int batches = nb0 * nb1;
+  add_kernel((std::string(name) + ".softmax").c_str(), [=](cudaStream_t st) {
+    return launch_softmax(logits, q_rows, batches, s_sb0, keys, ld_s, st);
+  });
+  GemmProblem pv;
+  pv.op = kOpBf16;
+  pv.M = q_rows;
+  pv.N = head_dim;
+  pv.K = keys;
+  pv.nb0 = nb0;
+  pv.nb1 = nb1;
+  pv.a = GemmOperand{logits, q_rows, ld_s, s_sb0, s_sb1};
+  pv.b = GemmOperand{v, keys, v_ld, v_sb0, v_sb1};
+  pv.b_mn_major = true;
+  const int prec = e_->precision();
+  pv.out = prec == kPrecInt8 ? out->wide : out->data;
+  pv.ldc = out_ld;
+  pv.out_sb0 = out_sb0;
+  pv.out_sb1 = out_sb1;
+  pv.out_type = prec == kPrecFp8 ? kOutE4m3 : kOutBf16;
+  pv.out_inv_scale = 1.0f / e_->act_scale();
+  pv.status = e_->status();
+  PI05_TRY(add_gemm((std::string(name) + ".pv").c_str(), pv));
+  if (prec == kPrecInt8) {
+    const void* wide = out->wide;
+    int8_t* data = static_cast<int8_t*>(out->data);
+    float* rs = out->row_scale;
+    const int rows = out->rows, cols = static_cast<int>(out->ld);
+    add_kernel("quantize_rows_int8", [=](cudaStream_t st) {
+      return launch_quantize_rows_int8(wide, data, rs, rows, cols, cols, cols, st);
+    });
+  }
+  return kPi05Ok;
+}
+
+int PreparedGraph::build(bool measuring) {
+  measuring_ = measuring;
+  ops_.clear();
+  tensors_.clear();
+  const ModelConfig& c = e_->cfg();
+  const int prec = e_->precision();
+  const float inv_act = 1.0f / e_->act_scale();
+  const GemmaDims& lg = c.language;
+  const GemmaDims& ac = c.action;
+  const int vw = c.vision_width, pp = c.patches_per_view(), heads_v = c.vision_heads,
+            hd_v = c.vision_head_dim;
+  const int Rv = B_ * V_, Rp = B_ * P_, Ra = B_ * H_;
+  const int n_images = B_ * c.num_views;
+  const int cache_rows = P_ + H_;
+  const int hd = lg.head_dim, qh = lg.num_heads, qw = qh * hd;
+  const long long patch_ld = e_->patch.ldk;
+
+  // ---- inputs / persistent buffers ----
+  d_images_ = static_cast<uint8_t*>(arena_.alloc((size_t)n_images * c.image_size * c.image_size * 3));
+  d_tokens_ = static_cast<uint32_t*>(arena_.alloc((size_t)B_ * T_ * 4));
+  d_noise_ = arena_.alloc((size_t)Ra * c.action_dim * 2);
+  d_state_ = arena_.alloc((size_t)Ra * c.action_dim * 2);
+  d_styles_ = arena_.alloc((size_t)(2 * ac.depth + 1) * S_ * 3 * ac.width * 2);
+  d_time_emb_ = arena_.alloc((size_t)S_ * ac.width * 2);
+  note("state", d_state_, (size_t)Ra * c.action_dim * 2);
+  note("styles", d_styles_, (size_t)(2 * ac.depth + 1) * S_ * 3 * ac.width * 2);
+  std::vector<void*> k_cache(lg.depth), v_cache(lg.depth);
+  for (int l = 0; l < lg.depth; ++l) {
+    k_cache[l] = arena_.alloc((size_t)B_ * cache_rows * hd * 2);
+    v_cache[l] = arena_.alloc((size_t)B_ * cache_rows * hd * 2);
+    note(("kv." + std::to_string(l) + ".k").c_str(), k_cache[l], (size_t)B_ * cache_rows * hd * 2);
+    note(("kv." + std::to_string(l) + ".v").c_str(), v_cache[l], (size_t)B_ * cache_rows * hd * 2);
+  }
+
+  // ---- style pre-pass buffers (conditioning is per flow step, not per sample) ----
+  Act time_in_act = make_act(S_, ac.width);
+  Act time_hidden = make_act(S_, ac.width);
+  Act cond = make_act(S_, ac.width);
+
+  if (styles_only_) {
+    // time embedding -> conditioning -> 2*depth+1 style vectors, all steps as GEMM rows
+    // (crates/apxinf-model/src/pi05/bf16_runtime.rs:258-303).
+    stage_ = 3;
+    const void* emb = d_time_emb_;
+    if (prec == kPrecBf16) {
+      time_in_act.data = d_time_emb_;
+    } else if (prec == kPrecFp8) {
+      uint8_t* dst = static_cast<uint8_t*>(time_in_act.data);
+      const long long count = (long long)S_ * ac.width;
+      add_kernel("quantize_time", [=](cudaStream_t s) { return launch_quantize_e4m3(emb, dst, count, inv_act, s); });
+    } else {
+      int8_t* dst = static_cast<int8_t*>(time_in_act.data);
+      float* rs = time_in_act.row_scale;
+      const int rows = S_, cols = ac.width;
+      add_kernel("quantize_time", [=](cudaStream_t s) { return launch_quantize_rows_int8(emb, dst, rs, rows, cols, cols, cols, s); });
+    }
+    PI05_TRY(linear_to_act("time_mlp_in", time_in_act, S_, e_->time_in, kEpiBiasSilu, &time_hidden));
+    PI05_TRY(linear_to_act("time_mlp_out", time_hidden, S_, e_->time_out, kEpiBiasSilu, &cond));
+    for (int idx = 0; idx <= 2 * ac.depth; ++idx) {
+      const Linear& w = idx == 2 * ac.depth ? e_->final_style
+                        : (idx % 2 == 0 ? e_->action[idx / 2].input_style
+                                        : e_->action[idx / 2].post_style);
+      void* dst = static_cast<uint16_t*>(d_styles_) + (size_t)idx * S_ * 3 * ac.width;
+      PI05_TRY(linear("style", cond, S_, w, kEpiStore, dst, 3 * ac.width, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
+    }
+    return kPi05Ok;
+  }
+  auto style_ptr = [&](int idx, int step) -> const void* {
+    return static_cast<const uint16_t*>(d_styles_) + ((size_t)idx * S_ + step) * 3 * ac.width;
+  };
+
+  // ---- stage 0: preprocessing + SigLIP tower ----
+  stage_ = 0;
+  Act patches = make_act(Rv, patch_ld);
+  void* xv = arena_.alloc((size_t)Rv * vw * 2);
+  Act nv = make_act(Rv, vw);
+  void* qkv_v = arena_.alloc((size_t)Rv * 3 * vw * 2);
+  void* logits_v = arena_.alloc((size_t)n_images * heads_v * pp * round_up(pp, 8) * 2);
+  Act attn_v = make_act(Rv, vw);
+  Act act_v = make_act(Rv, c.vision_mlp_dim);
+  void* xp = arena_.alloc((size_t)Rp * lg.width * 2);
+  note("patches", prec == kPrecInt8 ? patches.wide : patches.data, (size_t)Rv * patch_ld * (prec == kPrecFp8 ? 1 : 2));
+  note("vision.hidden", xv, (size_t)Rv * vw * 2);
+  note("prefix", xp, (size_t)Rp * lg.width * 2);
+  {
+    PatchifyArgs pa{};
+    pa.images = d_images_;
+    pa.patches = prec == kPrecInt8 ? patches.wide : patches.data;
+    pa.n_images = n_images;
+    pa.image_size = c.image_size;
+    pa.patch_size = c.patch_size;
+    pa.ld = static_cast<int>(patch_ld);
+    pa.nchw = nchw_;
+    pa.out = prec == kPrecFp8 ? kRowE4m3 : kRowBf16;
+    pa.inv_scale = inv_act;
+    add_kernel("patchify", [pa](cudaStream_t s) { return launch_patchify(pa, s); });
+    if (prec == kPrecInt8) {
+      const void* wide = patches.wide;
+      int8_t* data = static_cast<int8_t*>(patches.data);
+      float* rs = patches.row_scale;
+      const int cols = static_cast<int>(patch_ld);
+      add_kernel("quantize_rows_int8", [=](cudaStream_t s) { return launch_quantize_rows_int8(wide, data, rs, Rv, cols, cols, cols, s); });
+    }
+  }
+  PI05_TRY(linear("vision.patch_embed", patches, Rv, e_->patch, kEpiBiasPos, xv, vw, kOutBf16, nullptr, nullptr, e_->position_embedding, pp, 1.0f));
+  PI05_TRY(norm_to_act("vision.ln1", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv));
+  const float scale_v = static_cast<float>(1.0 / std::sqrt(static_cast<double>(hd_v)));
+  for (int i = 0; i < c.vision_depth; ++i) {
+    const Engine::VisionBlock& w = e_->vision[i];
+    PI05_TRY(linear("vision.qkv", nv, Rv, w.qkv, kEpiStore, qkv_v, 3 * vw, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
+    const uint16_t* base = static_cast<const uint16_t*>(qkv_v);
+    PI05_TRY(attention("vision.attn", base, 3 * vw, hd_v, (long long)pp * 3 * vw, base + vw, 3 * vw, hd_v,
+                       (long long)pp * 3 * vw, base + 2 * vw, 3 * vw, hd_v, (long long)pp * 3 * vw, pp, pp,
+                       hd_v, heads_v, n_images, scale_v, logits_v, &attn_v, vw, hd_v, (long long)pp * vw));
+    PI05_TRY(linear("vision.o", attn_v, Rv, w.o, kEpiBiasResidual, xv, vw, kOutBf16, xv, nullptr, nullptr, 1, 1.0f));
+    PI05_TRY(norm_to_act("vision.ln2", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv));
+    PI05_TRY(linear_to_act("vision.fc1", nv, Rv, w.fc1, kEpiBiasGelu, &act_v));
+    PI05_TRY(linear("vision.fc2", act_v, Rv, w.fc2, kEpiBiasResidual, xv, vw, kOutBf16, xv, nullptr, nullptr, 1, 1.0f));
+    PI05_TRY(norm_to_act(i + 1 < c.vision_depth ? "vision.ln1" : "vision.post_ln", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv));
+  }
+  // projector writes the image tokens straight into rows [0, V) of each sample's prefix
+  PI05_TRY(linear("vision.projector", nv, V_, e_->projector, kEpiStore, xp, lg.width, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f, B_, (long long)V_ * vw, (long long)P_ * lg.width));
+  {
+    const void* table = e_->token_embedding;
+    const uint32_t* ids = d_tokens_;
+    const int batch = B_, tokens = T_, width = lg.width, vocab = c.vocab_size, rows = P_, off = V_;
+    add_kernel("embedding", [=](cudaStream_t s) { return launch_embedding(table, ids, xp, batch, tokens, width, vocab, rows, off, s); });
+  }
+
+  // ---- stage 1: Gemma prefix prefill into the KV cache ----
+  stage_ = 1;
+  Act np_ = make_act(Rp, lg.width);
+  void* qkv_p = arena_.alloc((size_t)Rp * (qw + 2 * hd) * 2);
+  void* qbuf_p = arena_.alloc((size_t)Rp * qw * 2);
+  void* logits_p = arena_.alloc((size_t)B_ * qh * P_ * round_up(cache_rows, 8) * 2);
+  Act attn_p = make_act(Rp, qw);
+  Act act_p = make_act(Rp, lg.mlp_dim);
+  const float scale_g = static_cast<float>(1.0 / std::sqrt(static_cast<double>(hd)));
+  PI05_TRY(norm_to_act("language.norm", xp, Rp, lg.width, kNormRms, nullptr, c.rms_norm_eps, &np_));
+  for (int l = 0; l < lg.depth; ++l) {
+    const Engine::LanguageLayer& w = e_->language[l];
+    PI05_TRY(linear("language.qkv", np_, Rp, w.qkv, kEpiStore, qkv_p, qw + 2 * hd, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
+    RopeArgs ra{};
+    ra.qkv = qkv_p;
+    ra.q_out = qbuf_p;
+    ra.k_cache = k_cache[l];
+    ra.v_cache = v_cache[l];
+    ra.cos_table = e_->rope_cos;
+    ra.sin_table = e_->rope_sin;
+    ra.rows = Rp;
+    ra.tokens = P_;
+    ra.q_heads = qh;
+    ra.head_dim = hd;
+    ra.position_offset = 0;
+    ra.cache_rows = cache_rows;
+    add_kernel("language.rope", [ra](cudaStream_t s) { return launch_rope(ra, s); });
+    if (l + 1 == lg.depth) break;  // the last layer only contributes K/V (bf16_runtime.rs:233)
+    PI05_TRY(attention("language.attn", qbuf_p, hd, (long long)P_ * qw, 0, k_cache[l], hd, (long long)cache_rows * hd, 0,
+                       v_cache[l], hd, (long long)cache_rows * hd, 0, P_ * qh, P_, hd, B_, 1, scale_g,
+                       logits_p, &attn_p, hd, (long long)P_ * qw, 0));
+    PI05_TRY(linear("language.o", attn_p, Rp, w.o, kEpiBiasResidual, xp, lg.width, kOutBf16, xp, nullptr, nullptr, 1, 1.0f));
+    PI05_TRY(norm_to_act("language.norm", xp, Rp, lg.width, kNormRms, nullptr, c.rms_norm_eps, &np_));
+    PI05_TRY(linear_to_act("language.gate_up", np_, Rp, w.gate_up, kEpiGeglu, &act_p));
+    PI05_TRY(linear("language.down", act_p, Rp, w.down, kEpiBiasResidual, xp, lg.width, kOutBf16, xp, nullptr, nullptr, 1, 1.0f));
+    PI05_TRY(norm_to_act("language.norm", xp, Rp, lg.width, kNormRms, nullptr, c.rms_norm_eps, &np_));
+  }
+
+  // ---- stage 2: flow-matching denoise loop of the action expert ----
+  stage_ = 2;
+  Act state_act = make_act(Ra, c.action_dim);
+  void* ha = arena_.alloc((size_t)Ra * ac.width * 2);
+  Act na = make_act(Ra, ac.width);
+  void* qkv_a = arena_.alloc((size_t)Ra * (qw + 2 * hd) * 2);
+  void* qbuf_a = arena_.alloc((size_t)Ra * qw * 2);
+  void* logits_a = arena_.alloc((size_t)B_ * qh * H_ * round_up(cache_rows, 8) * 2);
+  Act attn_a = make_act(Ra, qw);
+  Act act_a = make_act(Ra, ac.mlp_dim);
+  void* velocity = arena_.alloc((size_t)Ra * c.action_dim * 2);
+  note("action.hidden", ha, (size_t)Ra * ac.width * 2);
+  {
+    void* dst = d_state_;
+    const void* src = d_noise_;
+    const size_t bytes = (size_t)Ra * c.action_dim * 2;
+    add_kernel("load_noise", [=](cudaStream_t s) { return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, s); });
+  }
+  const float dt = -1.0f / static_cast<float>(S_);
+  for (int step = 0; step < S_; ++step) {
+    const void* state = d_state_;
+    if (prec == kPrecBf16) {
+      state_act.data = d_state_;
+    } else if (prec == kPrecFp8) {
+      uint8_t* dst = static_cast<uint8_t*>(state_act.data);
+      const long long count = (long long)Ra * c.action_dim;
+      add_kernel("quantize_state", [=](cudaStream_t s) { return launch_quantize_e4m3(state, dst, count, inv_act, s); });
+    } else {
+      int8_t* dst = static_cast<int8_t*>(state_act.data);
+      float* rs = state_act.row_scale;
+      const int cols = c.action_dim;
+      add_kernel("quantize_state", [=](cudaStream_t s) { return launch_quantize_rows_int8(state, dst, rs, Ra, cols, cols, cols, s); });
+    }
+    PI05_TRY(linear("action.in", state_act, Ra, e_->action_in, kEpiStore, ha, ac.width, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
+    PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, style_ptr(0, step), c.rms_norm_eps, &na));
+    for (int l = 0; l < ac.depth; ++l) {
+      const Engine::ActionLayer& w = e_->action[l];
+      const uint16_t* attn_style = static_cast<const uint16_t*>(style_ptr(2 * l, step));
+      const uint16_t* mlp_style = static_cast<const uint16_t*>(style_ptr(2 * l + 1, step));
+      const void* next_style = style_ptr(2 * l + 2, step);  // next layer's input style or the final style
+      PI05_TRY(linear("action.qkv", na, Ra, w.qkv, kEpiStore, qkv_a, qw + 2 * hd, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
+      RopeArgs ra{};
+      ra.qkv = qkv_a;
+      ra.q_out = qbuf_a;
+      ra.k_cache = k_cache[l];
+      ra.v_cache = v_cache[l];
+      ra.cos_table = e_->rope_cos;
+      ra.sin_table = e_->rope_sin;
+      ra.rows = Ra;
+      ra.tokens = H_;
+      ra.q_heads = qh;
+      ra.head_dim = hd;
+      ra.position_offset = P_;
+      ra.cache_rows = cache_rows;
+      add_kernel("action.rope", [ra](cudaStream_t s) { return launch_rope(ra, s); });
+      PI05_TRY(attention("action.attn", qbuf_a, hd, (long long)H_ * qw, 0, k_cache[l], hd, (long long)cache_rows * hd, 0,
+                         v_cache[l], hd, (long long)cache_rows * hd, 0, H_ * qh, cache_rows, hd, B_, 1, scale_g,
+                         logits_a, &attn_a, hd, (long long)H_ * qw, 0));
+      PI05_TRY(linear("action.o", attn_a, Ra, w.o, kEpiGateResidual, ha, ac.width, kOutBf16, ha, attn_style + 2 * ac.width, nullptr, 1, 1.0f));
+      PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, mlp_style, c.rms_norm_eps, &na));
+      PI05_TRY(linear_to_act("action.gate_up", na, Ra, w.gate_up, kEpiGeglu, &act_a));
+      PI05_TRY(linear("action.down", act_a, Ra, w.down, kEpiGateResidual, ha, ac.width, kOutBf16, ha, mlp_style + 2 * ac.width, nullptr, 1, 1.0f));
+      PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, next_style, c.rms_norm_eps, &na));
+    }
+    PI05_TRY(linear("action.out", na, Ra, e_->action_out, kEpiStore, velocity, c.action_dim, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
+    {
+      void* st = d_state_;
+      const long long count = (long long)Ra * c.action_dim;
+      add_kernel("euler", [=](cudaStream_t s) { return launch_euler(st, velocity, count, dt, s); });
+    }
+  }
+  return kPi05Ok;
+}
+
+int PreparedGraph::build_styles() {
+  // Runs the style pre-pass once, eagerly, into d_styles_ (outside the replayed graph, as
+  // the reference does at capture time: crates/apxinf-model/src/pi05/runtime.rs:691-693).
+  const ModelConfig& c = e_->cfg();
+  const int aw = c.action.width, half = aw / 2;
+  std::vector<uint16_t> emb(static_cast<size_t>(S_) * aw);
+  for (int step = 0; step < S_; ++step) {
+    const float time = 1.0f - static_cast<float>(step) / static_cast<float>(S_);
+    for (int i = 0; i < half; ++i) {
+      const double fraction = half == 1 ? 0.0 : static_cast<double>(i) / (half - 1);
+      const double period = static_cast<double>(c.time_min_period) *
+                            std::pow(static_cast<double>(c.time_max_period) /
+                                         static_cast<double>(c.time_min_period),
+                                     fraction);
+      const double phase = static_cast<double>(time) * 6.283185307179586476925286766559 / period;
+      emb[(size_t)step * aw + i] = bf16_bits(static_cast<float>(std::sin(phase)));
+      emb[(size_t)step * aw + half + i] = bf16_bits(static_cast<float>(std::cos(phase)));
+    }
+  }
+  PI05_CUDA(cudaMemcpyAsync(d_time_emb_, emb.data(), emb.size() * 2, cudaMemcpyHostToDevice, e_->stream()));
+  PI05_CUDA(cudaStreamSynchronize(e_->stream()));
+  return kPi05Ok;
+}
+
+int PreparedGraph::prepare() {
+  const ModelConfig& c = e_->cfg();
+  if (T_ <= 0 || T_ > c.max_token_len || B_ <= 0 || P_ + H_ > 1024) return kPi05ErrInvalidValue;
+  PI05_CUDA(cudaSetDevice(e_->device()));
+  // pass 1: measure the arena; pass 2: styles-only launch list; pass 3: the forward.
+  arena_.reset(nullptr, 0);
+  styles_only_ = false;
+  PI05_TRY(build(true));
+  const size_t need = arena_.used() + 4096;
+  PI05_CUDA(cudaMalloc(reinterpret_cast<void**>(&arena_base_), need));
+  PI05_CUDA(cudaMemsetAsync(arena_base_, 0, need, e_->stream()));
+  PI05_CUDA(cudaMallocHost(reinterpret_cast<void**>(&h_out_), (size_t)B_ * H_ * c.action_dim * 2));
+
+  arena_.reset(arena_base_, need);
+  styles_only_ = true;
+  PI05_TRY(build(false));
+  PI05_TRY(build_styles());
+  PI05_TRY(run_eager());
+  PI05_TRY(sync());
+
+  arena_.reset(arena_base_, need);
+  styles_only_ = false;
+  PI05_TRY(build(false));
+  return kPi05Ok;
+}
+
+int PreparedGraph::run_eager() {
+  PI05_CUDA(cudaSetDevice(e_->device()));
+  for (const Op& op : ops_) {
+    if (op.is_gemm) {
+      PI05_CUDA(gemm_plan_launch(op.plan, e_->stream()));
+    } else {
+      PI05_CUDA(op.launch(e_->stream()));
+    }
+  }
+  return kPi05Ok;
+}
+
+int PreparedGraph::capture() {
+  PI05_CUDA(cudaSetDevice(e_->device()));
+  if (exec_ != nullptr) return kPi05Ok;
+  PI05_CUDA(cudaStreamBeginCapture(e_->stream(), cudaStreamCaptureModeThreadLocal));
+  const int rc = run_eager();
+  cudaGraph_t graph = nullptr;
+  const cudaError_t end = cudaStreamEndCapture(e_->stream(), &graph);
+  if (rc != kPi05Ok) {
+    if (graph != nullptr) cudaGraphDestroy(graph);
+    return rc;
+  }
+  PI05_CUDA(end);
+  graph_ = graph;
+  PI05_CUDA(cudaGraphInstantiate(&exec_, graph_, 0));
+  return kPi05Ok;
+}
+
+int PreparedGraph::replay() {
+  if (exec_ == nullptr) return kPi05ErrInvalidValue;
+  PI05_CUDA(cudaGraphLaunch(exec_, e_->stream()));
+  return kPi05Ok;
+}
+
+int PreparedGraph::sync() {
+  PI05_CUDA(cudaStreamSynchronize(e_->stream()));
+  int status = 0;
+  PI05_CUDA(cudaMemcpy(&status, e_->status(), 4, cudaMemcpyDeviceToHost));
+  if (status != 0) {
+    cudaMemset(e_->status(), 0, 4);
+    return kPi05ErrDeviceTimeout;
+  }
+  return kPi05Ok;
+}
+
+int PreparedGraph::update_inputs(const uint8_t* images, const uint32_t* tokens,
+                                 const uint16_t* noise_bf16) {
+  const ModelConfig& c = e_->cfg();
+  if (images == nullptr || tokens == nullptr || noise_bf16 == nullptr) return kPi05ErrInvalidValue;
+  PI05_CUDA(cudaSetDevice(e_->device()));
+  cudaStream_t s = e_->stream();
+  PI05_CUDA(cudaMemcpyAsync(d_images_, images, (size_t)B_ * c.num_views * c.image_size * c.image_size * 3, cudaMemcpyHostToDevice, s));
+  PI05_CUDA(cudaMemcpyAsync(d_tokens_, tokens, (size_t)B_ * T_ * 4, cudaMemcpyHostToDevice, s));
+  PI05_CUDA(cudaMemcpyAsync(d_noise_, noise_bf16, (size_t)B_ * H_ * c.action_dim * 2, cudaMemcpyHostToDevice, s));
+  return kPi05Ok;
+}
+
+int PreparedGraph::output(float* host_f32) {
+  const ModelConfig& c = e_->cfg();
+  if (host_f32 == nullptr) return kPi05ErrInvalidValue;
+  const size_t count = (size_t)B_ * H_ * c.action_dim;
+  PI05_CUDA(cudaMemcpyAsync(h_out_, d_state_, count * 2, cudaMemcpyDeviceToHost, e_->stream()));
+  PI05_TRY(sync());
+  for (size_t i = 0; i < count; ++i) host_f32[i] = bf16_to_float(h_out_[i]);
+  return kPi05Ok;
+}
+
+int PreparedGraph::time_replays(int iterations, float* ms_each) {
+  if (iterations <= 0 || ms_each == nullptr || exec_ == nullptr) return kPi05ErrInvalidValue;
+  cudaEvent_t begin, end;
+  PI05_CUDA(cudaEventCreate(&begin));
+  PI05_CUDA(cudaEventCreate(&end));
+  int rc = kPi05Ok;
+  for (int i = 0; i < iterations && rc == kPi05Ok; ++i) {
+    cudaEventRecord(begin, e_->stream());
+    rc = replay();
+    cudaEventRecord(end, e_->stream());
+    if (rc == kPi05Ok) rc = record_cuda(cudaEventSynchronize(end));
+    if (rc == kPi05Ok) cudaEventElapsedTime(&ms_each[i], begin, end);
+  }
+  cudaEventDestroy(begin);
+  cudaEventDestroy(end);
+  if (rc == kPi05Ok) rc = sync();
+  return rc;
+}
+
+int PreparedGraph::stage_times(float* ms3) {
+  if (ms3 == nullptr) return kPi05ErrInvalidValue;
+  cudaEvent_t ev[4];
+  for (auto& e : ev) PI05_CUDA(cudaEventCreate(&e));
+  int stage = 0;
+  cudaEventRecord(ev[0], e_->stream());
+  int rc = kPi05Ok;
+  for (const Op& op : ops_) {
+    while (op.stage > stage && stage < 2) cudaEventRecord(ev[++stage], e_->stream());
+    const cudaError_t err = op.is_gemm ? gemm_plan_launch(op.plan, e_->stream()) : op.launch(e_->stream());
+    if (err != cudaSuccess) {
+      rc = record_cuda(err);
+      break;
+    }
+  }
+  while (stage < 2) cudaEventRecord(ev[++stage], e_->stream());
+  cudaEventRecord(ev[3], e_->stream());
+  if (rc == kPi05Ok) rc = sync();
+  if (rc == kPi05Ok) {
+    for (int i = 0; i < 3; ++i) cudaEventElapsedTime(&ms3[i], ev[i], ev[i + 1]);
+  }
+  for (auto& e : ev) cudaEventDestroy(e);
+  return rc;
+}
+
+int PreparedGraph::read_tensor(const char* name, void* host, size_t capacity, size_t* actual) {
+  auto it = tensors_.find(name);
+  if (it == tensors_.end()) return kPi05ErrInvalidValue;
+  if (actual != nullptr) *actual = it->second.second;
+  if (host == nullptr) return kPi05Ok;
+  if (capacity < it->second.second) return kPi05ErrInvalidValue;
+  PI05_CUDA(cudaSetDevice(e_->device()));
+  PI05_CUDA(cudaStreamSynchronize(e_->stream()));
+  PI05_CUDA(cudaMemcpy(host, it->second.first, it->second.second, cudaMemcpyDeviceToHost));
+  return kPi05Ok;
+}
+
+}  // namespace pi05

@@ -1,0 +1,210 @@
+// Host side of the PI0.5 policy forward: device weights, the prepared (shape
+// fixed) launch list, CUDA-graph capture and replay. One Engine per (GPU, host
+// thread); engines share nothing.
+//
+// Mirrors, in C++, the reference runtimes
+//   crates/apxinf-model/src/pi05/bf16_runtime.rs:132-575 (Pi05Bf16CudaRuntime),
+//   crates/apxinf-model/src/pi05/runtime.rs:261-818      (Pi05CudaRuntime, FP8),
+//   crates/apxinf-model/src/pi05/int8_runtime.rs         (Pi05Int8CudaRuntime),
+// their captured-graph objects (bf16_runtime.rs:27-123) and the arena of
+//   crates/apxinf-cuda/src/workspace.rs:13-251.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <functional>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "gemm.h"
+
+namespace pi05 {
+
+enum Precision : int { kPrecBf16 = 0, kPrecFp8 = 1, kPrecInt8 = 2 };
+
+struct GemmaDims {
+  int width, depth, mlp_dim, num_heads, num_kv_heads, head_dim;
+};
+
+struct ModelConfig {
+  int action_dim = 32, action_horizon = 10, max_token_len = 200, num_flow_steps = 10;
+  int num_views = 2, image_size = 224, patch_size = 14;
+  int vision_width = 1152, vision_depth = 27, vision_mlp_dim = 4304, vision_heads = 16,
+      vision_head_dim = 72;
+  int vocab_size = 257152;
+  float rms_norm_eps = 1e-6f, layer_norm_eps = 1e-6f, rope_theta = 10000.0f;
+  float time_min_period = 4e-3f, time_max_period = 4.0f;
+  GemmaDims language{2048, 18, 16384, 8, 1, 256};
+  GemmaDims action{1024, 18, 4096, 8, 1, 256};
+
+  int patches_per_view() const { return (image_size / patch_size) * (image_size / patch_size); }
+  int patch_width() const { return 3 * patch_size * patch_size; }
+  int validate() const;
+};
+
+// One (possibly packed) projection in GEMM-operand layout.
+struct Linear {
+  void* w = nullptr;          // [n, ldk] bf16 | e4m3 | int8, K-major
+  float* col_scale = nullptr; // [n] (fp8 / int8)
+  void* bias = nullptr;       // bf16 [n] or null
+  int n = 0, k = 0;
+  long long ldk = 0;
+};
+
+// A GEMM input as the active precision wants it.
+struct Act {
+  void* data = nullptr;       // bf16 | e4m3 | int8 [rows, ld]
+  float* row_scale = nullptr; // int8: per-row dynamic scale
+  void* wide = nullptr;       // int8 only: bf16 staging the quantiser reads
+  long long ld = 0;
+  int rows = 0;
+};
+
+struct Op {
+  std::string name;
+  int stage = 0;
+  bool is_gemm = false;
+  GemmPlan plan;
+  std::function<cudaError_t(cudaStream_t)> launch;
+};
+
+class Arena {
+ public:
+  void reset(uint8_t* base, size_t capacity) { base_ = base; capacity_ = capacity; used_ = 0; }
+  void* alloc(size_t bytes) {
+    const size_t aligned = (bytes + 255) & ~static_cast<size_t>(255);
+    void* p = base_ == nullptr ? reinterpret_cast<void*>(static_cast<uintptr_t>(256 + used_))
+                               : static_cast<void*>(base_ + used_);
+    used_ += aligned;
+    return p;
+  }
+  size_t used() const { return used_; }
+  size_t capacity() const { return capacity_; }
+  bool measuring() const { return base_ == nullptr; }
+
+ private:
+  uint8_t* base_ = nullptr;
+  size_t capacity_ = 0, used_ = 0;
+};
+
+class Engine;
+
+// One prepared inference: fixed token count, image layout and batch.
+class PreparedGraph {
+ public:
+  PreparedGraph(Engine* engine, int token_count, int nchw, int batch);
+  ~PreparedGraph();
+  int prepare();                       // allocate, plan every launch, compute the styles
+  int capture();                       // record the launch list into one CUDA graph
+  int run_eager();                     // same launch list, no graph
+  int replay();                        // cudaGraphLaunch
+  int sync();                          // stream synchronize + device status word
+  int update_inputs(const uint8_t* images, const uint32_t* tokens, const uint16_t* noise_bf16);
+  int output(float* host_f32);         // [batch, horizon, action_dim]
+  int time_replays(int iterations, float* ms_each);
+  int stage_times(float* ms3);
+  int read_tensor(const char* name, void* host, size_t capacity, size_t* actual);
+  size_t workspace_bytes() const { return arena_.capacity(); }
+  size_t workspace_used() const { return arena_.used(); }
+  int num_launches() const { return static_cast<int>(ops_.size()); }
+  int batch() const { return B_; }
+  const std::vector<Op>& ops() const { return ops_; }
+
+ private:
+  friend class Engine;
+  int build(bool measuring);
+  int build_styles();
+  void add_kernel(const char* name, std::function<cudaError_t(cudaStream_t)> fn);
+  int add_gemm(const char* name, const GemmProblem& problem);
+  int linear(const char* name, const Act& in, int rows, const Linear& w, int mode, void* out,
+             long long ldc, int out_type, const void* residual, const void* gate,
+             const void* pos, int pos_rows, float out_inv_scale, int nb0 = 1,
+             long long a_sb0 = 0, long long out_sb0 = 0);
+  int linear_to_act(const char* name, const Act& in, int rows, const Linear& w, int mode,
+                    Act* out);
+  int norm_to_act(const char* name, const void* x, int rows, int cols, int kind,
+                  const void* style, float eps, Act* out);
+  Act make_act(int rows, long long ld);
+  int attention(const char* name, const void* q, long long q_ld, long long q_sb0, long long q_sb1,
+                const void* k, long long k_ld, long long k_sb0, long long k_sb1, const void* v,
+                long long v_ld, long long v_sb0, long long v_sb1, int q_rows, int keys,
+                int head_dim, int nb0, int nb1, float scale, void* logits, Act* out,
+                long long out_ld, long long out_sb0, long long out_sb1);
+  void note(const char* name, void* ptr, size_t bytes) { tensors_[name] = {ptr, bytes}; }
+
+  Engine* e_;
+  int T_, nchw_, B_;
+  int V_, P_, H_, S_;
+  Arena arena_;
+  uint8_t* arena_base_ = nullptr;
+  std::vector<Op> ops_;
+  int stage_ = 0;
+  bool measuring_ = false;
+  bool styles_only_ = false;
+  cudaGraph_t graph_ = nullptr;
+  cudaGraphExec_t exec_ = nullptr;
+  std::unordered_map<std::string, std::pair<void*, size_t>> tensors_;
+  // inputs / outputs
+  uint8_t* d_images_ = nullptr;
+  uint32_t* d_tokens_ = nullptr;
+  void* d_noise_ = nullptr;
+  void* d_state_ = nullptr;
+  void* d_styles_ = nullptr;
+  void* d_time_emb_ = nullptr;
+  uint16_t* h_out_ = nullptr;  // pinned
+};
+
+class Engine {
+ public:
+  Engine(const ModelConfig& cfg, int precision, int device, uint64_t seed, float act_scale);
+  ~Engine();
+  int init();  // stream, status word, rope tables, synthetic weights
+  const ModelConfig& cfg() const { return cfg_; }
+  int precision() const { return prec_; }
+  cudaStream_t stream() const { return stream_; }
+  int* status() const { return status_; }
+  int device() const { return device_; }
+  float act_scale() const { return act_scale_; }
+  size_t weight_bytes() const { return weight_bytes_; }
+  int read_weight(const char* name, void* host, size_t capacity, size_t* actual);
+
+  struct VisionBlock { Linear qkv, o, fc1, fc2; };
+  struct LanguageLayer { Linear qkv, o, gate_up, down; };
+  struct ActionLayer { Linear input_style, qkv, o, post_style, gate_up, down; };
+  std::vector<VisionBlock> vision;
+  Linear patch, projector;
+  void* position_embedding = nullptr;
+  void* token_embedding = nullptr;
+  std::vector<LanguageLayer> language;
+  std::vector<ActionLayer> action;
+  Linear final_style, action_in, action_out, time_in, time_out;
+  float* rope_cos = nullptr;
+  float* rope_sin = nullptr;
+  int rope_positions = 0;
+
+ private:
+  struct Part { const char* suffix; int k, n; bool bias; };
+  int make_linear(const std::string& prefix, const std::vector<std::string>& parts, int k,
+                  const std::vector<int>& ns, bool bias, bool interleave, Linear* out);
+  void* dmalloc(size_t bytes);
+  ModelConfig cfg_;
+  int prec_, device_;
+  uint64_t seed_;
+  float act_scale_;
+  cudaStream_t stream_ = nullptr;
+  int* status_ = nullptr;
+  uint64_t cursor_ = 0;  // element offset in the synthetic stream
+  void* tmp_src_ = nullptr;
+  void* tmp_stage_ = nullptr;
+  size_t tmp_src_bytes_ = 0, tmp_stage_bytes_ = 0;
+  size_t weight_bytes_ = 0;
+  std::vector<void*> allocations_;
+  std::unordered_map<std::string, std::pair<void*, size_t>> named_;
+};
+
+int record_cuda(cudaError_t error);
+
+}  // namespace pi05

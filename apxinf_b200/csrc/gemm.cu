@@ -174,6 +174,7 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   p.bias = reinterpret_cast<const __nv_bfloat16*>(q.bias);
   p.col_scale = q.col_scale;
   p.row_scale = q.row_scale;
+  p.row_scale_sb0 = q.row_scale_sb0;
   p.pos = reinterpret_cast<const __nv_bfloat16*>(q.pos);
   p.gate = reinterpret_cast<const __nv_bfloat16*>(q.gate);
   p.alpha = q.alpha;

@@ -37,6 +37,7 @@ struct GemmProblem {
   const void* bias = nullptr;
   const float* col_scale = nullptr;
   const float* row_scale = nullptr;
+  long long row_scale_sb0 = 0;
   const void* pos = nullptr;
   int pos_rows = 1;
   long long pos_ld = 0;

@@ -69,6 +69,7 @@ struct GemmParams {
   const __nv_bfloat16* bias;      // [N]
   const float* col_scale;         // [N] or null (per-output-channel weight scale)
   const float* row_scale;         // [M] or null (per-row activation scale)
+  long long row_scale_sb0;        // batch-0 stride of row_scale
   const __nv_bfloat16* pos;       // [pos_rows, N]
   const __nv_bfloat16* gate;      // [N]
   float alpha;                    // scalar scale applied with row_scale
@@ -341,6 +342,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (!ok && lane == 0) atomicCAS(p.status, 0, kGemmTimeoutEpilogue);
     ptx::tc_fence_after();
     const long long out_base = (long long)b0 * p.out_sb0 + (long long)b1 * p.out_sb1;
+    const float* row_scale = p.row_scale != nullptr ? p.row_scale + (long long)b0 * p.row_scale_sb0 : nullptr;
     const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
 
     auto to_float = [](uint32_t raw) -> float {
@@ -351,7 +353,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (p.mode == kEpiGeglu) {
       if constexpr (!SWAP) {
         // columns [128t, 128t+64) gate, [128t+64, 128t+128) up; thread-local.
-        const float sr = p.alpha * (p.row_scale != nullptr && gi < p.rows_a ? p.row_scale[gi] : 1.0f);
+        const float sr = p.alpha * (row_scale != nullptr && gi < p.rows_a ? row_scale[gi] : 1.0f);
 #pragma unroll 1
         for (int pair = 0; pair < BLOCK_N / 128; ++pair) {
 #pragma unroll 1
@@ -393,7 +395,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int t = 0; t < 16; ++t) {
             const int r = tile_b * BLOCK_N + cc * 16 + t;
             const float sr =
-                p.alpha * (p.row_scale != nullptr && r < p.rows_b ? p.row_scale[r] : 1.0f);
+                p.alpha * (row_scale != nullptr && r < p.rows_b ? row_scale[r] : 1.0f);
             vals[cc * 16 + t] = round_bf16(to_float(raw[t]) * sr * sc);
           }
         }
@@ -418,7 +420,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     } else if constexpr (!SWAP) {
       const int r = gi;
-      const float sr = p.alpha * (p.row_scale != nullptr && r < p.rows_a ? p.row_scale[r] : 1.0f);
+      const float sr = p.alpha * (row_scale != nullptr && r < p.rows_a ? row_scale[r] : 1.0f);
 #pragma unroll 1
       for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
         uint32_t raw[16];
@@ -461,7 +463,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
             reinterpret_cast<int*>(p.out)[index] = static_cast<int>(raw[t]);
             continue;
           }
-          const float sr = p.alpha * (p.row_scale != nullptr ? p.row_scale[r] : 1.0f);
+          const float sr = p.alpha * (row_scale != nullptr ? row_scale[r] : 1.0f);
           const float v = to_float(raw[t]) * sr * sc;
           const float o = p.out_type == kOutF32 ? v : epilogue_value(p, out_base, r, c, v);
           store_one(p, index, o);

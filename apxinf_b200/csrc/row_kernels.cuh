@@ -1,0 +1,86 @@
+// Row-wise and elementwise kernels of the PI0.5 forward (everything that is not
+// a contraction): LayerNorm / RMSNorm / adaptive RMSNorm with fused output
+// quantisation, RoPE + KV-cache write, row softmax, uint8 NHWC image -> patch
+// rows, token embedding, per-row INT8 / static E4M3 quantisation, Euler update.
+//
+// All of them are HBM-bound: one global read and one global write per element,
+// 16-byte vector accesses, reductions by warp shuffles.
+//
+// They restate, for sm_100a, the reference kernels in
+// crates/apxinf-cuda/kernels/custom/{normalization,fused,attention,preprocess,
+// embedding,quantization,elementwise}.cuh; the rounding points are the same.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pi05 {
+
+enum NormKind : int { kNormLayer = 0, kNormRms = 1, kNormAda = 2 };
+enum RowOut : int { kRowBf16 = 0, kRowE4m3 = 1, kRowInt8 = 2 };
+
+struct NormArgs {
+  const void* input;    // bf16 [rows, cols]
+  void* output;         // bf16 | e4m3 | int8 [rows, cols]
+  float* row_scale;     // f32 [rows], written when out == kRowInt8
+  const void* weight;   // bf16 [cols] (LayerNorm gamma / RMSNorm scale); may be null (= 1)
+  const void* bias;     // bf16 [cols] (LayerNorm beta); may be null (= 0)
+  const void* style;    // bf16 [>= 2*cols]: scale | shift (adaptive RMSNorm)
+  int rows, cols;
+  float eps;
+  float inv_scale;      // 1 / activation scale for kRowE4m3
+  int kind, out;
+};
+cudaError_t launch_norm(const NormArgs& args, cudaStream_t stream);
+
+struct RopeArgs {
+  const void* qkv;      // bf16 [rows, (q_heads + 2*kv) * head_dim], packed q | k | v
+  void* q_out;          // bf16 [rows, q_heads, head_dim]
+  void* k_cache;        // bf16 [batch, cache_rows, head_dim]
+  void* v_cache;        // bf16 [batch, cache_rows, head_dim]
+  const float* cos_table;  // f32 [positions, head_dim/2]
+  const float* sin_table;
+  int rows;             // batch * tokens
+  int tokens;           // tokens per sample
+  int q_heads, head_dim;
+  int position_offset;  // position of token 0; also its row in the cache
+  int cache_rows;       // rows per sample in the caches
+};
+cudaError_t launch_rope(const RopeArgs& args, cudaStream_t stream);
+
+// In-place softmax over `cols` <= 1024 bf16 scores per row; batch stride and
+// leading dimension in elements. Result rounded to bf16.
+cudaError_t launch_softmax(void* scores, int rows_per_batch, int batches, long long batch_stride,
+                           int cols, long long ld, cudaStream_t stream);
+
+struct PatchifyArgs {
+  const uint8_t* images;  // [n_images, size, size, 3] (NHWC) or [n_images, 3, size, size]
+  void* patches;          // [n_images * pps * pps, ld] bf16 or e4m3, columns c*ps*ps + dy*ps + dx
+  int n_images, image_size, patch_size;
+  int ld;                 // >= 3*ps*ps, multiple of 16; pad columns are written as zero
+  int nchw;
+  int out;                // kRowBf16 | kRowE4m3
+  float inv_scale;
+};
+cudaError_t launch_patchify(const PatchifyArgs& args, cudaStream_t stream);
+
+// out[b, row_offset + t, :] = table[ids[b, t], :] * sqrt(width); ids >= vocab give zeros.
+cudaError_t launch_embedding(const void* table, const uint32_t* ids, void* out, int batch,
+                             int tokens, int width, int vocab, int out_rows_per_batch,
+                             int row_offset, cudaStream_t stream);
+
+// Dynamic per-row symmetric INT8: scale = max(absmax/127, 1e-12), round half away.
+cudaError_t launch_quantize_rows_int8(const void* input, int8_t* output, float* row_scale, int rows,
+                                      int cols, long long ld_in, long long ld_out,
+                                      cudaStream_t stream);
+
+// Static per-tensor E4M3: e4m3(clamp(x * inv_scale)).
+cudaError_t launch_quantize_e4m3(const void* input, uint8_t* output, long long count,
+                                 float inv_scale, cudaStream_t stream);
+
+// state <- bf16(state + dt * velocity)
+cudaError_t launch_euler(void* state, const void* velocity, long long count, float dt,
+                         cudaStream_t stream);
+
+}  // namespace pi05

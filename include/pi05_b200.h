@@ -85,6 +85,84 @@ typedef struct Pi05GemmArgs {
 
 int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream);
 
+
+/* ------------------------------------------------------------------------- */
+/* Engine level                                                              */
+/* ------------------------------------------------------------------------- */
+
+enum { PI05_DTYPE_BF16 = 0, PI05_DTYPE_FP8 = 1, PI05_DTYPE_INT8 = 2 };
+enum { PI05_IMAGE_NHWC = 0, PI05_IMAGE_NCHW = 1 };
+
+/* Architecture constants; field meaning and defaults follow Pi05Config /
+ * GemmaVariantConfig (crates/apxinf-model/src/pi05/config.rs:5-109).
+ * pi05_default_config() fills the two-view, horizon-10 bench profile. */
+typedef struct Pi05Gemma {
+  int32_t width, depth, mlp_dim, num_heads, num_kv_heads, head_dim;
+} Pi05Gemma;
+
+typedef struct Pi05ModelConfig {
+  int32_t action_dim, action_horizon, max_token_len, num_flow_steps;
+  int32_t num_views, image_size, patch_size;
+  int32_t vision_width, vision_depth, vision_mlp_dim, vision_heads, vision_head_dim;
+  int32_t vocab_size;
+  float rms_norm_eps, layer_norm_eps, rope_theta, time_min_period, time_max_period;
+  Pi05Gemma language, action_expert;
+} Pi05ModelConfig;
+
+typedef struct Pi05Engine Pi05Engine; /* weights + stream of one GPU; one host thread at a time */
+typedef struct Pi05Graph Pi05Graph;   /* one prepared (token_count, layout, batch) inference */
+
+void pi05_default_config(Pi05ModelConfig* config);
+
+/* Creates the runtime on `device` with Pi05Weights::synthetic(config, seed) weights
+ * (crates/apxinf-model/src/pi05/weights.rs:255-330) generated on the GPU and
+ * packed/quantised for `dtype` — the `pi05_bench random --dtype ...` path
+ * (crates/apxinf-model/examples/pi05_bench.rs:901-990). `fp8_act_scale` is the
+ * uniform static activation scale of Pi05ActivationScales::uniform
+ * (crates/apxinf-model/src/pi05/runtime.rs:86-113); ignored unless dtype is FP8.
+ * Allocates device memory. Replaces Pi05{Bf16,,Int8}CudaRuntime::new. */
+int pi05_engine_create(const Pi05ModelConfig* config, int32_t dtype, int32_t device, uint64_t seed,
+                       float fp8_act_scale, Pi05Engine** out);
+void pi05_engine_destroy(Pi05Engine* engine);
+size_t pi05_engine_weight_bytes(const Pi05Engine* engine);
+/* Copies a device weight tensor ("language.3.qkv.weight", ".scale", ".bias", ...) to the host;
+ * with host == NULL only reports its size. For parity tests. */
+int pi05_engine_read_weight(Pi05Engine* engine, const char* name, void* host, size_t capacity,
+                            size_t* actual);
+
+/* capture_infer_rgb_u8 (crates/apxinf-model/src/pi05/bf16_runtime.rs:457-575): sizes and
+ * allocates the workspace, precomputes the per-step adaRMSNorm styles outside the graph,
+ * plans every launch and records them into one CUDA graph. `batch` independent observations
+ * share the weights (batch 1 = the reference's only mode). Allocates device memory; no later
+ * call on the graph does. */
+int pi05_engine_capture(Pi05Engine* engine, int32_t token_count, int32_t image_layout,
+                        int32_t batch, Pi05Graph** out);
+void pi05_graph_destroy(Pi05Graph* graph);
+
+/* update_raw_image_inputs (bf16_runtime.rs:88-123): queues the host->device copies of
+ * images u8 [batch, views, size, size, 3] (or NCHW), token ids u32 [batch, token_count] and
+ * noise bf16 bits [batch, horizon, action_dim] on the engine stream. The host buffers must
+ * stay valid until the next pi05_graph_sync / pi05_graph_output. */
+int pi05_graph_update_raw_image_inputs(Pi05Graph* graph, const uint8_t* images,
+                                       const uint32_t* token_ids, const uint16_t* noise_bf16);
+int pi05_graph_replay(Pi05Graph* graph);     /* cudaGraphLaunch, asynchronous */
+int pi05_graph_run_eager(Pi05Graph* graph);  /* the same launch list without the graph */
+int pi05_graph_sync(Pi05Graph* graph);       /* waits; PI05_ERR_DEVICE_TIMEOUT if a device wait ran out */
+/* Waits, then writes the action chunk [batch, horizon, action_dim] as float32. */
+int pi05_graph_output(Pi05Graph* graph, float* host_out);
+/* `iterations` replays, each timed with CUDA events on the engine stream (milliseconds). */
+int pi05_graph_time_replays(Pi05Graph* graph, int32_t iterations, float* ms_each);
+/* One eager pass timed per stage: {vision tower, prefix prefill, denoise loop} in ms. */
+int pi05_graph_stage_times(Pi05Graph* graph, float* ms3);
+size_t pi05_graph_workspace_bytes(const Pi05Graph* graph);
+size_t pi05_graph_workspace_used_bytes(const Pi05Graph* graph);
+int32_t pi05_graph_num_launches(const Pi05Graph* graph);
+/* Name of launch `index` (for launch-list summaries); NULL when out of range. */
+const char* pi05_graph_launch_name(const Pi05Graph* graph, int32_t index);
+/* Copies a named intermediate ("prefix", "kv.3.k", "state", "vision.hidden", ...) to the host. */
+int pi05_graph_read_tensor(Pi05Graph* graph, const char* name, void* host, size_t capacity,
+                           size_t* actual);
+
 /* Last CUDA runtime error string seen by this library on the calling thread. */
 const char* pi05_last_cuda_error(void);
 
