@@ -38,6 +38,7 @@ PROTOTYPES = [
     ("pi05_graph_output", C.c_int, [_P, _P]),
     ("pi05_graph_time_replays", C.c_int, [_P, C.c_int32, _P]),
     ("pi05_graph_stage_times", C.c_int, [_P, _P]),
+    ("pi05_graph_time_launches", C.c_int, [_P, C.c_char_p, _P, _P]),
     ("pi05_graph_workspace_bytes", _SZ, [_P]),
     ("pi05_graph_workspace_used_bytes", _SZ, [_P]),
     ("pi05_graph_num_launches", C.c_int32, [_P]),

@@ -153,6 +153,11 @@ extern "C" int pi05_graph_time_replays(Pi05Graph* graph, int32_t iterations, flo
 extern "C" int pi05_graph_stage_times(Pi05Graph* graph, float* ms3) {
   return PI05_GRAPH_CALL(stage_times(ms3));
 }
+extern "C" int pi05_graph_time_launches(Pi05Graph* graph, const char* name, float* mean_ms,
+                                        int32_t* count) {
+  if (name == nullptr) return pi05::kPi05ErrInvalidValue;
+  return PI05_GRAPH_CALL(time_launches(name, mean_ms, count));
+}
 extern "C" size_t pi05_graph_workspace_bytes(const Pi05Graph* graph) {
   return graph == nullptr ? 0 : graph->impl->workspace_bytes();
 }

@@ -859,6 +859,46 @@ int PreparedGraph::stage_times(float* ms3) {
   return rc;
 }
 
+int PreparedGraph::time_launches(const char* name, float* mean_ms, int* count) {
+  if (name == nullptr || mean_ms == nullptr || count == nullptr) return kPi05ErrInvalidValue;
+  PI05_CUDA(cudaSetDevice(e_->device()));
+  std::vector<cudaEvent_t> events;
+  int rc = kPi05Ok;
+  for (const Op& op : ops_) {
+    const bool timed = op.name == name;
+    if (timed) {
+      cudaEvent_t a, b;
+      if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) {
+        rc = kPi05ErrCuda;
+        break;
+      }
+      events.push_back(a);
+      events.push_back(b);
+      cudaEventRecord(a, e_->stream());
+    }
+    const cudaError_t err =
+        op.is_gemm ? gemm_plan_launch(op.plan, e_->stream()) : op.launch(e_->stream());
+    if (timed) cudaEventRecord(events.back(), e_->stream());
+    if (err != cudaSuccess) {
+      rc = record_cuda(err);
+      break;
+    }
+  }
+  if (rc == kPi05Ok) rc = sync();
+  double total = 0.0;
+  if (rc == kPi05Ok) {
+    for (size_t i = 0; i + 1 < events.size(); i += 2) {
+      float ms = 0.0f;
+      cudaEventElapsedTime(&ms, events[i], events[i + 1]);
+      total += ms;
+    }
+  }
+  for (cudaEvent_t e : events) cudaEventDestroy(e);
+  *count = static_cast<int>(events.size() / 2);
+  *mean_ms = *count > 0 ? static_cast<float>(total / *count) : 0.0f;
+  return rc;
+}
+
 int PreparedGraph::read_tensor(const char* name, void* host, size_t capacity, size_t* actual) {
   auto it = tensors_.find(name);
   if (it == tensors_.end()) return kPi05ErrInvalidValue;

@@ -106,6 +106,7 @@ class PreparedGraph {
   int output(float* host_f32);         // [batch, horizon, action_dim]
   int time_replays(int iterations, float* ms_each);
   int stage_times(float* ms3);
+  int time_launches(const char* name, float* mean_ms, int* count);
   int read_tensor(const char* name, void* host, size_t capacity, size_t* actual);
   size_t workspace_bytes() const { return arena_.capacity(); }
   size_t workspace_used() const { return arena_.used(); }

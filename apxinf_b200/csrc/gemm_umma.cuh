@@ -127,53 +127,43 @@ constexpr int kStageABytes = kTileRowsA * 128;
 
 __host__ __device__ constexpr int gemm_stage_bytes(int block_n) { return kStageABytes + block_n * 128; }
 __host__ __device__ constexpr int gemm_smem_bytes(int block_n, int stages) {
-  return stages * gemm_stage_bytes(block_n) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  return stages * gemm_stage_bytes(block_n) + 1024 /*alignment slack*/ + 512 /*barriers*/ +
+         3 * 256 * 4 /*epilogue vectors*/;
 }
 __host__ __device__ constexpr uint32_t tmem_cols_for(int block_n) {
   return block_n <= 32 ? 32u : block_n <= 64 ? 64u : block_n <= 128 ? 128u : 256u;
 }
 
-// One output element through the fused epilogue. `v` is the scaled
-// accumulator; (r, c) are logical output coordinates.
-struct EpilogueCtx {
-  const GemmParams& p;
-  long long out_base;  // batch offset in elements
-};
+// ---------------------------------------------------------------------------
+// Epilogue building blocks
+// ---------------------------------------------------------------------------
 
-__device__ __forceinline__ float epilogue_value(const GemmParams& p, long long out_base, int r,
-                                                int c, float v) {
-  switch (p.mode) {
-    case kEpiStore: {
-      float o = round_bf16(v);
-      if (p.bias != nullptr) o = round_bf16(o + __bfloat162float(p.bias[c]));
-      return o;
-    }
-    case kEpiBiasGelu: {
-      float x = round_bf16(v);
-      if (p.bias != nullptr) x += __bfloat162float(p.bias[c]);
-      return gelu_tanh_f(x);
-    }
-    case kEpiBiasSilu: {
-      float x = round_bf16(v);
-      if (p.bias != nullptr) x += __bfloat162float(p.bias[c]);
-      return silu_f(x);
-    }
-    case kEpiBiasResidual: {
-      float o = round_bf16(v) + __bfloat162float(p.residual[out_base + (long long)r * p.ldc + c]);
-      if (p.bias != nullptr) o += __bfloat162float(p.bias[c]);
-      return o;
-    }
-    case kEpiBiasPos: {
-      float o = round_bf16(v) + __bfloat162float(p.pos[(long long)(r % p.pos_rows) * p.pos_ld + c]);
-      if (p.bias != nullptr) o += __bfloat162float(p.bias[c]);
-      return o;
-    }
-    case kEpiGateResidual: {
-      return __bfloat162float(p.residual[out_base + (long long)r * p.ldc + c]) +
-             round_bf16(v) * __bfloat162float(p.gate[c]);
-    }
-    default:
-      return v;
+template <int OP>
+__device__ __forceinline__ float acc_to_float(uint32_t raw) {
+  if constexpr (OP == kOpS8) {
+    return static_cast<float>(static_cast<int>(raw));
+  } else {
+    return __uint_as_float(raw);
+  }
+}
+
+// One output element. `v` = scaled accumulator, `bias` / `gate` = per-column
+// values (0 when absent: adding 0 changes nothing), `extra` = residual or
+// position-embedding element.
+template <int MODE>
+__device__ __forceinline__ float epi_apply(float v, float bias, float extra, float gate) {
+  if constexpr (MODE == kEpiStore) {
+    return round_bf16(round_bf16(v) + bias);
+  } else if constexpr (MODE == kEpiBiasGelu) {
+    return gelu_tanh_f(round_bf16(v) + bias);
+  } else if constexpr (MODE == kEpiBiasSilu) {
+    return silu_f(round_bf16(v) + bias);
+  } else if constexpr (MODE == kEpiBiasResidual || MODE == kEpiBiasPos) {
+    return (round_bf16(v) + extra) + bias;
+  } else if constexpr (MODE == kEpiGateResidual) {
+    return extra + round_bf16(v) * gate;
+  } else {
+    return v;
   }
 }
 
@@ -203,7 +193,10 @@ __device__ __forceinline__ void store_chunk16(const GemmParams& p, long long ind
       reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
       reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
     } else {
-      for (int t = 0; t < valid; ++t) dst[t] = __float2bfloat16(o[t]);
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        if (t < valid) dst[t] = __float2bfloat16(o[t]);
+      }
     }
   } else if (p.out_type == kOutE4m3) {
     uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + index;
@@ -218,11 +211,134 @@ __device__ __forceinline__ void store_chunk16(const GemmParams& p, long long ind
       }
       *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
     } else {
-      for (int t = 0; t < valid; ++t) dst[t] = to_e4m3(o[t] * p.out_inv_scale);
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        if (t < valid) dst[t] = to_e4m3(o[t] * p.out_inv_scale);
+      }
     }
   } else {
     float* dst = reinterpret_cast<float*>(p.out) + index;
-    for (int t = 0; t < valid; ++t) dst[t] = o[t];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      if (t < valid) dst[t] = o[t];
+    }
+  }
+}
+
+// 16 consecutive bf16 of one row as floats (vector loads when aligned).
+__device__ __forceinline__ void load_row16(const __nv_bfloat16* src, int valid, float (&x)[16]) {
+  if (valid == 16 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+    const uint4 lo = reinterpret_cast<const uint4*>(src)[0];
+    const uint4 hi = reinterpret_cast<const uint4*>(src)[1];
+    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&lo);
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&hi);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 fa = __bfloat1622float2(a[t]);
+      const float2 fb = __bfloat1622float2(b[t]);
+      x[2 * t] = fa.x;
+      x[2 * t + 1] = fa.y;
+      x[8 + 2 * t] = fb.x;
+      x[8 + 2 * t + 1] = fb.y;
+    }
+  } else {
+#pragma unroll
+    for (int t = 0; t < 16; ++t) x[t] = t < valid ? __bfloat162float(src[t]) : 0.0f;
+  }
+}
+
+// Thread = one output row, TMEM columns = output columns.
+template <int OP, int BLOCK_N, int MODE>
+__device__ __forceinline__ void epilogue_normal(const GemmParams& p, uint32_t taddr_row, int r,
+                                                int tile_b, long long out_base, float sr,
+                                                const float* s_scale, const float* s_bias,
+                                                const float* s_gate) {
+  constexpr bool kExtra =
+      MODE == kEpiBiasResidual || MODE == kEpiBiasPos || MODE == kEpiGateResidual;
+  const bool row_ok = r < p.rows_a;
+  const __nv_bfloat16* extra_row = nullptr;
+  if (kExtra && row_ok) {
+    extra_row = MODE == kEpiBiasPos ? p.pos + (long long)(r % p.pos_rows) * p.pos_ld
+                                    : p.residual + out_base + (long long)r * p.ldc;
+  }
+#pragma unroll 2
+  for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
+    uint32_t raw[16];
+    ptx::tmem_ld_16(taddr_row + cc * 16, raw);
+    const int c0 = tile_b * BLOCK_N + cc * 16;
+    const int valid = row_ok ? min(16, p.rows_b - c0) : 0;
+    float extra[16];
+    if (kExtra && valid > 0) {
+      load_row16(extra_row + c0, valid, extra);
+    } else {
+#pragma unroll
+      for (int t = 0; t < 16; ++t) extra[t] = 0.0f;
+    }
+    ptx::tmem_ld_wait();
+    if (valid <= 0) continue;
+    const long long index = out_base + (long long)r * p.ldc + c0;
+    if (p.out_type == kOutS32) {
+      int* dst = reinterpret_cast<int*>(p.out) + index;
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        if (t < valid) dst[t] = static_cast<int>(raw[t]);
+      }
+      continue;
+    }
+    float o[16];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const int j = cc * 16 + t;
+      const float v = acc_to_float<OP>(raw[t]) * sr * s_scale[j];
+      o[t] = p.out_type == kOutF32 ? v : epi_apply<MODE>(v, s_bias[j], extra[t], s_gate[j]);
+    }
+    store_chunk16(p, index, valid, o);
+  }
+}
+
+// Thread = one output column (weight row), TMEM columns = output rows.
+template <int OP, int BLOCK_N, int MODE>
+__device__ __forceinline__ void epilogue_swapped(const GemmParams& p, uint32_t taddr_row, int c,
+                                                 int tile_b, long long out_base,
+                                                 const float* s_rowscale) {
+  constexpr bool kExtra =
+      MODE == kEpiBiasResidual || MODE == kEpiBiasPos || MODE == kEpiGateResidual;
+  const bool col_ok = c < p.rows_a;
+  const float sc = p.col_scale != nullptr && col_ok ? p.col_scale[c] : 1.0f;
+  const float bias = p.bias != nullptr && col_ok ? __bfloat162float(p.bias[c]) : 0.0f;
+  const float gate = p.gate != nullptr && col_ok ? __bfloat162float(p.gate[c]) : 0.0f;
+#pragma unroll
+  for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
+    uint32_t raw[16];
+    ptx::tmem_ld_16(taddr_row + cc * 16, raw);
+    const int r0 = tile_b * BLOCK_N + cc * 16;
+    const int valid = col_ok ? min(16, p.rows_b - r0) : 0;
+    float extra[16];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      extra[t] = 0.0f;
+      if (kExtra && t < valid) {
+        const int r = r0 + t;
+        extra[t] = MODE == kEpiBiasPos
+                       ? __bfloat162float(p.pos[(long long)(r % p.pos_rows) * p.pos_ld + c])
+                       : __bfloat162float(p.residual[out_base + (long long)r * p.ldc + c]);
+      }
+    }
+    ptx::tmem_ld_wait();
+    if (valid <= 0) continue;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      if (t < valid) {
+        const long long index = out_base + (long long)(r0 + t) * p.ldc + c;
+        if (p.out_type == kOutS32) {
+          reinterpret_cast<int*>(p.out)[index] = static_cast<int>(raw[t]);
+        } else {
+          const float v = acc_to_float<OP>(raw[t]) * s_rowscale[cc * 16 + t] * sc;
+          const float o = p.out_type == kOutF32 ? v : epi_apply<MODE>(v, bias, extra[t], gate);
+          store_one(p, index, o);
+        }
+      }
+    }
   }
 }
 
@@ -247,6 +363,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* accum_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  float* s_scale = reinterpret_cast<float*>(smem + STAGES * kStageBytes + 512);
+  float* s_bias = s_scale + 256;
+  float* s_gate = s_bias + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -337,41 +456,55 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ---------------- epilogue (warps 2..5) ----------------
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     const int row_in_tile = quarter * 32 + lane;
+    const int ep_tid = threadIdx.x - 64;
     const int gi = tile_a * kTileRowsA + row_in_tile;  // index on the 128-row side
+    const long long out_base = (long long)b0 * p.out_sb0 + (long long)b1 * p.out_sb1;
+    const float* row_scale =
+        p.row_scale != nullptr ? p.row_scale + (long long)b0 * p.row_scale_sb0 : nullptr;
+
+    // Stage the per-column (normal) or per-row (swapped) vectors of this tile
+    // in shared memory while the main loop runs.
+    for (int j = ep_tid; j < BLOCK_N; j += 128) {
+      const int idx = tile_b * BLOCK_N + j;
+      const bool in = idx < p.rows_b;
+      if constexpr (!SWAP) {
+        s_scale[j] = p.col_scale != nullptr && in ? p.col_scale[idx] : 1.0f;
+        s_bias[j] = p.bias != nullptr && in ? __bfloat162float(p.bias[idx]) : 0.0f;
+        s_gate[j] = p.gate != nullptr && in ? __bfloat162float(p.gate[idx]) : 0.0f;
+      } else {
+        s_scale[j] = p.alpha * (row_scale != nullptr && in ? row_scale[idx] : 1.0f);
+      }
+    }
+    float sr = p.alpha;
+    if constexpr (!SWAP) {
+      if (row_scale != nullptr && gi < p.rows_a) sr = p.alpha * row_scale[gi];
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+
     const bool ok = ptx::mbar_wait(accum_bar, 0);
     if (!ok && lane == 0) atomicCAS(p.status, 0, kGemmTimeoutEpilogue);
     ptx::tc_fence_after();
-    const long long out_base = (long long)b0 * p.out_sb0 + (long long)b1 * p.out_sb1;
-    const float* row_scale = p.row_scale != nullptr ? p.row_scale + (long long)b0 * p.row_scale_sb0 : nullptr;
     const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-
-    auto to_float = [](uint32_t raw) -> float {
-      if constexpr (OP == kOpS8) return static_cast<float>(static_cast<int>(raw));
-      return __uint_as_float(raw);
-    };
 
     if (p.mode == kEpiGeglu) {
       if constexpr (!SWAP) {
         // columns [128t, 128t+64) gate, [128t+64, 128t+128) up; thread-local.
-        const float sr = p.alpha * (row_scale != nullptr && gi < p.rows_a ? row_scale[gi] : 1.0f);
 #pragma unroll 1
         for (int pair = 0; pair < BLOCK_N / 128; ++pair) {
-#pragma unroll 1
+#pragma unroll 2
           for (int sub = 0; sub < 4; ++sub) {
             uint32_t rg[16], ru[16];
             ptx::tmem_ld_16(taddr_row + pair * 128 + sub * 16, rg);
             ptx::tmem_ld_16(taddr_row + pair * 128 + 64 + sub * 16, ru);
             ptx::tmem_ld_wait();
-            const int cg = tile_b * BLOCK_N + pair * 128 + sub * 16;  // packed gate column
-            const int oc = (cg / 128) * 64 + (cg % 128);              // output column
+            const int jg = pair * 128 + sub * 16;
+            const int cg = tile_b * BLOCK_N + jg;         // packed gate column
+            const int oc = (cg / 128) * 64 + (cg % 128);  // output column
             float o[16];
 #pragma unroll
             for (int t = 0; t < 16; ++t) {
-              const float sg = p.col_scale != nullptr ? p.col_scale[min(cg + t, p.rows_b - 1)] : 1.0f;
-              const float su =
-                  p.col_scale != nullptr ? p.col_scale[min(cg + 64 + t, p.rows_b - 1)] : 1.0f;
-              const float g = round_bf16(to_float(rg[t]) * sr * sg);
-              const float u = round_bf16(to_float(ru[t]) * sr * su);
+              const float g = round_bf16(acc_to_float<OP>(rg[t]) * sr * s_scale[jg + t]);
+              const float u = round_bf16(acc_to_float<OP>(ru[t]) * sr * s_scale[jg + 64 + t]);
               o[t] = gelu_tanh_f(g) * u;
             }
             if (gi < p.rows_a && cg < p.rows_b) {
@@ -383,7 +516,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // lanes [0,64) hold gate features, lanes [64,128) the matching up
         // features; the up half goes through shared memory (stage 0 is idle
         // once the accumulator barrier has fired).
-        float* xchg = reinterpret_cast<float*>(smem);  // [64][BLOCK_N]
+        float* xchg = reinterpret_cast<float*>(smem);  // [BLOCK_N][64]
         const float sc = p.col_scale != nullptr && gi < p.rows_a ? p.col_scale[gi] : 1.0f;
         float vals[BLOCK_N];
 #pragma unroll
@@ -393,10 +526,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ptx::tmem_ld_wait();
 #pragma unroll
           for (int t = 0; t < 16; ++t) {
-            const int r = tile_b * BLOCK_N + cc * 16 + t;
-            const float sr =
-                p.alpha * (row_scale != nullptr && r < p.rows_b ? row_scale[r] : 1.0f);
-            vals[cc * 16 + t] = round_bf16(to_float(raw[t]) * sr * sc);
+            vals[cc * 16 + t] =
+                round_bf16(acc_to_float<OP>(raw[t]) * s_scale[cc * 16 + t] * sc);
           }
         }
         if (row_in_tile >= 64) {
@@ -404,71 +535,51 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int j = 0; j < BLOCK_N; ++j) xchg[j * 64 + (row_in_tile - 64)] = vals[j];
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (row_in_tile < 64) {
+        if (row_in_tile < 64 && gi < p.rows_a) {
           const int oc = tile_a * 64 + row_in_tile;
-          if (gi < p.rows_a) {
 #pragma unroll
-            for (int j = 0; j < BLOCK_N; ++j) {
-              const int r = tile_b * BLOCK_N + j;
-              if (r < p.rows_b) {
-                const float o = gelu_tanh_f(vals[j]) * xchg[j * 64 + row_in_tile];
-                store_one(p, out_base + (long long)r * p.ldc + oc, o);
-              }
+          for (int j = 0; j < BLOCK_N; ++j) {
+            const int r = tile_b * BLOCK_N + j;
+            if (r < p.rows_b) {
+              const float o = gelu_tanh_f(vals[j]) * xchg[j * 64 + row_in_tile];
+              store_one(p, out_base + (long long)r * p.ldc + oc, o);
             }
           }
         }
       }
     } else if constexpr (!SWAP) {
-      const int r = gi;
-      const float sr = p.alpha * (row_scale != nullptr && r < p.rows_a ? row_scale[r] : 1.0f);
-#pragma unroll 1
-      for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
-        uint32_t raw[16];
-        ptx::tmem_ld_16(taddr_row + cc * 16, raw);
-        ptx::tmem_ld_wait();
-        const int c0 = tile_b * BLOCK_N + cc * 16;
-        if (r >= p.rows_a || c0 >= p.rows_b) continue;
-        const int valid = min(16, p.rows_b - c0);
-        if (p.out_type == kOutS32) {
-          int* dst = reinterpret_cast<int*>(p.out) + out_base + (long long)r * p.ldc + c0;
-          for (int t = 0; t < valid; ++t) dst[t] = static_cast<int>(raw[t]);
-          continue;
-        }
-        float o[16];
-#pragma unroll
-        for (int t = 0; t < 16; ++t) {
-          const int c = min(c0 + t, p.rows_b - 1);
-          const float sc = p.col_scale != nullptr ? p.col_scale[c] : 1.0f;
-          const float v = to_float(raw[t]) * sr * sc;
-          o[t] = p.out_type == kOutF32 ? v : epilogue_value(p, out_base, r, c, v);
-        }
-        store_chunk16(p, out_base + (long long)r * p.ldc + c0, valid, o);
+#define PI05_EPI_CASE(MODE)                                                                      \
+  case MODE:                                                                                     \
+    epilogue_normal<OP, BLOCK_N, MODE>(p, taddr_row, gi, tile_b, out_base, sr, s_scale, s_bias, \
+                                       s_gate);                                                  \
+    break;
+      switch (p.mode) {
+        PI05_EPI_CASE(kEpiStore)
+        PI05_EPI_CASE(kEpiBiasGelu)
+        PI05_EPI_CASE(kEpiBiasSilu)
+        PI05_EPI_CASE(kEpiBiasResidual)
+        PI05_EPI_CASE(kEpiBiasPos)
+        PI05_EPI_CASE(kEpiGateResidual)
+        default:
+          break;
       }
+#undef PI05_EPI_CASE
     } else {
-      // swapped: lane index = logical column, TMEM column = logical row
-      const int c = gi;
-      const float sc = p.col_scale != nullptr && c < p.rows_a ? p.col_scale[c] : 1.0f;
-#pragma unroll 1
-      for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
-        uint32_t raw[16];
-        ptx::tmem_ld_16(taddr_row + cc * 16, raw);
-        ptx::tmem_ld_wait();
-        if (c >= p.rows_a) continue;
-#pragma unroll 1
-        for (int t = 0; t < 16; ++t) {
-          const int r = tile_b * BLOCK_N + cc * 16 + t;
-          if (r >= p.rows_b) break;
-          const long long index = out_base + (long long)r * p.ldc + c;
-          if (p.out_type == kOutS32) {
-            reinterpret_cast<int*>(p.out)[index] = static_cast<int>(raw[t]);
-            continue;
-          }
-          const float sr = p.alpha * (row_scale != nullptr ? row_scale[r] : 1.0f);
-          const float v = to_float(raw[t]) * sr * sc;
-          const float o = p.out_type == kOutF32 ? v : epilogue_value(p, out_base, r, c, v);
-          store_one(p, index, o);
-        }
+#define PI05_EPI_CASE(MODE)                                                               \
+  case MODE:                                                                              \
+    epilogue_swapped<OP, BLOCK_N, MODE>(p, taddr_row, gi, tile_b, out_base, s_scale);     \
+    break;
+      switch (p.mode) {
+        PI05_EPI_CASE(kEpiStore)
+        PI05_EPI_CASE(kEpiBiasGelu)
+        PI05_EPI_CASE(kEpiBiasSilu)
+        PI05_EPI_CASE(kEpiBiasResidual)
+        PI05_EPI_CASE(kEpiBiasPos)
+        PI05_EPI_CASE(kEpiGateResidual)
+        default:
+          break;
       }
+#undef PI05_EPI_CASE
     }
   }
 

@@ -181,6 +181,14 @@ class CapturedGraph:
         check(lib().pi05_graph_stage_times(self._h, ms.ctypes.data), "pi05_graph_stage_times")
         return {"vision": float(ms[0]), "prefix": float(ms[1]), "denoise": float(ms[2])}
 
+    def time_launches(self, name: str):
+        """(mean ms, count) of the launches called `name`, CUDA events on the engine stream."""
+        mean = C.c_float(0.0)
+        count = C.c_int32(0)
+        check(lib().pi05_graph_time_launches(self._h, name.encode(), C.byref(mean), C.byref(count)),
+              "pi05_graph_time_launches")
+        return float(mean.value), int(count.value)
+
     def workspace_bytes(self) -> int:
         return int(lib().pi05_graph_workspace_bytes(self._h))
 

@@ -154,6 +154,9 @@ int pi05_graph_output(Pi05Graph* graph, float* host_out);
 int pi05_graph_time_replays(Pi05Graph* graph, int32_t iterations, float* ms_each);
 /* One eager pass timed per stage: {vision tower, prefix prefill, denoise loop} in ms. */
 int pi05_graph_stage_times(Pi05Graph* graph, float* ms3);
+/* One eager pass with a CUDA-event pair around every launch called `name`
+ * ("language.gate_up", "action.qkv", ...): mean duration in ms and number of launches. */
+int pi05_graph_time_launches(Pi05Graph* graph, const char* name, float* mean_ms, int32_t* count);
 size_t pi05_graph_workspace_bytes(const Pi05Graph* graph);
 size_t pi05_graph_workspace_used_bytes(const Pi05Graph* graph);
 int32_t pi05_graph_num_launches(const Pi05Graph* graph);

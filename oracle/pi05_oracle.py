@@ -285,24 +285,34 @@ def _lcg_block_tables() -> Tuple[np.ndarray, np.ndarray]:
     return _lcg_tables
 
 
-def lcg_values(seed: int, offset: int, count: int) -> np.ndarray:
-    """Elements [offset, offset+count) of SyntheticRng(seed) as bf16-rounded float32."""
-    state0 = (seed ^ LCG_SEED_XOR) & MASK64
-    ja, jc = lcg_jump(offset)
-    state = (ja * state0 + jc) & MASK64
+def _lcg_block(seed_state: int, start: int, out: np.ndarray) -> None:
+    ja, jc = lcg_jump(start)
+    state = (ja * seed_state + jc) & MASK64
     ta, tc = _lcg_block_tables()
-    out = np.empty(count, dtype=F32)
-    done = 0
+    take = out.shape[0]
     with np.errstate(over="ignore"):
-        while done < count:
-            take = min(_LCG_BLOCK, count - done)
-            s = ta[:take] * np.uint64(state) + tc[:take]
-            bits = (s >> np.uint64(33)).astype(np.uint32)
-            unit = bits.astype(F32) / F32(2147483648.0)
-            out[done:done + take] = (unit * F32(2.0) - F32(1.0)) * AMPLITUDE
-            state = int(s[take - 1])
-            done += take
-    return round_bf16(out)
+        s = ta[:take] * np.uint64(state) + tc[:take]
+        bits = (s >> np.uint64(33)).astype(np.uint32)
+        unit = bits.astype(F32) / F32(2147483648.0)
+        out[:] = round_bf16((unit * F32(2.0) - F32(1.0)) * AMPLITUDE)
+
+
+def lcg_values(seed: int, offset: int, count: int) -> np.ndarray:
+    """Elements [offset, offset+count) of SyntheticRng(seed) as bf16-rounded float32.
+    Blocks of 2^20 elements are independent (jump-ahead), so they run on a thread pool."""
+    state0 = (seed ^ LCG_SEED_XOR) & MASK64
+    _lcg_block_tables()
+    out = np.empty(count, dtype=F32)
+    starts = list(range(0, count, _LCG_BLOCK))
+    if len(starts) <= 2:
+        for b in starts:
+            _lcg_block(state0, offset + b, out[b:b + _LCG_BLOCK])
+    else:
+        import concurrent.futures
+        import os
+        with concurrent.futures.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
+            list(pool.map(lambda b: _lcg_block(state0, offset + b, out[b:b + _LCG_BLOCK]), starts))
+    return out
 
 
 def synthetic_layout(cfg: Pi05Config) -> Dict[str, Tuple[int, Tuple[int, ...]]]:
@@ -498,7 +508,7 @@ class Pi05Oracle:
 
     # ---- linear layers -----------------------------------------------------
     def _prepare(self, key: str, names) -> tuple:
-        cacheable = key.startswith(("action", "time_mlp"))
+        cacheable = key.startswith(("action", "time_mlp")) or getattr(self, "_prepare_all", False)
         if cacheable and key in self._prepared:
             return self._prepared[key]
         w = self.w.packed(names)
