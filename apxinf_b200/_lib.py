@@ -50,6 +50,9 @@ class GemmArgs(C.Structure):
         ("alpha", C.c_float), ("out_inv_scale", C.c_float),
         ("status", C.c_void_p),
         ("force_swap", C.c_int32), ("force_block_n", C.c_int32),
+        ("partials", C.c_void_p), ("partials_bytes", C.c_uint64),
+        ("tile_counters", C.c_void_p), ("max_tiles", C.c_int32), ("force_split_k", C.c_int32),
+        ("trace", C.c_void_p),
     ]
 
 

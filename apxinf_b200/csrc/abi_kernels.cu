@@ -53,6 +53,12 @@ extern "C" int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream) {
   q.status = args->status;
   q.force_swap = args->force_swap;
   q.force_block_n = args->force_block_n;
+  q.partials = args->partials;
+  q.partials_bytes = args->partials_bytes;
+  q.tile_counters = args->tile_counters;
+  q.max_tiles = args->max_tiles;
+  q.force_split_k = args->force_split_k;
+  q.trace = args->trace;
   GemmPlan plan;
   const int rc = gemm_plan_build(q, &plan);
   if (rc != kPi05Ok) return rc;

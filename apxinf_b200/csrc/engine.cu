@@ -25,6 +25,9 @@ namespace pi05 {
 
 namespace {
 
+constexpr size_t kSplitScratchBytes = 32u << 20;  // split-K partial tiles
+constexpr int kSplitMaxTiles = 4096;
+
 uint16_t bf16_bits(float value) {
   uint32_t bits;
   std::memcpy(&bits, &value, 4);
@@ -294,8 +297,13 @@ void PreparedGraph::add_kernel(const char* name, std::function<cudaError_t(cudaS
   ops_.push_back(std::move(op));
 }
 
-int PreparedGraph::add_gemm(const char* name, const GemmProblem& problem) {
+int PreparedGraph::add_gemm(const char* name, const GemmProblem& request) {
   if (measuring_) return kPi05Ok;
+  GemmProblem problem = request;
+  problem.partials = d_partials_;
+  problem.partials_bytes = kSplitScratchBytes;
+  problem.tile_counters = d_tile_counters_;
+  problem.max_tiles = kSplitMaxTiles;
   Op op;
   op.name = name;
   op.stage = stage_;
@@ -349,6 +357,7 @@ int PreparedGraph::linear(const char* name, const Act& in, int rows, const Linea
   q.alpha = prec == kPrecFp8 ? e_->act_scale() : 1.0f;
   q.out_inv_scale = out_inv_scale;
   q.status = e_->status();
+  q.b_static = true;
   return add_gemm(name, q);
 }
 
@@ -480,6 +489,8 @@ int PreparedGraph::build(bool measuring) {
   d_state_ = arena_.alloc((size_t)Ra * c.action_dim * 2);
   d_styles_ = arena_.alloc((size_t)(2 * ac.depth + 1) * S_ * 3 * ac.width * 2);
   d_time_emb_ = arena_.alloc((size_t)S_ * ac.width * 2);
+  d_partials_ = arena_.alloc(kSplitScratchBytes);
+  d_tile_counters_ = static_cast<int*>(arena_.alloc((size_t)kSplitMaxTiles * 4));
   note("state", d_state_, (size_t)Ra * c.action_dim * 2);
   note("styles", d_styles_, (size_t)(2 * ac.depth + 1) * S_ * 3 * ac.width * 2);
   std::vector<void*> k_cache(lg.depth), v_cache(lg.depth);

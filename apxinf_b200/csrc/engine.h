@@ -155,6 +155,8 @@ class PreparedGraph {
   void* d_state_ = nullptr;
   void* d_styles_ = nullptr;
   void* d_time_emb_ = nullptr;
+  void* d_partials_ = nullptr;      // split-K scratch shared by every GEMM of the graph
+  int* d_tile_counters_ = nullptr;
   uint16_t* h_out_ = nullptr;  // pinned
 };
 

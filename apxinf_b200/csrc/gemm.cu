@@ -4,9 +4,17 @@
 
 #include <cudaTypedefs.h>
 
+#include <algorithm>
 #include <mutex>
 
 namespace pi05 {
+
+namespace {
+bool g_pdl_enabled = true;
+}
+bool pdl_enabled() { return g_pdl_enabled; }
+void set_pdl_enabled(bool enabled) { g_pdl_enabled = enabled; }
+
 namespace {
 
 using EncodeTiledFn = PFN_cuTensorMapEncodeTiled_v12000;
@@ -185,7 +193,33 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   p.out_type = q.out_type;
   p.status = q.status;
 
-  plan->grid = dim3((p.rows_a + 127) / 128, (p.rows_b + block_n - 1) / block_n, q.nb0 * q.nb1);
+  const int tiles_x = (p.rows_a + 127) / 128, tiles_y = (p.rows_b + block_n - 1) / block_n;
+  const long long tiles = (long long)tiles_x * tiles_y * q.nb0 * q.nb1;
+  int split = 1;
+  if (q.partials != nullptr && q.tile_counters != nullptr && q.out_type != kOutS32 &&
+      q.force_split_k != 1) {
+    if (q.force_split_k > 1) {
+      split = q.force_split_k;
+    } else if (swap) {
+      // weight streaming for a handful of rows: spread the K range until ~one CTA per SM
+      if (p.num_kb >= 4) split = static_cast<int>(std::min<long long>(p.num_kb / 2, 148 / tiles));
+    } else if (tiles <= 100 && p.num_kb >= 32) {
+      split = static_cast<int>(std::min<long long>(p.num_kb / 8, 296 / tiles));
+    }
+    split = std::max(1, std::min(split, p.num_kb));
+    const size_t need = static_cast<size_t>(tiles) * split * 128 * block_n * 4;
+    if (need > q.partials_bytes || tiles > q.max_tiles) split = 1;
+  }
+  p.kb_per_split = (p.num_kb + split - 1) / split;
+  split = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+  p.split_k = split;
+  p.partials = reinterpret_cast<uint32_t*>(q.partials);
+  p.tile_counters = q.tile_counters;
+  p.trace = q.trace;
+  p.static_a = (swap && q.b_static) ? 1 : 0;
+  p.static_b = (!swap && q.b_static) ? 1 : 0;
+  plan->split_k = split;
+  plan->grid = dim3(tiles_x, tiles_y, q.nb0 * q.nb1 * split);
   plan->smem_bytes = smem;
   plan->kernel = kernel;
   plan->swap = swap;
@@ -196,8 +230,17 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
 cudaError_t gemm_plan_launch(const GemmPlan& plan, cudaStream_t stream) {
   void* args[3] = {const_cast<CUtensorMap*>(&plan.tmap_a), const_cast<CUtensorMap*>(&plan.tmap_b),
                    const_cast<GemmParams*>(&plan.params)};
-  return cudaLaunchKernel(plan.kernel, plan.grid, dim3(kGemmThreads), args, plan.smem_bytes,
-                          stream);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = plan.grid;
+  config.blockDim = dim3(kGemmThreads);
+  config.dynamicSmemBytes = plan.smem_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelExC(&config, plan.kernel, args);
 }
 
 }  // namespace pi05

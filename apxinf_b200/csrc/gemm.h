@@ -45,6 +45,16 @@ struct GemmProblem {
   float alpha = 1.0f;
   float out_inv_scale = 1.0f;
   int* status = nullptr;
+  // optional split-K scratch (device): raw 32-bit partial tiles and per-tile arrival counters
+  // (counters must be zero before the first launch; every launch leaves them zero again)
+  void* partials = nullptr;
+  size_t partials_bytes = 0;
+  int* tile_counters = nullptr;
+  int max_tiles = 0;
+  int force_split_k = 0;  // 0 = automatic, 1 = off, n = exactly n (clamped to the K blocks)
+  unsigned int* trace = nullptr;  // optional device uint32[6], see GemmParams::trace
+  // the b operand is a weight matrix no kernel of the stream writes (enables early TMA loads)
+  bool b_static = false;
   // tuning overrides (0 / -1 = automatic)
   int force_swap = -1;
   int force_block_n = 0;
@@ -59,6 +69,7 @@ struct GemmPlan {
   const void* kernel = nullptr;
   bool swap = false;
   int block_n = 0;
+  int split_k = 1;
 };
 
 // Error codes of this library's C ABI (negative = rejected before launch).

@@ -25,6 +25,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace pi05 {
@@ -79,6 +80,20 @@ struct GemmParams {
   int mode;
   int out_type;
   int* status;                    // device status word, 0 = ok
+  // split-K: blockIdx.z = split + split_k * batch; each split owns kb_per_split K blocks,
+  // dumps its raw accumulator tile to `partials`, and the last split to arrive on a tile
+  // (per-tile arrival counter, left at zero again) sums them in split order and runs the epilogue.
+  int split_k;
+  int kb_per_split;
+  uint32_t* partials;             // [tiles][split_k][128][BLOCK_N] raw 32-bit accumulators
+  int* tile_counters;             // [tiles], zero between launches
+  // optional: CTA (0,0,0) writes SM-clock deltas from kernel entry to
+  // {setup done, first operands landed, last MMA issued, accumulator ready,
+  //  epilogue done, TMEM freed} for latency breakdowns
+  unsigned int* trace;
+  // operands that no kernel of the stream writes (weights): their TMA loads may be issued
+  // before the programmatic-dependency wait
+  int static_a, static_b;
 };
 
 __device__ __forceinline__ float round_bf16(float x) {
@@ -247,12 +262,65 @@ __device__ __forceinline__ void load_row16(const __nv_bfloat16* src, int valid, 
   }
 }
 
+// Where the epilogue reads the accumulator from: this CTA's TMEM (one split) or
+// the sum over all splits' partial tiles in global memory, added in split order
+// so the result does not depend on which split arrived last.
+template <int OP, int BLOCK_N>
+struct AccSource {
+  uint32_t taddr_row;
+  const uint32_t* partial_row;  // this thread's row in split 0, or null
+  long long split_stride;       // elements between splits
+  int splits;
+
+  __device__ __forceinline__ void load16(int col0, uint32_t (&raw)[16]) const {
+    if (partial_row == nullptr) {
+      ptx::tmem_ld_16(taddr_row + col0, raw);
+      return;
+    }
+    float facc[16];
+    int iacc[16];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      facc[t] = 0.0f;
+      iacc[t] = 0;
+    }
+    for (int s = 0; s < splits; ++s) {
+      const uint4* src = reinterpret_cast<const uint4*>(partial_row + s * split_stride + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 v = __ldcg(src + q);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if constexpr (OP == kOpS8) {
+            iacc[q * 4 + e] += static_cast<int>(w[e]);
+          } else {
+            facc[q * 4 + e] += __uint_as_float(w[e]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      if constexpr (OP == kOpS8) {
+        raw[t] = static_cast<uint32_t>(iacc[t]);
+      } else {
+        raw[t] = __float_as_uint(facc[t]);
+      }
+    }
+  }
+  __device__ __forceinline__ void wait() const {
+    if (partial_row == nullptr) ptx::tmem_ld_wait();
+  }
+};
+
 // Thread = one output row, TMEM columns = output columns.
 template <int OP, int BLOCK_N, int MODE>
-__device__ __forceinline__ void epilogue_normal(const GemmParams& p, uint32_t taddr_row, int r,
+__device__ __forceinline__ void epilogue_normal(const GemmParams& p, const AccSource<OP, BLOCK_N>& acc, int r,
                                                 int tile_b, long long out_base, float sr,
                                                 const float* s_scale, const float* s_bias,
-                                                const float* s_gate) {
+                                                const float* s_gate, long long t_entry = 0,
+                                                bool tracing = false) {
   constexpr bool kExtra =
       MODE == kEpiBiasResidual || MODE == kEpiBiasPos || MODE == kEpiGateResidual;
   const bool row_ok = r < p.rows_a;
@@ -264,7 +332,7 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p, uint32_t ta
 #pragma unroll 2
   for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
     uint32_t raw[16];
-    ptx::tmem_ld_16(taddr_row + cc * 16, raw);
+    acc.load16(cc * 16, raw);
     const int c0 = tile_b * BLOCK_N + cc * 16;
     const int valid = row_ok ? min(16, p.rows_b - c0) : 0;
     float extra[16];
@@ -274,7 +342,8 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p, uint32_t ta
 #pragma unroll
       for (int t = 0; t < 16; ++t) extra[t] = 0.0f;
     }
-    ptx::tmem_ld_wait();
+    acc.wait();
+    if (tracing && cc == 0) p.trace[6] = static_cast<unsigned int>(clock64() - t_entry);
     if (valid <= 0) continue;
     const long long index = out_base + (long long)r * p.ldc + c0;
     if (p.out_type == kOutS32) {
@@ -293,12 +362,13 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p, uint32_t ta
       o[t] = p.out_type == kOutF32 ? v : epi_apply<MODE>(v, s_bias[j], extra[t], s_gate[j]);
     }
     store_chunk16(p, index, valid, o);
+    if (tracing && cc == 0) p.trace[7] = static_cast<unsigned int>(clock64() - t_entry);
   }
 }
 
 // Thread = one output column (weight row), TMEM columns = output rows.
 template <int OP, int BLOCK_N, int MODE>
-__device__ __forceinline__ void epilogue_swapped(const GemmParams& p, uint32_t taddr_row, int c,
+__device__ __forceinline__ void epilogue_swapped(const GemmParams& p, const AccSource<OP, BLOCK_N>& acc, int c,
                                                  int tile_b, long long out_base,
                                                  const float* s_rowscale) {
   constexpr bool kExtra =
@@ -310,7 +380,7 @@ __device__ __forceinline__ void epilogue_swapped(const GemmParams& p, uint32_t t
 #pragma unroll
   for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
     uint32_t raw[16];
-    ptx::tmem_ld_16(taddr_row + cc * 16, raw);
+    acc.load16(cc * 16, raw);
     const int r0 = tile_b * BLOCK_N + cc * 16;
     const int valid = col_ok ? min(16, p.rows_b - r0) : 0;
     float extra[16];
@@ -324,7 +394,7 @@ __device__ __forceinline__ void epilogue_swapped(const GemmParams& p, uint32_t t
                        : __bfloat162float(p.residual[out_base + (long long)r * p.ldc + c]);
       }
     }
-    ptx::tmem_ld_wait();
+    acc.wait();
     if (valid <= 0) continue;
 #pragma unroll
     for (int t = 0; t < 16; ++t) {
@@ -367,12 +437,20 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   float* s_bias = s_scale + 256;
   float* s_gate = s_bias + 256;
 
+  pdl_launch_dependents();
+  const long long t_entry = clock64();
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tile_a = blockIdx.x;
   const int tile_b = blockIdx.y;
-  const int b0 = blockIdx.z % p.nb0;
-  const int b1 = blockIdx.z / p.nb0;
+  const int split = blockIdx.z % p.split_k;
+  const int batch = blockIdx.z / p.split_k;
+  const int b0 = batch % p.nb0;
+  const int b1 = batch / p.nb0;
+  const int kb_begin = split * p.kb_per_split;
+  const int kb_end = min(p.num_kb, kb_begin + p.kb_per_split);
+  const int my_kb = kb_end - kb_begin;  // >= 1 by construction
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -391,6 +469,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (tracing && threadIdx.x == 0) p.trace[0] = static_cast<unsigned int>(clock64() - t_entry);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -399,15 +478,15 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::prefetch_tensormap(&tmap_b);
       bool ok = true;
       int issued = 0;
-      for (int kb = 0; kb < p.num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t round = kb / STAGES;
-        if (round > 0) ok = ptx::mbar_wait(&empty_bar[s], (round - 1) & 1);
-        if (!ok) break;
-        uint8_t* sa = smem + s * kStageBytes;
-        uint8_t* sb = sa + kStageABytes;
-        ptx::mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
-        ptx::tma_load_4d(sa, &tmap_a, &full_bar[s], kb * kBlockK, tile_a * kTileRowsA, b0, b1);
+      auto load_a = [&](int it) {
+        const int s = it % STAGES;
+        ptx::tma_load_4d(smem + s * kStageBytes, &tmap_a, &full_bar[s], (kb_begin + it) * kBlockK,
+                         tile_a * kTileRowsA, b0, b1);
+      };
+      auto load_b = [&](int it) {
+        const int s = it % STAGES;
+        uint8_t* sb = smem + s * kStageBytes + kStageABytes;
+        const int kb = kb_begin + it;
         if constexpr (B_MN) {
 #pragma unroll
           for (int chunk = 0; chunk < BLOCK_N / 64; ++chunk) {
@@ -417,25 +496,50 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
         } else {
           ptx::tma_load_4d(sb, &tmap_b, &full_bar[s], kb * kBlockK, tile_b * BLOCK_N, b0, b1);
         }
+      };
+      // First ring fill: static operands (weights) stream in while the producer of the
+      // activations may still be running; the dependent operand follows the wait.
+      const int first_fill = min(my_kb, STAGES);
+      for (int it = 0; it < first_fill; ++it) {
+        ptx::mbar_arrive_expect_tx(&full_bar[it], kStageBytes);
+        if (p.static_a) load_a(it);
+        if (p.static_b) load_b(it);
+      }
+      pdl_wait();
+      for (int it = 0; it < first_fill; ++it) {
+        if (!p.static_a) load_a(it);
+        if (!p.static_b) load_b(it);
+      }
+      issued = first_fill;
+      for (int it = first_fill; it < my_kb && ok; ++it) {
+        const int s = it % STAGES;
+        const uint32_t round = it / STAGES;
+        ok = ptx::mbar_wait(&empty_bar[s], (round - 1) & 1);
+        if (!ok) break;
+        ptx::mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+        load_a(it);
+        load_b(it);
         ++issued;
       }
       if (!ok) {
         atomicCAS(p.status, 0, kGemmTimeoutProducer);
         // let copies already in flight land before the CTA retires
         const int first = issued > STAGES ? issued - STAGES : 0;
-        for (int kb = first; kb < issued; ++kb) {
-          ptx::mbar_wait(&full_bar[kb % STAGES], (kb / STAGES) & 1);
+        for (int it = first; it < issued; ++it) {
+          ptx::mbar_wait(&full_bar[it % STAGES], (it / STAGES) & 1);
         }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
+    pdl_wait();
     if (lane == 0) {
       bool ok = true;
-      for (int kb = 0; kb < p.num_kb; ++kb) {
+      for (int kb = 0; kb < my_kb; ++kb) {
         const int s = kb % STAGES;
         ok = ptx::mbar_wait(&full_bar[s], (kb / STAGES) & 1);
         if (!ok) break;
+        if (tracing && kb == 0) p.trace[1] = static_cast<unsigned int>(clock64() - t_entry);
         ptx::tc_fence_after();
         const uint32_t a_addr = ptx::smem_u32(smem + s * kStageBytes);
         const uint32_t b_addr = a_addr + kStageABytes;
@@ -451,6 +555,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (!ok) atomicCAS(p.status, 0, kGemmTimeoutMma);
       // Always signal the epilogue so that it never waits on a dead pipeline.
       ptx::umma_commit(accum_bar);
+      if (tracing) p.trace[2] = static_cast<unsigned int>(clock64() - t_entry);
     }
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
@@ -464,14 +569,20 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     // Stage the per-column (normal) or per-row (swapped) vectors of this tile
     // in shared memory while the main loop runs.
-    for (int j = ep_tid; j < BLOCK_N; j += 128) {
-      const int idx = tile_b * BLOCK_N + j;
-      const bool in = idx < p.rows_b;
-      if constexpr (!SWAP) {
+    if constexpr (!SWAP) {
+      for (int j = ep_tid; j < BLOCK_N; j += 128) {
+        const int idx = tile_b * BLOCK_N + j;
+        const bool in = idx < p.rows_b;
         s_scale[j] = p.col_scale != nullptr && in ? p.col_scale[idx] : 1.0f;
         s_bias[j] = p.bias != nullptr && in ? __bfloat162float(p.bias[idx]) : 0.0f;
         s_gate[j] = p.gate != nullptr && in ? __bfloat162float(p.gate[idx]) : 0.0f;
-      } else {
+      }
+    }
+    pdl_wait();  // everything below may read what earlier kernels of the stream wrote
+    if constexpr (SWAP) {
+      for (int j = ep_tid; j < BLOCK_N; j += 128) {
+        const int idx = tile_b * BLOCK_N + j;
+        const bool in = idx < p.rows_b;
         s_scale[j] = p.alpha * (row_scale != nullptr && in ? row_scale[idx] : 1.0f);
       }
     }
@@ -484,9 +595,45 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const bool ok = ptx::mbar_wait(accum_bar, 0);
     if (!ok && lane == 0) atomicCAS(p.status, 0, kGemmTimeoutEpilogue);
     ptx::tc_fence_after();
+    if (tracing && ep_tid == 0) p.trace[3] = static_cast<unsigned int>(clock64() - t_entry);
     const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
 
-    if (p.mode == kEpiGeglu) {
+    AccSource<OP, BLOCK_N> acc{taddr_row, nullptr, 0, 1};
+    bool run_epilogue = true;
+    if (p.split_k > 1) {
+      const long long tile_id =
+          ((long long)batch * gridDim.y + tile_b) * gridDim.x + tile_a;
+      uint32_t* tile_ws = p.partials + tile_id * p.split_k * (128LL * BLOCK_N);
+      uint32_t* mine = tile_ws + (long long)split * (128LL * BLOCK_N) + row_in_tile * BLOCK_N;
+#pragma unroll
+      for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
+        uint32_t raw[16];
+        ptx::tmem_ld_16(taddr_row + cc * 16, raw);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          __stcg(reinterpret_cast<uint4*>(mine + cc * 16) + q,
+                 make_uint4(raw[4 * q], raw[4 * q + 1], raw[4 * q + 2], raw[4 * q + 3]));
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      int* flag = reinterpret_cast<int*>(tmem_slot + 1);
+      if (ep_tid == 0) *flag = atomicAdd(&p.tile_counters[tile_id], 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      run_epilogue = *flag == p.split_k - 1;
+      if (run_epilogue) {
+        __threadfence();
+        if (ep_tid == 0) p.tile_counters[tile_id] = 0;
+        acc.partial_row = tile_ws + row_in_tile * BLOCK_N;
+        acc.split_stride = 128LL * BLOCK_N;
+        acc.splits = p.split_k;
+      }
+    }
+
+    if (!run_epilogue) {
+      // another split finishes this tile
+    } else if (p.mode == kEpiGeglu) {
       if constexpr (!SWAP) {
         // columns [128t, 128t+64) gate, [128t+64, 128t+128) up; thread-local.
 #pragma unroll 1
@@ -494,9 +641,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll 2
           for (int sub = 0; sub < 4; ++sub) {
             uint32_t rg[16], ru[16];
-            ptx::tmem_ld_16(taddr_row + pair * 128 + sub * 16, rg);
-            ptx::tmem_ld_16(taddr_row + pair * 128 + 64 + sub * 16, ru);
-            ptx::tmem_ld_wait();
+            acc.load16(pair * 128 + sub * 16, rg);
+            acc.load16(pair * 128 + 64 + sub * 16, ru);
+            acc.wait();
             const int jg = pair * 128 + sub * 16;
             const int cg = tile_b * BLOCK_N + jg;         // packed gate column
             const int oc = (cg / 128) * 64 + (cg % 128);  // output column
@@ -522,8 +669,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
         for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
           uint32_t raw[16];
-          ptx::tmem_ld_16(taddr_row + cc * 16, raw);
-          ptx::tmem_ld_wait();
+          acc.load16(cc * 16, raw);
+          acc.wait();
 #pragma unroll
           for (int t = 0; t < 16; ++t) {
             vals[cc * 16 + t] =
@@ -550,8 +697,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     } else if constexpr (!SWAP) {
 #define PI05_EPI_CASE(MODE)                                                                      \
   case MODE:                                                                                     \
-    epilogue_normal<OP, BLOCK_N, MODE>(p, taddr_row, gi, tile_b, out_base, sr, s_scale, s_bias, \
-                                       s_gate);                                                  \
+    epilogue_normal<OP, BLOCK_N, MODE>(p, acc, gi, tile_b, out_base, sr, s_scale, s_bias,       \
+                                       s_gate, t_entry, tracing && ep_tid == 0);                                                  \
     break;
       switch (p.mode) {
         PI05_EPI_CASE(kEpiStore)
@@ -567,7 +714,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     } else {
 #define PI05_EPI_CASE(MODE)                                                               \
   case MODE:                                                                              \
-    epilogue_swapped<OP, BLOCK_N, MODE>(p, taddr_row, gi, tile_b, out_base, s_scale);     \
+    epilogue_swapped<OP, BLOCK_N, MODE>(p, acc, gi, tile_b, out_base, s_scale);           \
     break;
       switch (p.mode) {
         PI05_EPI_CASE(kEpiStore)
@@ -583,11 +730,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
+  if (tracing && threadIdx.x == 64) p.trace[4] = static_cast<unsigned int>(clock64() - t_entry);
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
+    if (tracing && lane == 0) p.trace[5] = static_cast<unsigned int>(clock64() - t_entry);
   }
 }
 

@@ -2,6 +2,8 @@
 
 #include <cuda_fp8.h>
 
+#include "launch.cuh"
+
 namespace pi05 {
 namespace {
 
@@ -58,6 +60,8 @@ __device__ __forceinline__ float block_reduce(float v, float* scratch) {
 // One CTA per row, one 8-element vector per thread (cols <= 8 * blockDim.x).
 template <int KIND, int OUT>
 __global__ void norm_rows_kernel(NormArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[32];
   const int row = blockIdx.x;
   const int vec = threadIdx.x;
@@ -166,18 +170,14 @@ template <int KIND>
 cudaError_t launch_norm_kind(const NormArgs& a, int threads, cudaStream_t stream) {
   switch (a.out) {
     case kRowBf16:
-      norm_rows_kernel<KIND, kRowBf16><<<a.rows, threads, 0, stream>>>(a);
-      break;
+      return launch_pdl(norm_rows_kernel<KIND, kRowBf16>, dim3(a.rows), dim3(threads), 0, stream, a);
     case kRowE4m3:
-      norm_rows_kernel<KIND, kRowE4m3><<<a.rows, threads, 0, stream>>>(a);
-      break;
+      return launch_pdl(norm_rows_kernel<KIND, kRowE4m3>, dim3(a.rows), dim3(threads), 0, stream, a);
     case kRowInt8:
-      norm_rows_kernel<KIND, kRowInt8><<<a.rows, threads, 0, stream>>>(a);
-      break;
+      return launch_pdl(norm_rows_kernel<KIND, kRowInt8>, dim3(a.rows), dim3(threads), 0, stream, a);
     default:
       return cudaErrorInvalidValue;
   }
-  return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------
@@ -185,6 +185,8 @@ cudaError_t launch_norm_kind(const NormArgs& a, int threads, cudaStream_t stream
 // One CTA per token row. Work items of 4 rotary pairs (two 8-byte loads):
 // q_heads*half/4 for Q, half/4 for K, then head_dim/4 plain copies for V.
 __global__ void rope_kv_kernel(RopeArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int sample = row / a.tokens;
   const int token = row - sample * a.tokens;
@@ -251,6 +253,8 @@ __global__ void rope_kv_kernel(RopeArgs a) {
 // One warp per row, up to 1024 columns held in registers.
 __global__ void softmax_rows_kernel(__nv_bfloat16* scores, int rows_per_batch, int batches,
                                     long long batch_stride, int cols, long long ld) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp_global >= rows_per_batch * batches) return;
@@ -286,6 +290,8 @@ __global__ void softmax_rows_kernel(__nv_bfloat16* scores, int rows_per_batch, i
 // One thread per 8 output columns of one patch row.
 template <int OUT>
 __global__ void patchify_kernel(PatchifyArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int vec_per_row = a.ld >> 3;
   const int side = a.image_size / a.patch_size;
   const int area = a.patch_size * a.patch_size;
@@ -333,6 +339,8 @@ __global__ void patchify_kernel(PatchifyArgs a) {
 __global__ void embedding_kernel(const __nv_bfloat16* table, const uint32_t* ids,
                                  __nv_bfloat16* out, int batch, int tokens, int width, int vocab,
                                  int out_rows_per_batch, int row_offset) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int vec_per_row = width >> 3;
   const long long total = (long long)batch * tokens * vec_per_row;
   const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -360,6 +368,8 @@ __global__ void embedding_kernel(const __nv_bfloat16* table, const uint32_t* ids
 __global__ void quantize_rows_int8_kernel(const __nv_bfloat16* input, int8_t* output,
                                           float* row_scale, int cols, long long ld_in,
                                           long long ld_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[32];
   const int row = blockIdx.x;
   const __nv_bfloat16* in = input + (long long)row * ld_in;
@@ -392,6 +402,8 @@ __global__ void quantize_rows_int8_kernel(const __nv_bfloat16* input, int8_t* ou
 
 __global__ void quantize_e4m3_kernel(const __nv_bfloat16* input, uint8_t* output, long long count,
                                      float inv_scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)blockDim.x * gridDim.x;
   for (; index < count; index += stride) {
@@ -401,6 +413,8 @@ __global__ void quantize_e4m3_kernel(const __nv_bfloat16* input, uint8_t* output
 
 __global__ void euler_kernel(__nv_bfloat16* state, const __nv_bfloat16* velocity, long long count,
                              float dt) {
+  pdl_launch_dependents();
+  pdl_wait();
   long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)blockDim.x * gridDim.x;
   for (; index < count; index += stride) {
@@ -437,8 +451,7 @@ cudaError_t launch_rope(const RopeArgs& a, cudaStream_t stream) {
       a.position_offset < 0 || a.position_offset + a.tokens > a.cache_rows) {
     return cudaErrorInvalidValue;
   }
-  rope_kv_kernel<<<a.rows, 128, 0, stream>>>(a);
-  return cudaGetLastError();
+  return launch_pdl(rope_kv_kernel, dim3(a.rows), dim3(128), 0, stream, a);
 }
 
 cudaError_t launch_softmax(void* scores, int rows_per_batch, int batches, long long batch_stride,
@@ -450,9 +463,9 @@ cudaError_t launch_softmax(void* scores, int rows_per_batch, int batches, long l
   const long long warps = (long long)rows_per_batch * batches;
   const int threads = 256;
   const long long blocks = (warps * 32 + threads - 1) / threads;
-  softmax_rows_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
-      reinterpret_cast<__nv_bfloat16*>(scores), rows_per_batch, batches, batch_stride, cols, ld);
-  return cudaGetLastError();
+  return launch_pdl(softmax_rows_kernel, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0,
+                    stream, reinterpret_cast<__nv_bfloat16*>(scores), rows_per_batch, batches,
+                    batch_stride, cols, ld);
 }
 
 cudaError_t launch_patchify(const PatchifyArgs& a, cudaStream_t stream) {
@@ -467,11 +480,9 @@ cudaError_t launch_patchify(const PatchifyArgs& a, cudaStream_t stream) {
   const int threads = 256;
   const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
   if (a.out == kRowBf16) {
-    patchify_kernel<kRowBf16><<<blocks, threads, 0, stream>>>(a);
-  } else {
-    patchify_kernel<kRowE4m3><<<blocks, threads, 0, stream>>>(a);
+    return launch_pdl(patchify_kernel<kRowBf16>, dim3(blocks), dim3(threads), 0, stream, a);
   }
-  return cudaGetLastError();
+  return launch_pdl(patchify_kernel<kRowE4m3>, dim3(blocks), dim3(threads), 0, stream, a);
 }
 
 cudaError_t launch_embedding(const void* table, const uint32_t* ids, void* out, int batch,
@@ -484,10 +495,10 @@ cudaError_t launch_embedding(const void* table, const uint32_t* ids, void* out, 
   }
   const long long total = (long long)batch * tokens * (width >> 3);
   const int threads = 256;
-  embedding_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(table), ids, reinterpret_cast<__nv_bfloat16*>(out),
-      batch, tokens, width, vocab, out_rows_per_batch, row_offset);
-  return cudaGetLastError();
+  return launch_pdl(embedding_kernel, dim3(static_cast<unsigned>((total + threads - 1) / threads)),
+                    dim3(threads), 0, stream, reinterpret_cast<const __nv_bfloat16*>(table), ids,
+                    reinterpret_cast<__nv_bfloat16*>(out), batch, tokens, width, vocab,
+                    out_rows_per_batch, row_offset);
 }
 
 cudaError_t launch_quantize_rows_int8(const void* input, int8_t* output, float* row_scale, int rows,
@@ -498,9 +509,9 @@ cudaError_t launch_quantize_rows_int8(const void* input, int8_t* output, float* 
     return cudaErrorInvalidValue;
   }
   const int threads = cols >= 2048 ? 256 : 128;
-  quantize_rows_int8_kernel<<<rows, threads, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(input), output, row_scale, cols, ld_in, ld_out);
-  return cudaGetLastError();
+  return launch_pdl(quantize_rows_int8_kernel, dim3(rows), dim3(threads), 0, stream,
+                    reinterpret_cast<const __nv_bfloat16*>(input), output, row_scale, cols, ld_in,
+                    ld_out);
 }
 
 cudaError_t launch_quantize_e4m3(const void* input, uint8_t* output, long long count,
@@ -508,10 +519,9 @@ cudaError_t launch_quantize_e4m3(const void* input, uint8_t* output, long long c
   if (input == nullptr || output == nullptr || count <= 0) return cudaErrorInvalidValue;
   const int threads = 256;
   const long long blocks = (count + threads - 1) / threads;
-  quantize_e4m3_kernel<<<static_cast<unsigned>(blocks > 1184 ? 1184 : blocks), threads, 0,
-                         stream>>>(reinterpret_cast<const __nv_bfloat16*>(input), output, count,
-                                   inv_scale);
-  return cudaGetLastError();
+  return launch_pdl(quantize_e4m3_kernel, dim3(static_cast<unsigned>(blocks > 1184 ? 1184 : blocks)),
+                    dim3(threads), 0, stream, reinterpret_cast<const __nv_bfloat16*>(input), output,
+                    count, inv_scale);
 }
 
 cudaError_t launch_euler(void* state, const void* velocity, long long count, float dt,
@@ -519,10 +529,9 @@ cudaError_t launch_euler(void* state, const void* velocity, long long count, flo
   if (state == nullptr || velocity == nullptr || count <= 0) return cudaErrorInvalidValue;
   const int threads = 256;
   const long long blocks = (count + threads - 1) / threads;
-  euler_kernel<<<static_cast<unsigned>(blocks > 1184 ? 1184 : blocks), threads, 0, stream>>>(
-      reinterpret_cast<__nv_bfloat16*>(state), reinterpret_cast<const __nv_bfloat16*>(velocity),
-      count, dt);
-  return cudaGetLastError();
+  return launch_pdl(euler_kernel, dim3(static_cast<unsigned>(blocks > 1184 ? 1184 : blocks)),
+                    dim3(threads), 0, stream, reinterpret_cast<__nv_bfloat16*>(state),
+                    reinterpret_cast<const __nv_bfloat16*>(velocity), count, dt);
 }
 
 }  // namespace pi05

@@ -41,7 +41,7 @@ def new_status(device="cuda") -> torch.Tensor:
 def gemm(a, b, out, *, op, mode=_lib.EPI_STORE, out_type=_lib.OUT_BF16, bias=None,
          residual=None, col_scale=None, row_scale=None, pos=None, gate=None, alpha=1.0,
          out_inv_scale=1.0, b_mn_major=False, status=None, stream=None, force_swap=-1,
-         force_block_n=0):
+         force_block_n=0, partials=None, tile_counters=None, force_split_k=0, trace=None):
     """out[.., M, N'] = epilogue(a[.., M, K] @ b[.., N, K]^T); see Pi05GemmArgs."""
     m, k, lda, nb0, nb1, a_sb0, a_sb1 = _operand(a)
     if b_mn_major:
@@ -63,6 +63,11 @@ def gemm(a, b, out, *, op, mode=_lib.EPI_STORE, out_type=_lib.OUT_BF16, bias=Non
         pos_rows=(pos.shape[0] if pos is not None else 1),
         pos_ld=(pos.stride(0) if pos is not None else 0),
         gate=_ptr(gate), alpha=alpha, out_inv_scale=out_inv_scale, status=_ptr(status),
-        force_swap=force_swap, force_block_n=force_block_n)
+        force_swap=force_swap, force_block_n=force_block_n,
+        partials=_ptr(partials),
+        partials_bytes=(partials.numel() * partials.element_size() if partials is not None else 0),
+        tile_counters=_ptr(tile_counters),
+        max_tiles=(tile_counters.numel() if tile_counters is not None else 0),
+        force_split_k=force_split_k, trace=_ptr(trace))
     check(lib().pi05_gemm(C.byref(args), _stream_ptr(stream)), "pi05_gemm")
     return status

@@ -81,6 +81,18 @@ typedef struct Pi05GemmArgs {
   int32_t* status;        /* device int32, must be 0 before the call; set on device timeouts */
   int32_t force_swap;     /* -1 auto */
   int32_t force_block_n;  /* 0 auto */
+  /* Optional split-K scratch, caller-owned device memory: `partials` (partials_bytes) holds
+   * raw 32-bit accumulator tiles, `tile_counters` (max_tiles int32, zero before the first
+   * call; every call leaves them zero) counts arrivals per output tile. NULL = no split-K. */
+  void* partials;
+  uint64_t partials_bytes;
+  int32_t* tile_counters;
+  int32_t max_tiles;
+  int32_t force_split_k;  /* 0 auto, 1 off, n = n splits */
+  /* Optional device uint32[6]: SM-clock deltas from kernel entry of CTA (0,0,0) to {setup
+   * done, first operands landed, last MMA issued, accumulator ready, epilogue done, TMEM
+   * freed}. NULL = off. */
+  uint32_t* trace;
 } Pi05GemmArgs;
 
 int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream);

@@ -251,3 +251,91 @@ def test_gemm_rejects_bad_arguments():
         K.gemm(a[:, :60][:, :60].contiguous()[:, :52], a[:, :52], out, op=L.OP_BF16)
     with pytest.raises(Pi05Error):  # s32 output only for int8 operands
         K.gemm(a, a, out, op=L.OP_BF16, out_type=L.OUT_S32)
+
+
+def _scratch():
+    partials = torch.zeros(8 << 20, dtype=torch.uint8, device="cuda")
+    counters = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    return partials, counters
+
+
+@pytest.mark.parametrize("op", [0, 1, 2])
+@pytest.mark.parametrize("M,N,Kd,swap,split", [(10, 1024, 4096, 1, 0), (10, 1024, 4096, 1, 7),
+                                                (50, 2560, 1024, 1, 0), (300, 256, 8192, 0, 5),
+                                                (522, 384, 4096, 0, 0)])
+def test_gemm_split_k_matches_single_pass(op, M, N, Kd, swap, split):
+    """K range spread over several CTAs, partial tiles summed in split order by the last
+    arrival; two calls in a row share the scratch (the arrival counters return to zero)."""
+    L, K = _lib()
+    gen = torch.Generator().manual_seed(4000 + M + N + Kd + op)
+    if op == L.OP_S8:
+        a = torch.randint(-8, 9, (M, Kd), generator=gen, dtype=torch.int8)
+        b = torch.randint(-8, 9, (N, Kd), generator=gen, dtype=torch.int8)
+        af, bf = a.float(), b.float()
+    else:
+        a, af = make_operand(M, Kd, op, gen)
+        b, bf = make_operand(N, Kd, op, gen)
+    want = (af.double() @ bf.double().t()).float()
+    partials, counters = _scratch()
+    ad, bd = a.cuda(), b.cuda()
+    for _ in range(2):
+        out = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+        st = K.gemm(ad, bd, out, op=op, out_type=L.OUT_F32, force_swap=swap, partials=partials,
+                    tile_counters=counters, force_split_k=split)
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        assert int(counters.abs().sum().item()) == 0
+        if op == L.OP_S8:
+            assert torch.equal(out.cpu(), want), "integer partial sums must be exact"
+        else:
+            scale = math.sqrt(Kd) * (16 if op == L.OP_E4M3 else 1)
+            check_close(out, want, 2e-3 * scale, 1e-3, "split-k")
+
+
+@pytest.mark.parametrize("mode", [0, 3, 5])
+def test_gemm_split_k_epilogues(mode):
+    L, K = _lib()
+    M, N, Kd = 10, 384, 2048
+    gen = torch.Generator().manual_seed(91 + mode)
+    a, af = make_operand(M, Kd, L.OP_BF16, gen)
+    b, bf = make_operand(N, Kd, L.OP_BF16, gen, 0.05)
+    bias = (torch.randn(N, generator=gen) * 0.1).to(torch.bfloat16)
+    residual = torch.randn(M, N, generator=gen).to(torch.bfloat16)
+    gate = torch.randn(N, generator=gen).to(torch.bfloat16)
+    v = (af.double() @ bf.double().t()).float()
+    ref = _epilogue_reference(mode, v, bias.float(), residual.float(), None, gate.float(), L)
+    want = rb(ref)
+    partials, counters = _scratch()
+    out = residual.cuda().clone()
+    st = K.gemm(a.cuda(), b.cuda(), out, op=L.OP_BF16, mode=mode, bias=bias.cuda(), residual=out,
+                gate=gate.cuda(), partials=partials, tile_counters=counters, force_split_k=4)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    err = (out.float().cpu() - want).abs()
+    assert (err <= want.abs() * 2 ** -7 + 1e-2).all(), err.max().item()
+    assert (err == 0).float().mean().item() > 0.95
+
+
+@pytest.mark.parametrize("M,swap", [(10, 1), (300, 0)])
+def test_gemm_split_k_geglu(M, swap):
+    L, K = _lib()
+    inner, Kd = 256, 2048
+    gen = torch.Generator().manual_seed(55 + M)
+    a, af = make_operand(M, Kd, L.OP_BF16, gen, 0.5)
+    wg, wgf = make_operand(inner, Kd, L.OP_BF16, gen, 0.05)
+    wu, wuf = make_operand(inner, Kd, L.OP_BF16, gen, 0.05)
+    packed = torch.empty(2 * inner, Kd, dtype=wg.dtype)
+    pv = packed.view(inner // 64, 2, 64, Kd)
+    pv[:, 0] = wg.view(inner // 64, 64, Kd)
+    pv[:, 1] = wu.view(inner // 64, 64, Kd)
+    g = rb((af.double() @ wgf.double().t()).float())
+    u = rb((af.double() @ wuf.double().t()).float())
+    want = rb(gelu_tanh(g) * u)
+    partials, counters = _scratch()
+    out = torch.zeros(M, inner, dtype=torch.bfloat16, device="cuda")
+    st = K.gemm(a.cuda(), packed.cuda(), out, op=L.OP_BF16, mode=L.EPI_GEGLU, force_swap=swap,
+                partials=partials, tile_counters=counters, force_split_k=4)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    err = (out.float().cpu() - want).abs()
+    assert (err <= want.abs() * 2 ** -6 + 2e-2).all(), err.max().item()
