@@ -24,6 +24,7 @@ STATUS_NAMES = {
     -4: "PI05_ERR_CUDA",
     -5: "PI05_ERR_DEVICE_TIMEOUT",
     -6: "PI05_ERR_NOT_BUILT",
+    -7: "PI05_ERR_SCRATCH_LIMIT",
 }
 
 
@@ -71,6 +72,8 @@ def lib() -> C.CDLL:
         handle.pi05_version.restype = C.c_char_p
         handle.pi05_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
         handle.pi05_gemm.restype = C.c_int
+        handle.pi05_gemm_static_scratch.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+        handle.pi05_gemm_static_scratch.restype = C.c_int
         _declare_optional(handle)
         _lib = handle
     return _lib
@@ -84,6 +87,6 @@ def _declare_optional(handle: C.CDLL) -> None:
 def check(code: int, where: str) -> None:
     if code != 0:
         detail = ""
-        if code == -4:
+        if code in (-4, -7):
             detail = (lib().pi05_last_cuda_error() or b"").decode()
         raise Pi05Error(code, where, detail)

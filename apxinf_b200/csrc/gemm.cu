@@ -208,7 +208,12 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
     }
     split = std::max(1, std::min(split, p.num_kb));
     const size_t need = static_cast<size_t>(tiles) * split * 128 * block_n * 4;
-    if (need > q.partials_bytes || tiles > q.max_tiles) split = 1;
+    if (need > q.partials_bytes || tiles > q.max_tiles) {
+      // an explicit split request that does not fit the scratch is an error; the
+      // automatic choice quietly stays single-pass
+      if (q.force_split_k > 1 && split > 1) return kPi05ErrScratchLimit;
+      split = 1;
+    }
   }
   p.kb_per_split = (p.num_kb + split - 1) / split;
   split = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split

@@ -81,6 +81,7 @@ enum Pi05Error : int {
   kPi05ErrCuda = -4,
   kPi05ErrDeviceTimeout = -5,
   kPi05ErrNotBuilt = -6,
+  kPi05ErrScratchLimit = -7,
 };
 
 int gemm_plan_build(const GemmProblem& problem, GemmPlan* plan);

@@ -28,7 +28,8 @@ typedef enum Pi05Status {
   PI05_ERR_DRIVER = -3,         /* CUDA driver entry point missing or tensor-map encode failed */
   PI05_ERR_CUDA = -4,           /* a CUDA runtime call failed; see pi05_last_cuda_error() */
   PI05_ERR_DEVICE_TIMEOUT = -5, /* a bounded device-side wait ran out (status word != 0) */
-  PI05_ERR_NOT_BUILT = -6
+  PI05_ERR_NOT_BUILT = -6,
+  PI05_ERR_SCRATCH_LIMIT = -7   /* the request needs more split-K scratch than is available */
 } Pi05Status;
 
 /* Operand / output element types and fused epilogues of pi05_gemm. */
@@ -96,6 +97,34 @@ typedef struct Pi05GemmArgs {
 } Pi05GemmArgs;
 
 int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream);
+
+/*
+ * Split-K pi05_gemm for callers that must not allocate. (No counterpart in the reference,
+ * whose launch functions take their workspace from its arena.) Some users of this library
+ * cannot call cudaMalloc at the point where they need a GEMM: a control loop that has
+ * finished its set-up phase and may not risk an allocation stall or failure, a plugin that was
+ * handed a fixed device-memory budget by its host, code running between other people's
+ * latency-critical launches. For them the split-K scratch (partial accumulator tiles and the
+ * per-tile arrival counters) lives in a fixed array inside the library image instead of in
+ * caller memory: PI05_STATIC_SCRATCH_BYTES of partial tiles and PI05_STATIC_SCRATCH_TILES
+ * counters per GPU, held by every GPU that loads the library until the process exits.
+ *
+ * Same arguments and results as pi05_gemm with `force_split_k` >= 2; the `partials`,
+ * `partials_bytes`, `tile_counters` and `max_tiles` fields are ignored. Inputs, outputs and the
+ * status word are still the caller's. A request whose tiles x splits need more than the fixed
+ * scratch is refused with PI05_ERR_SCRATCH_LIMIT before anything is launched (detail text in
+ * pi05_last_cuda_error()). The call performs no cudaMalloc / cudaFree and uses no allocating
+ * library routine.
+ *
+ * The first call on each device looks up the array's device address (with that device
+ * current) and remembers it; make that first call during set-up, before any stream capture.
+ * Every call shares the one array and the counters are cleared on the stream before each
+ * launch, so two calls that can overlap on the GPU (different streams, or one stream captured
+ * into concurrently running graphs) race on it: serialise them on one stream.
+ */
+#define PI05_STATIC_SCRATCH_BYTES (8u << 20)
+#define PI05_STATIC_SCRATCH_TILES 2048
+int pi05_gemm_static_scratch(const Pi05GemmArgs* args, void* cuda_stream);
 
 
 /* ------------------------------------------------------------------------- */

@@ -1,0 +1,74 @@
+"""pi05_gemm_static_scratch — the GEMM entry point for callers that cannot allocate.
+
+Some callers of the library must not call cudaMalloc where they need a GEMM (a control loop
+past its set-up phase, a plugin with a fixed memory budget), so this variant keeps the
+split-K scratch in a fixed array inside the library. It must give exactly what pi05_gemm
+gives with caller-provided scratch, on two calls in a row (the array is shared and keeps
+the previous call's contents), and must refuse requests larger than its fixed scratch.
+Collected last on purpose: a run that stops at the first failure has then run everything else.
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("op", [0, 1, 2])
+def test_static_scratch_matches_caller_scratch_twice(op):
+    from apxinf_b200 import _lib as L, kernels as K
+    gen = torch.Generator().manual_seed(123 + op)
+    M, N, Kd = 10, 1024, 4096
+    if op == L.OP_BF16:
+        a = torch.randn(M, Kd, generator=gen).to(torch.bfloat16)
+        b = (torch.randn(N, Kd, generator=gen) * 0.05).to(torch.bfloat16)
+    elif op == L.OP_E4M3:
+        a = (torch.randn(M, Kd, generator=gen) * 4).to(torch.float8_e4m3fn)
+        b = (torch.randn(N, Kd, generator=gen) * 4).to(torch.float8_e4m3fn)
+    else:
+        a = torch.randint(-128, 128, (M, Kd), generator=gen, dtype=torch.int8)
+        b = torch.randint(-128, 128, (N, Kd), generator=gen, dtype=torch.int8)
+    bias = (torch.randn(N, generator=gen) * 0.1).to(torch.bfloat16).cuda()
+    ad, bd = a.cuda(), b.cuda()
+    alpha = {0: 1.0, 1: 1.0 / 64, 2: 1e-4}[op]
+    partials = torch.zeros(8 << 20, dtype=torch.uint8, device="cuda")
+    counters = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    want = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    st = K.gemm(ad, bd, want, op=op, bias=bias, alpha=alpha, partials=partials,
+                tile_counters=counters, force_split_k=8)
+    torch.cuda.synchronize()
+    assert st.item() == 0 and want.float().abs().max().item() > 0
+    for call in range(2):
+        got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        st = K.gemm(ad, bd, got, op=op, bias=bias, alpha=alpha, force_split_k=8, static_scratch=True)
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        # same kernel, same split order: no tolerance needed (the GEMM tests allow one bf16
+        # ulp against the CPU reference; here both sides are the GPU)
+        assert torch.equal(got, want), f"call {call}: max diff {(got.float() - want.float()).abs().max().item()}"
+
+
+def test_static_scratch_large_rows_and_limits():
+    from apxinf_b200 import Pi05Error, _lib as L, kernels as K
+    gen = torch.Generator().manual_seed(9)
+    M, N, Kd = 300, 256, 4096
+    a = torch.randn(M, Kd, generator=gen).to(torch.bfloat16).cuda()
+    b = (torch.randn(N, Kd, generator=gen) * 0.05).to(torch.bfloat16).cuda()
+    partials = torch.zeros(8 << 20, dtype=torch.uint8, device="cuda")
+    counters = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    want = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+    K.gemm(a, b, want, op=L.OP_BF16, out_type=L.OUT_F32, partials=partials, tile_counters=counters,
+           force_split_k=4, force_swap=0)
+    got = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+    K.gemm(a, b, got, op=L.OP_BF16, out_type=L.OUT_F32, force_split_k=4, force_swap=0,
+           static_scratch=True)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    # more tiles x splits than the built-in scratch holds: refused before launch
+    big_a = torch.zeros(4096, 4096, dtype=torch.bfloat16, device="cuda")
+    big_b = torch.zeros(4096, 4096, dtype=torch.bfloat16, device="cuda")
+    big_out = torch.zeros(4096, 4096, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(Pi05Error) as info:
+        K.gemm(big_a, big_b, big_out, op=L.OP_BF16, force_split_k=8, static_scratch=True)
+    assert info.value.code == -7 and "scratch" in str(info.value)
+    with pytest.raises(Pi05Error):  # the entry point is the split-K variant only
+        K.gemm(a, b, got, op=L.OP_BF16, out_type=L.OUT_F32, force_split_k=1, static_scratch=True)
