@@ -64,9 +64,10 @@ int encode_map(CUtensorMap* map, int op, const void* ptr, uint64_t inner, uint64
   return result == CUDA_SUCCESS ? kPi05Ok : kPi05ErrDriver;
 }
 
-template <int OP, int BLOCK_N, int STAGES, bool SWAP, bool B_MN>
-const void* kernel_ptr(int* smem) {
-  auto kernel = &gemm_umma_kernel<OP, BLOCK_N, STAGES, SWAP, B_MN>;
+template <int OP, int BLOCK_N, int STAGES, bool SWAP, bool B_MN, int EPI_WARPS = 8>
+const void* kernel_ptr(int* smem, int* threads) {
+  auto kernel = &gemm_umma_kernel<OP, BLOCK_N, STAGES, SWAP, B_MN, EPI_WARPS>;
+  *threads = gemm_threads(EPI_WARPS);
   *smem = gemm_smem_bytes(BLOCK_N, STAGES);
   // per device, idempotent and cheap: set on every plan build
   cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -75,23 +76,33 @@ const void* kernel_ptr(int* smem) {
 }
 
 template <int OP>
-const void* select_kernel(int block_n, bool swap, bool b_mn, int* smem) {
+const void* select_kernel(int block_n, bool swap, bool b_mn, bool multi_wave, int* smem,
+                          int* threads) {
   if (b_mn) {
     if constexpr (OP == kOpBf16) {
-      if (block_n == 128) return kernel_ptr<OP, 128, 6, false, true>(smem);
-      if (block_n == 256) return kernel_ptr<OP, 256, 4, false, true>(smem);
+      if (multi_wave) {
+        if (block_n == 128) return kernel_ptr<OP, 128, 3, false, true, 4>(smem, threads);
+        if (block_n == 256) return kernel_ptr<OP, 256, 2, false, true, 4>(smem, threads);
+      }
+      if (block_n == 128) return kernel_ptr<OP, 128, 6, false, true>(smem, threads);
+      if (block_n == 256) return kernel_ptr<OP, 256, 4, false, true>(smem, threads);
     }
     return nullptr;
   }
   if (swap) {
-    if (block_n == 16) return kernel_ptr<OP, 16, 8, true, false>(smem);
-    if (block_n == 32) return kernel_ptr<OP, 32, 8, true, false>(smem);
-    if (block_n == 64) return kernel_ptr<OP, 64, 8, true, false>(smem);
+    if (block_n == 16) return kernel_ptr<OP, 16, 8, true, false>(smem, threads);
+    if (block_n == 32) return kernel_ptr<OP, 32, 8, true, false>(smem, threads);
+    if (block_n == 64) return kernel_ptr<OP, 64, 8, true, false>(smem, threads);
     return nullptr;
   }
-  if (block_n == 64) return kernel_ptr<OP, 64, 8, false, false>(smem);
-  if (block_n == 128) return kernel_ptr<OP, 128, 6, false, false>(smem);
-  if (block_n == 256) return kernel_ptr<OP, 256, 4, false, false>(smem);
+  if (multi_wave) {
+    if (block_n == 64) return kernel_ptr<OP, 64, 4, false, false, 4>(smem, threads);
+    if (block_n == 128) return kernel_ptr<OP, 128, 3, false, false, 4>(smem, threads);
+    if (block_n == 256) return kernel_ptr<OP, 256, 2, false, false, 4>(smem, threads);
+  }
+  if (block_n == 64) return kernel_ptr<OP, 64, 8, false, false>(smem, threads);
+  if (block_n == 128) return kernel_ptr<OP, 128, 6, false, false>(smem, threads);
+  if (block_n == 256) return kernel_ptr<OP, 256, 4, false, false>(smem, threads);
   return nullptr;
 }
 
@@ -139,12 +150,17 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   }
   if (swap && q.M > block_n) return kPi05ErrInvalidValue;
 
-  int smem = 0;
+  // more output tiles than SMs: two shallow-ring CTAs per SM overlap epilogue and main loop
+  const long long tiles_planned = (long long)((swap ? q.N : q.M) + 127) / 128 *
+                                  (((swap ? q.M : q.N) + block_n - 1) / block_n) * q.nb0 * q.nb1;
+  const bool multi_wave = q.force_two_per_sm >= 0 ? q.force_two_per_sm != 0 : tiles_planned > 148;
+  int smem = 0, threads = 0;
   const void* kernel = nullptr;
-  if (q.op == kOpBf16) kernel = select_kernel<kOpBf16>(block_n, swap, q.b_mn_major, &smem);
-  if (q.op == kOpE4m3) kernel = select_kernel<kOpE4m3>(block_n, swap, q.b_mn_major, &smem);
-  if (q.op == kOpS8) kernel = select_kernel<kOpS8>(block_n, swap, q.b_mn_major, &smem);
+  if (q.op == kOpBf16) kernel = select_kernel<kOpBf16>(block_n, swap, q.b_mn_major, multi_wave, &smem, &threads);
+  if (q.op == kOpE4m3) kernel = select_kernel<kOpE4m3>(block_n, swap, q.b_mn_major, multi_wave, &smem, &threads);
+  if (q.op == kOpS8) kernel = select_kernel<kOpS8>(block_n, swap, q.b_mn_major, multi_wave, &smem, &threads);
   if (kernel == nullptr) return kPi05ErrUnsupported;
+  plan->threads = threads;
 
   // A-side map = the operand with 128-row tiles.
   int rc;
@@ -237,7 +253,7 @@ cudaError_t gemm_plan_launch(const GemmPlan& plan, cudaStream_t stream) {
                    const_cast<GemmParams*>(&plan.params)};
   cudaLaunchConfig_t config = {};
   config.gridDim = plan.grid;
-  config.blockDim = dim3(kGemmThreads);
+  config.blockDim = dim3(plan.threads);
   config.dynamicSmemBytes = plan.smem_bytes;
   config.stream = stream;
   cudaLaunchAttribute attribute[1];

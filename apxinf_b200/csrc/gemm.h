@@ -58,6 +58,7 @@ struct GemmProblem {
   // tuning overrides (0 / -1 = automatic)
   int force_swap = -1;
   int force_block_n = 0;
+  int force_two_per_sm = -1;  // -1 auto, 0 = one deep-ring CTA per SM, 1 = two shallow-ring CTAs
 };
 
 struct GemmPlan {
@@ -66,6 +67,7 @@ struct GemmPlan {
   GemmParams params;
   dim3 grid;
   int smem_bytes = 0;
+  int threads = 0;
   const void* kernel = nullptr;
   bool swap = false;
   int block_n = 0;

@@ -100,9 +100,14 @@ __device__ __forceinline__ float round_bf16(float x) {
   return __bfloat162float(__float2bfloat16(x));
 }
 
+// gelu_tanh(x) = 0.5 x (1 + tanh(u)), u = 0.79788456 (x + 0.044715 x^3)
+// (crates/apxinf-cuda/kernels/custom/math.cuh:8-12), with tanh(u) = 1 - 2 / (1 + e^{2u})
+// on the fast exponential: a few 1e-7 of relative error, far below one bf16 ulp.
 __device__ __forceinline__ float gelu_tanh_f(float value) {
   constexpr float kAlpha = 0.7978845608028654f;
-  return 0.5f * value * (1.0f + tanhf(kAlpha * (value + 0.044715f * value * value * value)));
+  const float u = kAlpha * (value + 0.044715f * value * value * value);
+  const float t = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));
+  return 0.5f * value * (1.0f + t);
 }
 
 __device__ __forceinline__ float silu_f(float value) { return value / (1.0f + expf(-value)); }
@@ -136,7 +141,11 @@ struct OpTraits<kOpS8> {
   static constexpr uint32_t kCFormat = 2;  // s32
 };
 
-constexpr int kGemmThreads = 192;
+// TMA warp + MMA warp + EPI_WARPS epilogue warps. Single-wave launches use 8 epilogue warps
+// and a deep ring with one CTA per SM; multi-wave launches use 4 epilogue warps and a
+// shallow ring so that two CTAs share an SM and one tile's epilogue runs under the other's
+// main loop.
+__host__ __device__ constexpr int gemm_threads(int epi_warps) { return 64 + 32 * epi_warps; }
 constexpr int kTileRowsA = 128;
 constexpr int kStageABytes = kTileRowsA * 128;
 
@@ -162,13 +171,13 @@ __device__ __forceinline__ float acc_to_float(uint32_t raw) {
   }
 }
 
-// One output element. `v` = scaled accumulator, `bias` / `gate` = per-column
-// values (0 when absent: adding 0 changes nothing), `extra` = residual or
-// position-embedding element.
+// One output element before its final rounding (the store converts once).
+// `v` = scaled accumulator, `bias` / `gate` = per-column values (0 when absent),
+// `extra` = residual or position-embedding element.
 template <int MODE>
 __device__ __forceinline__ float epi_apply(float v, float bias, float extra, float gate) {
   if constexpr (MODE == kEpiStore) {
-    return round_bf16(round_bf16(v) + bias);
+    return round_bf16(v) + bias;
   } else if constexpr (MODE == kEpiBiasGelu) {
     return gelu_tanh_f(round_bf16(v) + bias);
   } else if constexpr (MODE == kEpiBiasSilu) {
@@ -262,6 +271,18 @@ __device__ __forceinline__ void load_row16(const __nv_bfloat16* src, int valid, 
   }
 }
 
+// 16 consecutive floats from shared memory with four 16-byte loads.
+__device__ __forceinline__ void lds16(const float* src, float (&x)[16]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float4 v = reinterpret_cast<const float4*>(src)[q];
+    x[4 * q] = v.x;
+    x[4 * q + 1] = v.y;
+    x[4 * q + 2] = v.z;
+    x[4 * q + 3] = v.w;
+  }
+}
+
 // Where the epilogue reads the accumulator from: this CTA's TMEM (one split) or
 // the sum over all splits' partial tiles in global memory, added in split order
 // so the result does not depend on which split arrived last.
@@ -314,23 +335,25 @@ struct AccSource {
   }
 };
 
-// Thread = one output row, TMEM columns = output columns.
-template <int OP, int BLOCK_N, int MODE>
-__device__ __forceinline__ void epilogue_normal(const GemmParams& p, const AccSource<OP, BLOCK_N>& acc, int r,
-                                                int tile_b, long long out_base, float sr,
+// Thread = one output row, TMEM columns = output columns. The two warps that share a
+// TMEM lane quarter take alternate 16-column chunks (`half` = 0 / 1).
+template <int OP, int BLOCK_N, int MODE, int HALVES>
+__device__ __forceinline__ void epilogue_normal(const GemmParams& p,
+                                                const AccSource<OP, BLOCK_N>& acc, int r,
+                                                int tile_b, long long out_base, float sr, int half,
                                                 const float* s_scale, const float* s_bias,
-                                                const float* s_gate, long long t_entry = 0,
-                                                bool tracing = false) {
+                                                const float* s_gate) {
   constexpr bool kExtra =
       MODE == kEpiBiasResidual || MODE == kEpiBiasPos || MODE == kEpiGateResidual;
   const bool row_ok = r < p.rows_a;
+  const bool has_scale = p.col_scale != nullptr;
   const __nv_bfloat16* extra_row = nullptr;
   if (kExtra && row_ok) {
     extra_row = MODE == kEpiBiasPos ? p.pos + (long long)(r % p.pos_rows) * p.pos_ld
                                     : p.residual + out_base + (long long)r * p.ldc;
   }
-#pragma unroll 2
-  for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
+#pragma unroll 1
+  for (int cc = half; cc < BLOCK_N / 16; cc += HALVES) {
     uint32_t raw[16];
     acc.load16(cc * 16, raw);
     const int c0 = tile_b * BLOCK_N + cc * 16;
@@ -342,8 +365,15 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p, const AccSo
 #pragma unroll
       for (int t = 0; t < 16; ++t) extra[t] = 0.0f;
     }
+    float bias[16], gate[16];
+    lds16(s_bias + cc * 16, bias);
+    if constexpr (MODE == kEpiGateResidual) {
+      lds16(s_gate + cc * 16, gate);
+    } else {
+#pragma unroll
+      for (int t = 0; t < 16; ++t) gate[t] = 0.0f;
+    }
     acc.wait();
-    if (tracing && cc == 0) p.trace[6] = static_cast<unsigned int>(clock64() - t_entry);
     if (valid <= 0) continue;
     const long long index = out_base + (long long)r * p.ldc + c0;
     if (p.out_type == kOutS32) {
@@ -356,29 +386,33 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p, const AccSo
     }
     float o[16];
 #pragma unroll
-    for (int t = 0; t < 16; ++t) {
-      const int j = cc * 16 + t;
-      const float v = acc_to_float<OP>(raw[t]) * sr * s_scale[j];
-      o[t] = p.out_type == kOutF32 ? v : epi_apply<MODE>(v, s_bias[j], extra[t], s_gate[j]);
+    for (int t = 0; t < 16; ++t) o[t] = acc_to_float<OP>(raw[t]) * sr;
+    if (has_scale) {
+      float scale[16];
+      lds16(s_scale + cc * 16, scale);
+#pragma unroll
+      for (int t = 0; t < 16; ++t) o[t] *= scale[t];
+    }
+    if (p.out_type != kOutF32) {
+#pragma unroll
+      for (int t = 0; t < 16; ++t) o[t] = epi_apply<MODE>(o[t], bias[t], extra[t], gate[t]);
     }
     store_chunk16(p, index, valid, o);
-    if (tracing && cc == 0) p.trace[7] = static_cast<unsigned int>(clock64() - t_entry);
   }
 }
 
 // Thread = one output column (weight row), TMEM columns = output rows.
-template <int OP, int BLOCK_N, int MODE>
-__device__ __forceinline__ void epilogue_swapped(const GemmParams& p, const AccSource<OP, BLOCK_N>& acc, int c,
-                                                 int tile_b, long long out_base,
+template <int OP, int BLOCK_N, int MODE, int HALVES>
+__device__ __forceinline__ void epilogue_swapped(const GemmParams& p,
+                                                 const AccSource<OP, BLOCK_N>& acc, int c,
+                                                 int tile_b, long long out_base, int half,
+                                                 float sc, float bias, float gate,
                                                  const float* s_rowscale) {
   constexpr bool kExtra =
       MODE == kEpiBiasResidual || MODE == kEpiBiasPos || MODE == kEpiGateResidual;
   const bool col_ok = c < p.rows_a;
-  const float sc = p.col_scale != nullptr && col_ok ? p.col_scale[c] : 1.0f;
-  const float bias = p.bias != nullptr && col_ok ? __bfloat162float(p.bias[c]) : 0.0f;
-  const float gate = p.gate != nullptr && col_ok ? __bfloat162float(p.gate[c]) : 0.0f;
-#pragma unroll
-  for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
+#pragma unroll 1
+  for (int cc = half; cc < BLOCK_N / 16; cc += HALVES) {
     uint32_t raw[16];
     acc.load16(cc * 16, raw);
     const int r0 = tile_b * BLOCK_N + cc * 16;
@@ -394,6 +428,8 @@ __device__ __forceinline__ void epilogue_swapped(const GemmParams& p, const AccS
                        : __bfloat162float(p.residual[out_base + (long long)r * p.ldc + c]);
       }
     }
+    float rs[16];
+    lds16(s_rowscale + cc * 16, rs);
     acc.wait();
     if (valid <= 0) continue;
 #pragma unroll
@@ -403,7 +439,7 @@ __device__ __forceinline__ void epilogue_swapped(const GemmParams& p, const AccS
         if (p.out_type == kOutS32) {
           reinterpret_cast<int*>(p.out)[index] = static_cast<int>(raw[t]);
         } else {
-          const float v = acc_to_float<OP>(raw[t]) * s_rowscale[cc * 16 + t] * sc;
+          const float v = acc_to_float<OP>(raw[t]) * rs[t] * sc;
           const float o = p.out_type == kOutF32 ? v : epi_apply<MODE>(v, bias, extra[t], gate);
           store_one(p, index, o);
         }
@@ -412,19 +448,26 @@ __device__ __forceinline__ void epilogue_swapped(const GemmParams& p, const AccS
   }
 }
 
-template <int OP, int BLOCK_N, int STAGES, bool SWAP, bool B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int OP, int BLOCK_N, int STAGES, bool SWAP, bool B_MN, int EPI_WARPS>
+__global__ void __launch_bounds__(gemm_threads(EPI_WARPS), EPI_WARPS == 4 ? 2 : 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   using T = OpTraits<OP>;
   static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 256, "bad BLOCK_N");
   static_assert(!B_MN || (OP == kOpBf16 && BLOCK_N % 64 == 0 && !SWAP), "MN-major B: bf16 only");
+  static_assert(EPI_WARPS == 4 || EPI_WARPS == 8, "4 or 8 epilogue warps");
+  constexpr int kHalves = EPI_WARPS / 4;
+  constexpr int kEpilogueThreads = 32 * EPI_WARPS;
   constexpr int kBlockK = 128 / T::kElemBytes;  // elements per 128-byte K block
   constexpr int kStageBBytes = BLOCK_N * 128;
   constexpr int kStageBytes = kStageABytes + kStageBBytes;
   constexpr uint32_t kTmemCols = tmem_cols_for(BLOCK_N);
   constexpr uint32_t kIdesc =
       ptx::make_idesc(T::kCFormat, T::kFormat, T::kFormat, 0, B_MN ? 1 : 0, 128, BLOCK_N);
+
+  pdl_launch_dependents();
+  const long long t_entry = clock64();
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -437,9 +480,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   float* s_bias = s_scale + 256;
   float* s_gate = s_bias + 256;
 
-  pdl_launch_dependents();
-  const long long t_entry = clock64();
-  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tile_a = blockIdx.x;
@@ -558,8 +598,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (tracing) p.trace[2] = static_cast<unsigned int>(clock64() - t_entry);
     }
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
-    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    // ---------------- epilogue (warps 2..9) ----------------
+    const int quarter = warp & 3;           // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;       // which of the quarter's two warps
     const int row_in_tile = quarter * 32 + lane;
     const int ep_tid = threadIdx.x - 64;
     const int gi = tile_a * kTileRowsA + row_in_tile;  // index on the 128-row side
@@ -567,20 +608,26 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const float* row_scale =
         p.row_scale != nullptr ? p.row_scale + (long long)b0 * p.row_scale_sb0 : nullptr;
 
-    // Stage the per-column (normal) or per-row (swapped) vectors of this tile
-    // in shared memory while the main loop runs.
+    // Per-column vectors of this tile (weights-side, static) go to shared memory while the
+    // main loop runs; anything an earlier kernel wrote is read after the dependency wait.
+    float sw_scale = 1.0f, sw_bias = 0.0f, sw_gate = 0.0f;
     if constexpr (!SWAP) {
-      for (int j = ep_tid; j < BLOCK_N; j += 128) {
+      for (int j = ep_tid; j < BLOCK_N; j += kEpilogueThreads) {
         const int idx = tile_b * BLOCK_N + j;
         const bool in = idx < p.rows_b;
         s_scale[j] = p.col_scale != nullptr && in ? p.col_scale[idx] : 1.0f;
         s_bias[j] = p.bias != nullptr && in ? __bfloat162float(p.bias[idx]) : 0.0f;
         s_gate[j] = p.gate != nullptr && in ? __bfloat162float(p.gate[idx]) : 0.0f;
       }
+    } else {
+      const bool in = gi < p.rows_a;
+      sw_scale = p.col_scale != nullptr && in ? p.col_scale[gi] : 1.0f;
+      sw_bias = p.bias != nullptr && in ? __bfloat162float(p.bias[gi]) : 0.0f;
+      sw_gate = p.gate != nullptr && in ? __bfloat162float(p.gate[gi]) : 0.0f;
     }
     pdl_wait();  // everything below may read what earlier kernels of the stream wrote
     if constexpr (SWAP) {
-      for (int j = ep_tid; j < BLOCK_N; j += 128) {
+      for (int j = ep_tid; j < BLOCK_N; j += kEpilogueThreads) {
         const int idx = tile_b * BLOCK_N + j;
         const bool in = idx < p.rows_b;
         s_scale[j] = p.alpha * (row_scale != nullptr && in ? row_scale[idx] : 1.0f);
@@ -590,7 +637,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if constexpr (!SWAP) {
       if (row_scale != nullptr && gi < p.rows_a) sr = p.alpha * row_scale[gi];
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
 
     const bool ok = ptx::mbar_wait(accum_bar, 0);
     if (!ok && lane == 0) atomicCAS(p.status, 0, kGemmTimeoutEpilogue);
@@ -601,12 +648,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     AccSource<OP, BLOCK_N> acc{taddr_row, nullptr, 0, 1};
     bool run_epilogue = true;
     if (p.split_k > 1) {
-      const long long tile_id =
-          ((long long)batch * gridDim.y + tile_b) * gridDim.x + tile_a;
+      const long long tile_id = ((long long)batch * gridDim.y + tile_b) * gridDim.x + tile_a;
       uint32_t* tile_ws = p.partials + tile_id * p.split_k * (128LL * BLOCK_N);
       uint32_t* mine = tile_ws + (long long)split * (128LL * BLOCK_N) + row_in_tile * BLOCK_N;
-#pragma unroll
-      for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
+#pragma unroll 1
+      for (int cc = half; cc < BLOCK_N / 16; cc += kHalves) {
         uint32_t raw[16];
         ptx::tmem_ld_16(taddr_row + cc * 16, raw);
         ptx::tmem_ld_wait();
@@ -617,10 +663,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
       __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
       int* flag = reinterpret_cast<int*>(tmem_slot + 1);
       if (ep_tid == 0) *flag = atomicAdd(&p.tile_counters[tile_id], 1);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
       run_epilogue = *flag == p.split_k - 1;
       if (run_epilogue) {
         __threadfence();
@@ -637,68 +683,87 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if constexpr (!SWAP) {
         // columns [128t, 128t+64) gate, [128t+64, 128t+128) up; thread-local.
 #pragma unroll 1
-        for (int pair = 0; pair < BLOCK_N / 128; ++pair) {
-#pragma unroll 2
-          for (int sub = 0; sub < 4; ++sub) {
-            uint32_t rg[16], ru[16];
-            acc.load16(pair * 128 + sub * 16, rg);
-            acc.load16(pair * 128 + 64 + sub * 16, ru);
-            acc.wait();
-            const int jg = pair * 128 + sub * 16;
-            const int cg = tile_b * BLOCK_N + jg;         // packed gate column
-            const int oc = (cg / 128) * 64 + (cg % 128);  // output column
-            float o[16];
+        for (int it = half; it < BLOCK_N / 32; it += kHalves) {
+          const int pair = it >> 2, sub = it & 3;
+          uint32_t rg[16], ru[16];
+          acc.load16(pair * 128 + sub * 16, rg);
+          acc.load16(pair * 128 + 64 + sub * 16, ru);
+          const int jg = pair * 128 + sub * 16;
+          float sg[16], su[16];
+          lds16(s_scale + jg, sg);
+          lds16(s_scale + jg + 64, su);
+          acc.wait();
+          const int cg = tile_b * BLOCK_N + jg;         // packed gate column
+          const int oc = (cg / 128) * 64 + (cg % 128);  // output column
+          float o[16];
 #pragma unroll
-            for (int t = 0; t < 16; ++t) {
-              const float g = round_bf16(acc_to_float<OP>(rg[t]) * sr * s_scale[jg + t]);
-              const float u = round_bf16(acc_to_float<OP>(ru[t]) * sr * s_scale[jg + 64 + t]);
-              o[t] = gelu_tanh_f(g) * u;
-            }
-            if (gi < p.rows_a && cg < p.rows_b) {
-              store_chunk16(p, out_base + (long long)gi * p.ldc + oc, 16, o);
-            }
+          for (int t = 0; t < 16; ++t) {
+            const float g = round_bf16(acc_to_float<OP>(rg[t]) * sr * sg[t]);
+            const float u = round_bf16(acc_to_float<OP>(ru[t]) * sr * su[t]);
+            o[t] = gelu_tanh_f(g) * u;
+          }
+          if (gi < p.rows_a && cg < p.rows_b) {
+            store_chunk16(p, out_base + (long long)gi * p.ldc + oc, 16, o);
           }
         }
       } else {
-        // lanes [0,64) hold gate features, lanes [64,128) the matching up
-        // features; the up half goes through shared memory (stage 0 is idle
-        // once the accumulator barrier has fired).
+        // lanes [0,64) hold gate features, lanes [64,128) the matching up features; the up
+        // half goes through shared memory (stage 0 is idle once the accumulator is ready).
         float* xchg = reinterpret_cast<float*>(smem);  // [BLOCK_N][64]
-        const float sc = p.col_scale != nullptr && gi < p.rows_a ? p.col_scale[gi] : 1.0f;
-        float vals[BLOCK_N];
+        constexpr int kMine = (BLOCK_N / 16 + kHalves - 1) / kHalves;  // 16-column chunks per warp
+        float vals[kMine * 16];
 #pragma unroll
-        for (int cc = 0; cc < BLOCK_N / 16; ++cc) {
-          uint32_t raw[16];
-          acc.load16(cc * 16, raw);
-          acc.wait();
+        for (int i = 0; i < kMine; ++i) {
+          const int cc = half + kHalves * i;
+          if (cc * 16 < BLOCK_N) {
+            uint32_t raw[16];
+            acc.load16(cc * 16, raw);
+            float rs[16];
+            lds16(s_scale + cc * 16, rs);
+            acc.wait();
 #pragma unroll
-          for (int t = 0; t < 16; ++t) {
-            vals[cc * 16 + t] =
-                round_bf16(acc_to_float<OP>(raw[t]) * s_scale[cc * 16 + t] * sc);
+            for (int t = 0; t < 16; ++t) {
+              vals[i * 16 + t] = round_bf16(acc_to_float<OP>(raw[t]) * rs[t] * sw_scale);
+            }
           }
         }
         if (row_in_tile >= 64) {
 #pragma unroll
-          for (int j = 0; j < BLOCK_N; ++j) xchg[j * 64 + (row_in_tile - 64)] = vals[j];
+          for (int i = 0; i < kMine; ++i) {
+            const int cc = half + kHalves * i;
+            if (cc * 16 < BLOCK_N) {
+#pragma unroll
+              for (int t = 0; t < 16; ++t) {
+                xchg[(cc * 16 + t) * 64 + (row_in_tile - 64)] = vals[i * 16 + t];
+              }
+            }
+          }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
         if (row_in_tile < 64 && gi < p.rows_a) {
           const int oc = tile_a * 64 + row_in_tile;
 #pragma unroll
-          for (int j = 0; j < BLOCK_N; ++j) {
-            const int r = tile_b * BLOCK_N + j;
-            if (r < p.rows_b) {
-              const float o = gelu_tanh_f(vals[j]) * xchg[j * 64 + row_in_tile];
-              store_one(p, out_base + (long long)r * p.ldc + oc, o);
+          for (int i = 0; i < kMine; ++i) {
+            const int cc = half + kHalves * i;
+            if (cc * 16 < BLOCK_N) {
+#pragma unroll
+              for (int t = 0; t < 16; ++t) {
+                const int j = cc * 16 + t;
+                const int r = tile_b * BLOCK_N + j;
+                if (r < p.rows_b) {
+                  const float o = gelu_tanh_f(vals[i * 16 + t]) * xchg[j * 64 + row_in_tile];
+                  store_one(p, out_base + (long long)r * p.ldc + oc, o);
+                }
+              }
             }
           }
         }
       }
     } else if constexpr (!SWAP) {
-#define PI05_EPI_CASE(MODE)                                                                      \
-  case MODE:                                                                                     \
-    epilogue_normal<OP, BLOCK_N, MODE>(p, acc, gi, tile_b, out_base, sr, s_scale, s_bias,       \
-                                       s_gate, t_entry, tracing && ep_tid == 0);                                                  \
+#define PI05_EPI_CASE(MODE)                                                                       \
+  case MODE:                                                                                      \
+    epilogue_normal<OP, BLOCK_N, MODE, kHalves>(p, acc, gi, tile_b, out_base, sr, half, s_scale,  \
+                                                s_bias, s_gate);                                  \
     break;
       switch (p.mode) {
         PI05_EPI_CASE(kEpiStore)
@@ -712,9 +777,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
 #undef PI05_EPI_CASE
     } else {
-#define PI05_EPI_CASE(MODE)                                                               \
-  case MODE:                                                                              \
-    epilogue_swapped<OP, BLOCK_N, MODE>(p, acc, gi, tile_b, out_base, s_scale);           \
+#define PI05_EPI_CASE(MODE)                                                                      \
+  case MODE:                                                                                     \
+    epilogue_swapped<OP, BLOCK_N, MODE, kHalves>(p, acc, gi, tile_b, out_base, half, sw_scale,   \
+                                                 sw_bias, sw_gate, s_scale);                      \
     break;
       switch (p.mode) {
         PI05_EPI_CASE(kEpiStore)
