@@ -59,6 +59,7 @@ extern "C" int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream) {
   q.max_tiles = args->max_tiles;
   q.force_split_k = args->force_split_k;
   q.trace = args->trace;
+  q.b_blocked = args->b_blocked != 0;
   GemmPlan plan;
   const int rc = gemm_plan_build(q, &plan);
   if (rc != kPi05Ok) return rc;

@@ -121,6 +121,7 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   if (q.mode == kEpiGateResidual && q.gate == nullptr) return kPi05ErrInvalidValue;
   if (q.mode == kEpiBiasPos && (q.pos == nullptr || q.pos_rows <= 0)) return kPi05ErrInvalidValue;
   if (q.b_mn_major && q.op != kOpBf16) return kPi05ErrUnsupported;
+  if (q.b_blocked && (q.b_mn_major || q.nb0 * q.nb1 != 1)) return kPi05ErrUnsupported;
 
   const int es = elem_bytes(q.op);
   const int block_k = 128 / es;
@@ -133,6 +134,9 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
     } else if (q.b_mn_major) {
       block_n = q.N > 128 ? 256 : 128;
     } else {
+      // Measured on B200: a 128-row tcgen05.mma takes ~140 cycles whatever its N, so narrow
+      // tiles cost MMA time but buy CTAs. Up to two CTAs share an SM (296 slots): use the
+      // widest tile that still fills them, and 256 once there is more than a wave anyway.
       const long long tiles_m = (q.M + 127) / 128;
       const long long batches = (long long)q.nb0 * q.nb1;
       const long long tiles256 = tiles_m * ((q.N + 255) / 256) * batches;
@@ -171,14 +175,22 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
     if (q.b_mn_major) {
       rc = encode_map(&plan->tmap_b, q.op, q.b.ptr, q.N, q.K, q.nb0, q.nb1, q.b.ld, q.b.sb0,
                       q.b.sb1, 64, 64);
+    } else if (q.b_blocked) {
+      rc = encode_map(&plan->tmap_b, q.op, q.b.ptr, block_k, q.N, (q.K + block_k - 1) / block_k, 1,
+                      block_k, (long long)q.N * block_k, 0, block_k, block_n);
     } else {
       rc = encode_map(&plan->tmap_b, q.op, q.b.ptr, q.K, q.N, q.nb0, q.nb1, q.b.ld, q.b.sb0,
                       q.b.sb1, block_k, block_n);
     }
     if (rc != kPi05Ok) return rc;
   } else {
-    rc = encode_map(&plan->tmap_a, q.op, q.b.ptr, q.K, q.N, q.nb0, q.nb1, q.b.ld, q.b.sb0, q.b.sb1,
-                    block_k, 128);
+    if (q.b_blocked) {
+      rc = encode_map(&plan->tmap_a, q.op, q.b.ptr, block_k, q.N, (q.K + block_k - 1) / block_k, 1,
+                      block_k, (long long)q.N * block_k, 0, block_k, 128);
+    } else {
+      rc = encode_map(&plan->tmap_a, q.op, q.b.ptr, q.K, q.N, q.nb0, q.nb1, q.b.ld, q.b.sb0,
+                      q.b.sb1, block_k, 128);
+    }
     if (rc != kPi05Ok) return rc;
     rc = encode_map(&plan->tmap_b, q.op, q.a.ptr, q.K, q.M, q.nb0, q.nb1, q.a.ld, q.a.sb0, q.a.sb1,
                     block_k, block_n);
@@ -220,6 +232,7 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
       // weight streaming for a handful of rows: spread the K range until ~one CTA per SM
       if (p.num_kb >= 4) split = static_cast<int>(std::min<long long>(p.num_kb / 2, 148 / tiles));
     } else if (tiles <= 100 && p.num_kb >= 32) {
+      // wide tiles make the last-arrival reduction expensive: only for long K ranges
       split = static_cast<int>(std::min<long long>(p.num_kb / 8, 296 / tiles));
     }
     split = std::max(1, std::min(split, p.num_kb));
@@ -239,6 +252,8 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   p.trace = q.trace;
   p.static_a = (swap && q.b_static) ? 1 : 0;
   p.static_b = (!swap && q.b_static) ? 1 : 0;
+  p.blocked_a = (swap && q.b_blocked) ? 1 : 0;
+  p.blocked_b = (!swap && q.b_blocked) ? 1 : 0;
   plan->split_k = split;
   plan->grid = dim3(tiles_x, tiles_y, q.nb0 * q.nb1 * split);
   plan->smem_bytes = smem;

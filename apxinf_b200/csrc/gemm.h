@@ -55,6 +55,8 @@ struct GemmProblem {
   unsigned int* trace = nullptr;  // optional device uint32[6], see GemmParams::trace
   // the b operand is a weight matrix no kernel of the stream writes (enables early TMA loads)
   bool b_static = false;
+  // b (weights) is stored K-block-major: [ceil(K / kb)][N][kb] with kb = 128 bytes of K
+  bool b_blocked = false;
   // tuning overrides (0 / -1 = automatic)
   int force_swap = -1;
   int force_block_n = 0;

@@ -95,6 +95,7 @@ extern "C" int pi05_gemm_static_scratch(const Pi05GemmArgs* args, void* cuda_str
   q.force_block_n = args->force_block_n;
   q.force_split_k = args->force_split_k;
   q.trace = args->trace;
+  q.b_blocked = args->b_blocked != 0;
   q.partials = scratch->partials;
   q.partials_bytes = PI05_STATIC_SCRATCH_BYTES;
   q.tile_counters = scratch->counters;

@@ -94,6 +94,9 @@ struct GemmParams {
   // operands that no kernel of the stream writes (weights): their TMA loads may be issued
   // before the programmatic-dependency wait
   int static_a, static_b;
+  // operand stored K-block-major ([K/128B][rows][128 B]): every TMA box is one contiguous
+  // 128-row x 128-byte run; its map is {128 B, rows, k-blocks}
+  int blocked_a, blocked_b;
 };
 
 __device__ __forceinline__ float round_bf16(float x) {
@@ -154,8 +157,12 @@ __host__ __device__ constexpr int gemm_smem_bytes(int block_n, int stages) {
   return stages * gemm_stage_bytes(block_n) + 1024 /*alignment slack*/ + 512 /*barriers*/ +
          3 * 256 * 4 /*epilogue vectors*/;
 }
+// (Measured: rotating over several accumulators does not shorten the ~140-cycle issue
+// interval of 128-row MMAs, so one accumulator per tile is used.)
+__host__ __device__ constexpr int accumulators_for(int block_n) { return block_n > 0 ? 1 : 1; }
 __host__ __device__ constexpr uint32_t tmem_cols_for(int block_n) {
-  return block_n <= 32 ? 32u : block_n <= 64 ? 64u : block_n <= 128 ? 128u : 256u;
+  const int cols = block_n * accumulators_for(block_n);
+  return cols <= 32 ? 32u : cols <= 64 ? 64u : cols <= 128 ? 128u : cols <= 256 ? 256u : 512u;
 }
 
 // ---------------------------------------------------------------------------
@@ -288,6 +295,7 @@ __device__ __forceinline__ void lds16(const float* src, float (&x)[16]) {
 // so the result does not depend on which split arrived last.
 template <int OP, int BLOCK_N>
 struct AccSource {
+  static constexpr int kAccs = accumulators_for(BLOCK_N);
   uint32_t taddr_row;
   const uint32_t* partial_row;  // this thread's row in split 0, or null
   long long split_stride;       // elements between splits
@@ -296,6 +304,24 @@ struct AccSource {
   __device__ __forceinline__ void load16(int col0, uint32_t (&raw)[16]) const {
     if (partial_row == nullptr) {
       ptx::tmem_ld_16(taddr_row + col0, raw);
+      if constexpr (kAccs > 1) {
+        // successive MMAs rotate over kAccs independent accumulators; add them up here
+        uint32_t more[kAccs - 1][16];
+#pragma unroll
+        for (int a = 1; a < kAccs; ++a) ptx::tmem_ld_16(taddr_row + a * BLOCK_N + col0, more[a - 1]);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int a = 1; a < kAccs; ++a) {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            if constexpr (OP == kOpS8) {
+              raw[t] = static_cast<uint32_t>(static_cast<int>(raw[t]) + static_cast<int>(more[a - 1][t]));
+            } else {
+              raw[t] = __float_as_uint(__uint_as_float(raw[t]) + __uint_as_float(more[a - 1][t]));
+            }
+          }
+        }
+      }
       return;
     }
     float facc[16];
@@ -305,18 +331,32 @@ struct AccSource {
       facc[t] = 0.0f;
       iacc[t] = 0;
     }
-    for (int s = 0; s < splits; ++s) {
-      const uint4* src = reinterpret_cast<const uint4*>(partial_row + s * split_stride + col0);
+    // four splits' loads are issued together (one L2 round trip per group), then added in order
+    for (int s0 = 0; s0 < splits; s0 += 4) {
+      uint4 v[4][4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint4 v = __ldcg(src + q);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      for (int u = 0; u < 4; ++u) {
+        if (s0 + u < splits) {
+          const uint4* src =
+              reinterpret_cast<const uint4*>(partial_row + (s0 + u) * split_stride + col0);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          if constexpr (OP == kOpS8) {
-            iacc[q * 4 + e] += static_cast<int>(w[e]);
-          } else {
-            facc[q * 4 + e] += __uint_as_float(w[e]);
+          for (int q = 0; q < 4; ++q) v[u][q] = __ldcg(src + q);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (s0 + u < splits) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t w[4] = {v[u][q].x, v[u][q].y, v[u][q].z, v[u][q].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if constexpr (OP == kOpS8) {
+                iacc[q * 4 + e] += static_cast<int>(w[e]);
+              } else {
+                facc[q * 4 + e] += __uint_as_float(w[e]);
+              }
+            }
           }
         }
       }
@@ -520,8 +560,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int issued = 0;
       auto load_a = [&](int it) {
         const int s = it % STAGES;
-        ptx::tma_load_4d(smem + s * kStageBytes, &tmap_a, &full_bar[s], (kb_begin + it) * kBlockK,
-                         tile_a * kTileRowsA, b0, b1);
+        if (p.blocked_a) {
+          ptx::tma_load_4d(smem + s * kStageBytes, &tmap_a, &full_bar[s], 0, tile_a * kTileRowsA,
+                           kb_begin + it, 0);
+        } else {
+          ptx::tma_load_4d(smem + s * kStageBytes, &tmap_a, &full_bar[s],
+                           (kb_begin + it) * kBlockK, tile_a * kTileRowsA, b0, b1);
+        }
       };
       auto load_b = [&](int it) {
         const int s = it % STAGES;
@@ -533,6 +578,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::tma_load_4d(sb + chunk * 8192, &tmap_b, &full_bar[s],
                              tile_b * BLOCK_N + chunk * 64, kb * kBlockK, b0, b1);
           }
+        } else if (p.blocked_b) {
+          ptx::tma_load_4d(sb, &tmap_b, &full_bar[s], 0, tile_b * BLOCK_N, kb, 0);
         } else {
           ptx::tma_load_4d(sb, &tmap_b, &full_bar[s], kb * kBlockK, tile_b * BLOCK_N, b0, b1);
         }
@@ -588,7 +635,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint64_t adesc = ptx::make_smem_desc(a_addr + k * 32, 16, 1024);
           const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b_addr + k * 2048, 8192, 1024)
                                       : ptx::make_smem_desc(b_addr + k * 32, 16, 1024);
-          ptx::umma<T::kKind>(tmem_base, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+          constexpr int kAccs = accumulators_for(BLOCK_N);
+          const int which = k % kAccs;
+          const bool first_touch = kb == 0 && k < kAccs;
+          ptx::umma<T::kKind>(tmem_base + which * BLOCK_N, adesc, bdesc, kIdesc,
+                              first_touch ? 0u : 1u);
         }
         ptx::umma_commit(&empty_bar[s]);
       }
@@ -654,8 +705,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll 1
       for (int cc = half; cc < BLOCK_N / 16; cc += kHalves) {
         uint32_t raw[16];
-        ptx::tmem_ld_16(taddr_row + cc * 16, raw);
-        ptx::tmem_ld_wait();
+        acc.load16(cc * 16, raw);
+        acc.wait();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           __stcg(reinterpret_cast<uint4*>(mine + cc * 16) + q,

@@ -42,10 +42,14 @@ def gemm(a, b, out, *, op, mode=_lib.EPI_STORE, out_type=_lib.OUT_BF16, bias=Non
          residual=None, col_scale=None, row_scale=None, pos=None, gate=None, alpha=1.0,
          out_inv_scale=1.0, b_mn_major=False, status=None, stream=None, force_swap=-1,
          force_block_n=0, partials=None, tile_counters=None, force_split_k=0, trace=None,
-         static_scratch=False):
+         static_scratch=False, b_blocked=None):
     """out[.., M, N'] = epilogue(a[.., M, K] @ b[.., N, K]^T); see Pi05GemmArgs."""
     m, k, lda, nb0, nb1, a_sb0, a_sb1 = _operand(a)
-    if b_mn_major:
+    if b_blocked is not None:
+        # b is [ceil(K / kb), N, kb]; the logical (N, K) comes with it
+        n, kb = b_blocked
+        ldb, b_sb0, b_sb1 = 0, 0, 0
+    elif b_mn_major:
         kb, n, ldb, _, _, b_sb0, b_sb1 = _operand(b)
     else:
         n, kb, ldb, _, _, b_sb0, b_sb1 = _operand(b)
@@ -69,7 +73,8 @@ def gemm(a, b, out, *, op, mode=_lib.EPI_STORE, out_type=_lib.OUT_BF16, bias=Non
         partials_bytes=(partials.numel() * partials.element_size() if partials is not None else 0),
         tile_counters=_ptr(tile_counters),
         max_tiles=(tile_counters.numel() if tile_counters is not None else 0),
-        force_split_k=force_split_k, trace=_ptr(trace))
+        force_split_k=force_split_k, trace=_ptr(trace),
+        b_blocked=int(b_blocked is not None))
     if static_scratch:
         check(lib().pi05_gemm_static_scratch(C.byref(args), _stream_ptr(stream)),
               "pi05_gemm_static_scratch")

@@ -94,6 +94,10 @@ typedef struct Pi05GemmArgs {
    * done, first operands landed, last MMA issued, accumulator ready, epilogue done, TMEM
    * freed}. NULL = off. */
   uint32_t* trace;
+  /* != 0: `b` is stored K-block-major, [ceil(k / kb)][n][kb] with kb = 128 bytes of K (64 bf16
+   * or 128 one-byte elements, the tail block zero padded), so each tile load is one
+   * contiguous run; ldb and the batch strides of b are ignored. */
+  int32_t b_blocked;
 } Pi05GemmArgs;
 
 int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream);
