@@ -336,6 +336,32 @@ __global__ void patchify_kernel(PatchifyArgs a) {
   }
 }
 
+// One thread per output element, for unpadded rows (ld not a multiple of 8).
+__global__ void patchify_scalar_kernel(PatchifyArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int side = a.image_size / a.patch_size;
+  const int area = a.patch_size * a.patch_size;
+  const int patch_width = 3 * area;
+  const long long total = (long long)a.n_images * side * side * patch_width;
+  const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= total) return;
+  const int col = static_cast<int>(index % patch_width);
+  const long long prow = index / patch_width;
+  const int image = static_cast<int>(prow / (side * side));
+  const int in_image = static_cast<int>(prow - (long long)image * side * side);
+  const int py = in_image / side, px = in_image - py * side;
+  const int channel = col / area;
+  const int pixel = col - channel * area;
+  const int dy = pixel / a.patch_size, dx = pixel - dy * a.patch_size;
+  const int yy = py * a.patch_size + dy, xx = px * a.patch_size + dx;
+  const long long src =
+      a.nchw ? (((long long)image * 3 + channel) * a.image_size + yy) * a.image_size + xx
+             : (((long long)image * a.image_size + yy) * a.image_size + xx) * 3 + channel;
+  const float value = (static_cast<float>(a.images[src]) / 255.0f) * 2.0f - 1.0f;
+  reinterpret_cast<__nv_bfloat16*>(a.patches)[prow * a.ld + col] = __float2bfloat16(value);
+}
+
 __global__ void embedding_kernel(const __nv_bfloat16* table, const uint32_t* ids,
                                  __nv_bfloat16* out, int batch, int tokens, int width, int vocab,
                                  int out_rows_per_batch, int row_offset) {
@@ -471,11 +497,16 @@ cudaError_t launch_softmax(void* scores, int rows_per_batch, int batches, long l
 cudaError_t launch_patchify(const PatchifyArgs& a, cudaStream_t stream) {
   if (a.images == nullptr || a.patches == nullptr || a.n_images <= 0 || a.image_size <= 0 ||
       a.patch_size <= 0 || a.image_size % a.patch_size != 0 ||
-      a.ld < 3 * a.patch_size * a.patch_size || (a.ld & 15) != 0 ||
-      (a.out != kRowBf16 && a.out != kRowE4m3)) {
+      a.ld < 3 * a.patch_size * a.patch_size || (a.out != kRowBf16 && a.out != kRowE4m3)) {
     return cudaErrorInvalidValue;
   }
   const int side = a.image_size / a.patch_size;
+  if ((a.ld & 15) != 0) {
+    if (a.out != kRowBf16) return cudaErrorInvalidValue;
+    const long long count = (long long)a.n_images * side * side * 3 * a.patch_size * a.patch_size;
+    return launch_pdl(patchify_scalar_kernel, dim3(static_cast<unsigned>((count + 255) / 256)),
+                      dim3(256), 0, stream, a);
+  }
   const long long total = (long long)a.n_images * side * side * (a.ld >> 3);
   const int threads = 256;
   const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);

@@ -11,16 +11,18 @@ ROOT = Path(__file__).resolve().parent.parent
 
 
 def _declared_symbols():
-    text = (ROOT / "include" / "pi05_b200.h").read_text()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(pi05_[a-z0-9_]+)\s*\(", text)))
+    names = set()
+    for header in sorted((ROOT / "include").glob("*.h")):
+        text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
+        names.update(re.findall(r"\b((?:pi05|apxinf_static)_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_library_exports_every_declared_symbol():
     from apxinf_b200 import lib
     handle = lib()
     names = _declared_symbols()
-    assert len(names) >= 20
+    assert len(names) >= 30 and any(n.startswith("apxinf_static_") for n in names)
     for name in names:
         assert hasattr(handle, name), f"{name} declared in include/pi05_b200.h but not exported"
     assert handle.pi05_version().startswith(b"pi05_b200 sm_100a")
