@@ -170,6 +170,20 @@ class CpuSample:
         return vision_s + prefix_s + action_s
 
 
+def cpu_block_cfg1():
+    """BASELINE configuration 1: one Gemma-style decoder block (522 tokens, hidden 2048, 8 query
+    heads / 1 KV head, head_dim 256, GeGLU 16384, causal) on the reference's CPU operators
+    (naive single-threaded f32 sgemm), restated in C under oracle/. Timed on 4 tokens and scaled
+    to 522 (the GEMMs, >99% of the work, are linear in tokens)."""
+    from oracle import cpu_block
+    tokens = 4
+    case = cpu_block.make_case(0, seq=tokens, hidden=2048, heads=8, kv_heads=1, head_dim=256, mlp=16384)
+    _, seconds = cpu_block.run_c(case, 8, 1, 256)
+    full = seconds / tokens * 522
+    return {"seconds_per_block": full, "gflops": 117.0 / full, "cores": 1, "kind": "port",
+            "sample": f"{tokens} of 522 tokens timed ({seconds:.2f} s), scaled linearly"}
+
+
 def run_reference_arm(args):
     rank, world, _ = dist_env()
     if rank != 0:
@@ -325,6 +339,7 @@ def run_ours(args):
             seconds = min(cpu.seconds() for _ in range(2))
             line["cpu_baseline"] = {"value": 1.0 / seconds, "unit": UNIT, "cores": cpu.threads,
                                     "kind": "port", "sample": cpu.sample}
+            line["cpu_block_cfg1"] = cpu_block_cfg1()
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line), flush=True)
