@@ -86,7 +86,7 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
 
 // 4-D tiled load global -> shared, completion signalled on `bar` as bytes.
 // Coordinate 0 is the innermost (contiguous) one and must land on a 16-byte
-// boundary; no multicast is used anywhere in this library.
+// boundary; every CTA issues its own loads (cluster size 1).
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
                                             int c0, int c1, int c2, int c3) {
   asm volatile(
