@@ -75,15 +75,36 @@ const void* kernel_ptr(int* smem, int* threads) {
   return reinterpret_cast<const void*>(kernel);
 }
 
+template <int OP, int BLOCK_N, int STAGES, bool B_MN>
+const void* persistent_ptr(int* smem, int* threads) {
+  auto kernel = &gemm_umma_persistent_kernel<OP, BLOCK_N, STAGES, B_MN>;
+  *threads = gemm_threads(8);
+  *smem = gemm_smem_bytes(BLOCK_N, STAGES);
+  cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       gemm_smem_bytes(BLOCK_N, STAGES));
+  return reinterpret_cast<const void*>(kernel);
+}
+
+template <int OP>
+const void* select_persistent(int block_n, bool b_mn, int* smem, int* threads) {
+  if (b_mn) {
+    if constexpr (OP == kOpBf16) {
+      if (block_n == 128) return persistent_ptr<OP, 128, 6, true>(smem, threads);
+      if (block_n == 256) return persistent_ptr<OP, 256, 4, true>(smem, threads);
+    }
+    return nullptr;
+  }
+  if (block_n == 64) return persistent_ptr<OP, 64, 8, false>(smem, threads);
+  if (block_n == 128) return persistent_ptr<OP, 128, 6, false>(smem, threads);
+  if (block_n == 256) return persistent_ptr<OP, 256, 4, false>(smem, threads);
+  return nullptr;
+}
+
 template <int OP>
 const void* select_kernel(int block_n, bool swap, bool b_mn, bool multi_wave, int* smem,
                           int* threads) {
   if (b_mn) {
     if constexpr (OP == kOpBf16) {
-      if (multi_wave) {
-        if (block_n == 128) return kernel_ptr<OP, 128, 3, false, true, 4>(smem, threads);
-        if (block_n == 256) return kernel_ptr<OP, 256, 2, false, true, 4>(smem, threads);
-      }
       if (block_n == 128) return kernel_ptr<OP, 128, 6, false, true>(smem, threads);
       if (block_n == 256) return kernel_ptr<OP, 256, 4, false, true>(smem, threads);
     }
@@ -94,11 +115,6 @@ const void* select_kernel(int block_n, bool swap, bool b_mn, bool multi_wave, in
     if (block_n == 32) return kernel_ptr<OP, 32, 8, true, false>(smem, threads);
     if (block_n == 64) return kernel_ptr<OP, 64, 8, true, false>(smem, threads);
     return nullptr;
-  }
-  if (multi_wave) {
-    if (block_n == 64) return kernel_ptr<OP, 64, 4, false, false, 4>(smem, threads);
-    if (block_n == 128) return kernel_ptr<OP, 128, 3, false, false, 4>(smem, threads);
-    if (block_n == 256) return kernel_ptr<OP, 256, 2, false, false, 4>(smem, threads);
   }
   if (block_n == 64) return kernel_ptr<OP, 64, 8, false, false>(smem, threads);
   if (block_n == 128) return kernel_ptr<OP, 128, 6, false, false>(smem, threads);
@@ -165,6 +181,8 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   if (q.op == kOpS8) kernel = select_kernel<kOpS8>(block_n, swap, q.b_mn_major, multi_wave, &smem, &threads);
   if (kernel == nullptr) return kPi05ErrUnsupported;
   plan->threads = threads;
+  plan->persistent = false;
+  plan->multi_wave_candidate = multi_wave && !swap;
 
   // A-side map = the operand with 128-row tiles.
   int rc;
@@ -256,6 +274,26 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   p.blocked_b = (!swap && q.b_blocked) ? 1 : 0;
   plan->split_k = split;
   plan->grid = dim3(tiles_x, tiles_y, q.nb0 * q.nb1 * split);
+  if (plan->multi_wave_candidate && split == 1 && q.trace == nullptr) {
+    const void* persistent = nullptr;
+    if (q.op == kOpBf16) persistent = select_persistent<kOpBf16>(block_n, q.b_mn_major, &smem, &threads);
+    if (q.op == kOpE4m3) persistent = select_persistent<kOpE4m3>(block_n, q.b_mn_major, &smem, &threads);
+    if (q.op == kOpS8) persistent = select_persistent<kOpS8>(block_n, q.b_mn_major, &smem, &threads);
+    if (persistent != nullptr) {
+      kernel = persistent;
+      plan->persistent = true;
+      plan->threads = threads;
+      plan->tiles_a = tiles_x;
+      plan->tiles_b = tiles_y;
+      plan->total_tiles = static_cast<int>(tiles);
+      int sms = 148;
+      int device = 0;
+      if (cudaGetDevice(&device) == cudaSuccess) {
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+      }
+      plan->grid = dim3(static_cast<unsigned>(std::min<long long>(tiles, sms)), 1, 1);
+    }
+  }
   plan->smem_bytes = smem;
   plan->kernel = kernel;
   plan->swap = swap;
@@ -264,8 +302,9 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
 }
 
 cudaError_t gemm_plan_launch(const GemmPlan& plan, cudaStream_t stream) {
-  void* args[3] = {const_cast<CUtensorMap*>(&plan.tmap_a), const_cast<CUtensorMap*>(&plan.tmap_b),
-                   const_cast<GemmParams*>(&plan.params)};
+  void* args[6] = {const_cast<CUtensorMap*>(&plan.tmap_a), const_cast<CUtensorMap*>(&plan.tmap_b),
+                   const_cast<GemmParams*>(&plan.params), const_cast<int*>(&plan.tiles_a),
+                   const_cast<int*>(&plan.tiles_b), const_cast<int*>(&plan.total_tiles)};
   cudaLaunchConfig_t config = {};
   config.gridDim = plan.grid;
   config.blockDim = dim3(plan.threads);

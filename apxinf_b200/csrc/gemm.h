@@ -74,6 +74,9 @@ struct GemmPlan {
   bool swap = false;
   int block_n = 0;
   int split_k = 1;
+  bool persistent = false;  // one CTA per SM walking tiles, double-buffered accumulator
+  bool multi_wave_candidate = false;
+  int tiles_a = 0, tiles_b = 0, total_tiles = 0;
 };
 
 // Error codes of this library's C ABI (negative = rejected before launch).

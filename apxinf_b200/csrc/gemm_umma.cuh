@@ -155,7 +155,7 @@ constexpr int kStageABytes = kTileRowsA * 128;
 __host__ __device__ constexpr int gemm_stage_bytes(int block_n) { return kStageABytes + block_n * 128; }
 __host__ __device__ constexpr int gemm_smem_bytes(int block_n, int stages) {
   return stages * gemm_stage_bytes(block_n) + 1024 /*alignment slack*/ + 512 /*barriers*/ +
-         3 * 256 * 4 /*epilogue vectors*/;
+         2 * 3 * 256 * 4 /*epilogue vectors (double-buffered in the persistent kernel)*/;
 }
 // (Measured: rotating over several accumulators does not shorten the ~140-cycle issue
 // interval of 128-row MMAs, so one accumulator per tile is used.)
@@ -438,6 +438,39 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
       for (int t = 0; t < 16; ++t) o[t] = epi_apply<MODE>(o[t], bias[t], extra[t], gate[t]);
     }
     store_chunk16(p, index, valid, o);
+  }
+}
+
+// GeGLU epilogue, thread = one output row: packed columns [128t, 128t+64) are gate features,
+// [128t+64, 128t+128) the matching up features.
+template <int OP, int BLOCK_N, int HALVES>
+__device__ __forceinline__ void epilogue_geglu_normal(const GemmParams& p,
+                                                      const AccSource<OP, BLOCK_N>& acc, int r,
+                                                      int tile_b, long long out_base, float sr,
+                                                      int half, const float* s_scale) {
+#pragma unroll 1
+  for (int it = half; it < BLOCK_N / 32; it += HALVES) {
+    const int pair = it >> 2, sub = it & 3;
+    uint32_t rg[16], ru[16];
+    acc.load16(pair * 128 + sub * 16, rg);
+    acc.load16(pair * 128 + 64 + sub * 16, ru);
+    const int jg = pair * 128 + sub * 16;
+    float sg[16], su[16];
+    lds16(s_scale + jg, sg);
+    lds16(s_scale + jg + 64, su);
+    acc.wait();
+    const int cg = tile_b * BLOCK_N + jg;         // packed gate column
+    const int oc = (cg / 128) * 64 + (cg % 128);  // output column
+    float o[16];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const float g = round_bf16(acc_to_float<OP>(rg[t]) * sr * sg[t]);
+      const float u = round_bf16(acc_to_float<OP>(ru[t]) * sr * su[t]);
+      o[t] = gelu_tanh_f(g) * u;
+    }
+    if (r < p.rows_a && cg < p.rows_b) {
+      store_chunk16(p, out_base + (long long)r * p.ldc + oc, 16, o);
+    }
   }
 }
 
@@ -732,31 +765,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // another split finishes this tile
     } else if (p.mode == kEpiGeglu) {
       if constexpr (!SWAP) {
-        // columns [128t, 128t+64) gate, [128t+64, 128t+128) up; thread-local.
-#pragma unroll 1
-        for (int it = half; it < BLOCK_N / 32; it += kHalves) {
-          const int pair = it >> 2, sub = it & 3;
-          uint32_t rg[16], ru[16];
-          acc.load16(pair * 128 + sub * 16, rg);
-          acc.load16(pair * 128 + 64 + sub * 16, ru);
-          const int jg = pair * 128 + sub * 16;
-          float sg[16], su[16];
-          lds16(s_scale + jg, sg);
-          lds16(s_scale + jg + 64, su);
-          acc.wait();
-          const int cg = tile_b * BLOCK_N + jg;         // packed gate column
-          const int oc = (cg / 128) * 64 + (cg % 128);  // output column
-          float o[16];
-#pragma unroll
-          for (int t = 0; t < 16; ++t) {
-            const float g = round_bf16(acc_to_float<OP>(rg[t]) * sr * sg[t]);
-            const float u = round_bf16(acc_to_float<OP>(ru[t]) * sr * su[t]);
-            o[t] = gelu_tanh_f(g) * u;
-          }
-          if (gi < p.rows_a && cg < p.rows_b) {
-            store_chunk16(p, out_base + (long long)gi * p.ldc + oc, 16, o);
-          }
-        }
+        epilogue_geglu_normal<OP, BLOCK_N, kHalves>(p, acc, gi, tile_b, out_base, sr, half, s_scale);
       } else {
         // lanes [0,64) hold gate features, lanes [64,128) the matching up features; the up
         // half goes through shared memory (stage 0 is idle once the accumulator is ready).
@@ -854,6 +863,214 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
     if (tracing && lane == 0) p.trace[5] = static_cast<unsigned int>(clock64() - t_entry);
+  }
+}
+
+
+// ---------------------------------------------------------------------------
+// Persistent variant for launches with more output tiles than SMs: one CTA per SM walks
+// tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the accumulator is double-buffered in TMEM
+// (2 x BLOCK_N columns), so the 8 epilogue warps drain tile i while the MMA warp already
+// works on tile i+1 and the TMA warp runs ahead through the shared-memory ring.
+// Normal orientation only (activations on the 128-row side), no split-K.
+// ---------------------------------------------------------------------------
+template <int OP, int BLOCK_N, int STAGES, bool B_MN>
+__global__ void __launch_bounds__(gemm_threads(8), 1)
+gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                            const __grid_constant__ CUtensorMap tmap_b, const GemmParams p,
+                            const int tiles_a, const int tiles_b, const int total_tiles) {
+  using T = OpTraits<OP>;
+  static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 256, "bad BLOCK_N");
+  constexpr int kEpilogueThreads = 256;
+  constexpr int kBlockK = 128 / T::kElemBytes;
+  constexpr int kStageBBytes = BLOCK_N * 128;
+  constexpr int kStageBytes = kStageABytes + kStageBBytes;
+  constexpr uint32_t kTmemCols = 2 * BLOCK_N <= 32    ? 32u
+                                 : 2 * BLOCK_N <= 64  ? 64u
+                                 : 2 * BLOCK_N <= 128 ? 128u
+                                 : 2 * BLOCK_N <= 256 ? 256u
+                                                      : 512u;
+  constexpr uint32_t kIdesc =
+      ptx::make_idesc(T::kCFormat, T::kFormat, T::kFormat, 0, B_MN ? 1 : 0, 128, BLOCK_N);
+
+  pdl_launch_dependents();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  float* s_vectors = reinterpret_cast<float*>(smem + STAGES * kStageBytes + 512);  // [2][3][256]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int my_tiles = (total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                       static_cast<int>(gridDim.x);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&acc_full[b], 1);
+      ptx::mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+    }
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  auto decode = [&](int local, int* ta, int* tb, int* b0, int* b1) {
+    const int tile = static_cast<int>(blockIdx.x) + local * static_cast<int>(gridDim.x);
+    *ta = tile % tiles_a;
+    const int rest = tile / tiles_a;
+    *tb = rest % tiles_b;
+    const int batch = rest / tiles_b;
+    *b0 = batch % p.nb0;
+    *b1 = batch / p.nb0;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tmap_a);
+      ptx::prefetch_tensormap(&tmap_b);
+      bool ok = true;
+      long long it = 0;
+      for (int local = 0; local < my_tiles && ok; ++local) {
+        int ta, tb, b0, b1;
+        decode(local, &ta, &tb, &b0, &b1);
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const int s = static_cast<int>(it % STAGES);
+          const long long round = it / STAGES;
+          if (round > 0) ok = ptx::mbar_wait(&empty_bar[s], static_cast<uint32_t>((round - 1) & 1));
+          if (!ok) break;
+          uint8_t* sa = smem + s * kStageBytes;
+          uint8_t* sb = sa + kStageABytes;
+          ptx::mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+          ptx::tma_load_4d(sa, &tmap_a, &full_bar[s], kb * kBlockK, ta * kTileRowsA, b0, b1);
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int chunk = 0; chunk < BLOCK_N / 64; ++chunk) {
+              ptx::tma_load_4d(sb + chunk * 8192, &tmap_b, &full_bar[s], tb * BLOCK_N + chunk * 64,
+                               kb * kBlockK, b0, b1);
+            }
+          } else if (p.blocked_b) {
+            ptx::tma_load_4d(sb, &tmap_b, &full_bar[s], 0, tb * BLOCK_N, kb, 0);
+          } else {
+            ptx::tma_load_4d(sb, &tmap_b, &full_bar[s], kb * kBlockK, tb * BLOCK_N, b0, b1);
+          }
+        }
+      }
+      if (!ok) atomicCAS(p.status, 0, kGemmTimeoutProducer);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      long long it = 0;
+      for (int local = 0; local < my_tiles; ++local) {
+        const int buf = local & 1;
+        if (ok && local >= 2) {
+          ok = ptx::mbar_wait(&acc_empty[buf], static_cast<uint32_t>(((local >> 1) - 1) & 1));
+          ptx::tc_fence_after();
+        }
+        for (int kb = 0; kb < p.num_kb && ok; ++kb, ++it) {
+          const int s = static_cast<int>(it % STAGES);
+          ok = ptx::mbar_wait(&full_bar[s], static_cast<uint32_t>((it / STAGES) & 1));
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const uint32_t a_addr = ptx::smem_u32(smem + s * kStageBytes);
+          const uint32_t b_addr = a_addr + kStageABytes;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t adesc = ptx::make_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b_addr + k * 2048, 8192, 1024)
+                                        : ptx::make_smem_desc(b_addr + k * 32, 16, 1024);
+            ptx::umma<T::kKind>(tmem_base + buf * BLOCK_N, adesc, bdesc, kIdesc,
+                                (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(&empty_bar[s]);
+        }
+        // signal the epilogue even after a timeout so that it never waits on a dead pipeline
+        ptx::umma_commit(&acc_full[buf]);
+      }
+      if (!ok) atomicCAS(p.status, 0, kGemmTimeoutMma);
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row_in_tile = quarter * 32 + lane;
+    const int ep_tid = threadIdx.x - 64;
+    for (int local = 0; local < my_tiles; ++local) {
+      const int buf = local & 1;
+      int ta, tb, b0, b1;
+      decode(local, &ta, &tb, &b0, &b1);
+      float* s_scale = s_vectors + buf * 768;
+      float* s_bias = s_scale + 256;
+      float* s_gate = s_bias + 256;
+      const int gi = ta * kTileRowsA + row_in_tile;
+      const long long out_base = (long long)b0 * p.out_sb0 + (long long)b1 * p.out_sb1;
+      const float* row_scale =
+          p.row_scale != nullptr ? p.row_scale + (long long)b0 * p.row_scale_sb0 : nullptr;
+      for (int j = ep_tid; j < BLOCK_N; j += kEpilogueThreads) {
+        const int idx = tb * BLOCK_N + j;
+        const bool in = idx < p.rows_b;
+        s_scale[j] = p.col_scale != nullptr && in ? p.col_scale[idx] : 1.0f;
+        s_bias[j] = p.bias != nullptr && in ? __bfloat162float(p.bias[idx]) : 0.0f;
+        s_gate[j] = p.gate != nullptr && in ? __bfloat162float(p.gate[idx]) : 0.0f;
+      }
+      float sr = p.alpha;
+      if (row_scale != nullptr && gi < p.rows_a) sr = p.alpha * row_scale[gi];
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
+
+      const bool ok = ptx::mbar_wait(&acc_full[buf], static_cast<uint32_t>((local >> 1) & 1));
+      if (!ok && lane == 0) atomicCAS(p.status, 0, kGemmTimeoutEpilogue);
+      ptx::tc_fence_after();
+      const uint32_t taddr_row =
+          tmem_base + buf * BLOCK_N + (static_cast<uint32_t>(quarter * 32) << 16);
+      AccSource<OP, BLOCK_N> acc{taddr_row, nullptr, 0, 1};
+      if (p.mode == kEpiGeglu) {
+        epilogue_geglu_normal<OP, BLOCK_N, 2>(p, acc, gi, tb, out_base, sr, half, s_scale);
+      } else {
+#define PI05_EPI_CASE(MODE)                                                                     \
+  case MODE:                                                                                    \
+    epilogue_normal<OP, BLOCK_N, MODE, 2>(p, acc, gi, tb, out_base, sr, half, s_scale, s_bias,  \
+                                          s_gate);                                              \
+    break;
+        switch (p.mode) {
+          PI05_EPI_CASE(kEpiStore)
+          PI05_EPI_CASE(kEpiBiasGelu)
+          PI05_EPI_CASE(kEpiBiasSilu)
+          PI05_EPI_CASE(kEpiBiasResidual)
+          PI05_EPI_CASE(kEpiBiasPos)
+          PI05_EPI_CASE(kEpiGateResidual)
+          default:
+            break;
+        }
+#undef PI05_EPI_CASE
+      }
+      // this warp has read everything it needs from the accumulator buffer
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
