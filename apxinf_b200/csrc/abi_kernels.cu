@@ -2,6 +2,7 @@
 #include <string>
 
 #include "../../include/pi05_b200.h"
+#include "fmha.h"
 #include "gemm.h"
 
 namespace pi05 {
@@ -64,4 +65,25 @@ extern "C" int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream) {
   const int rc = gemm_plan_build(q, &plan);
   if (rc != kPi05Ok) return rc;
   return record_cuda(gemm_plan_launch(plan, static_cast<cudaStream_t>(cuda_stream)));
+}
+
+extern "C" int pi05_attention(const Pi05AttentionArgs* args, void* cuda_stream) {
+  using namespace pi05;
+  if (args == nullptr) return kPi05ErrInvalidValue;
+  FmhaProblem f;
+  f.q = args->q; f.q_ld = args->q_ld; f.q_sb0 = args->q_sb0; f.q_sb1 = args->q_sb1;
+  f.k = args->k; f.k_ld = args->k_ld; f.k_sb0 = args->k_sb0; f.k_sb1 = args->k_sb1;
+  f.v = args->v; f.v_ld = args->v_ld; f.v_sb0 = args->v_sb0; f.v_sb1 = args->v_sb1;
+  f.out = args->out; f.out_ld = args->out_ld; f.out_sb0 = args->out_sb0; f.out_sb1 = args->out_sb1;
+  f.q_rows = args->q_rows; f.keys = args->keys; f.head_dim = args->head_dim;
+  f.nb0 = args->nb0; f.nb1 = args->nb1;
+  f.scale = args->scale;
+  f.out_e4m3 = args->out_e4m3 != 0;
+  f.out_inv_scale = args->out_inv_scale;
+  f.status = args->status;
+  f.trace = reinterpret_cast<unsigned int*>(args->trace);
+  FmhaPlan plan;
+  const int rc = fmha_plan_build(f, &plan);
+  if (rc != kPi05Ok) return rc;
+  return record_cuda(fmha_plan_launch(plan, static_cast<cudaStream_t>(cuda_stream)));
 }

@@ -49,6 +49,14 @@ long long round_up(long long v, long long m) { return (v + m - 1) / m * m; }
 
 }  // namespace
 
+namespace {
+cudaError_t launch_op(const Op& op, cudaStream_t stream) {
+  if (op.is_gemm) return gemm_plan_launch(op.plan, stream);
+  if (op.is_fmha) return fmha_plan_launch(op.fmha, stream);
+  return op.launch(stream);
+}
+}  // namespace
+
 int ModelConfig::validate() const {
   const bool ok =
       action_dim > 0 && action_dim % 8 == 0 && action_horizon > 0 && action_horizon <= 64 &&
@@ -411,6 +419,41 @@ int PreparedGraph::attention(const char* name, const void* q, long long q_ld, lo
                              long long v_sb1, int q_rows, int keys, int head_dim, int nb0, int nb1,
                              float scale, void* logits, Act* out, long long out_ld,
                              long long out_sb0, long long out_sb1) {
+  const int prec_now = e_->precision();
+  // the fused kernel gives one CTA per 128 query rows: with only a few of them (the B=1
+  // action expert) the three-launch path, which spreads keys over more CTAs, is quicker
+  const long long fused_ctas = (long long)((q_rows + 127) / 128) * nb0 * nb1;
+  if (fmha_supported(q_rows, keys, head_dim) && fused_ctas >= 8) {
+    if (!measuring_) {
+      FmhaProblem f;
+      f.q = q; f.q_ld = q_ld; f.q_sb0 = q_sb0; f.q_sb1 = q_sb1;
+      f.k = k; f.k_ld = k_ld; f.k_sb0 = k_sb0; f.k_sb1 = k_sb1;
+      f.v = v; f.v_ld = v_ld; f.v_sb0 = v_sb0; f.v_sb1 = v_sb1;
+      f.out = prec_now == kPrecInt8 ? out->wide : out->data;
+      f.out_ld = out_ld; f.out_sb0 = out_sb0; f.out_sb1 = out_sb1;
+      f.q_rows = q_rows; f.keys = keys; f.head_dim = head_dim; f.nb0 = nb0; f.nb1 = nb1;
+      f.scale = scale;
+      f.out_e4m3 = prec_now == kPrecFp8;
+      f.out_inv_scale = 1.0f / e_->act_scale();
+      f.status = e_->status();
+      Op op;
+      op.name = name;
+      op.stage = stage_;
+      op.is_fmha = true;
+      PI05_TRY(fmha_plan_build(f, &op.fmha));
+      ops_.push_back(std::move(op));
+    }
+    if (prec_now == kPrecInt8) {
+      const void* wide = out->wide;
+      int8_t* data = static_cast<int8_t*>(out->data);
+      float* rs = out->row_scale;
+      const int rows = out->rows, cols = static_cast<int>(out->ld);
+      add_kernel("quantize_rows_int8", [=](cudaStream_t st) {
+        return launch_quantize_rows_int8(wide, data, rs, rows, cols, cols, cols, st);
+      });
+    }
+    return kPi05Ok;
+  }
   const long long ld_s = round_up(keys, 8);
   const long long s_sb0 = static_cast<long long>(q_rows) * ld_s;
   const long long s_sb1 = s_sb0 * nb0;
@@ -761,11 +804,7 @@ int PreparedGraph::prepare() {
 int PreparedGraph::run_eager() {
   PI05_CUDA(cudaSetDevice(e_->device()));
   for (const Op& op : ops_) {
-    if (op.is_gemm) {
-      PI05_CUDA(gemm_plan_launch(op.plan, e_->stream()));
-    } else {
-      PI05_CUDA(op.launch(e_->stream()));
-    }
+    PI05_CUDA(launch_op(op, e_->stream()));
   }
   return kPi05Ok;
 }
@@ -854,7 +893,7 @@ int PreparedGraph::stage_times(float* ms3) {
   int rc = kPi05Ok;
   for (const Op& op : ops_) {
     while (op.stage > stage && stage < 2) cudaEventRecord(ev[++stage], e_->stream());
-    const cudaError_t err = op.is_gemm ? gemm_plan_launch(op.plan, e_->stream()) : op.launch(e_->stream());
+    const cudaError_t err = launch_op(op, e_->stream());
     if (err != cudaSuccess) {
       rc = record_cuda(err);
       break;
@@ -887,8 +926,7 @@ int PreparedGraph::time_launches(const char* name, float* mean_ms, int* count) {
       events.push_back(b);
       cudaEventRecord(a, e_->stream());
     }
-    const cudaError_t err =
-        op.is_gemm ? gemm_plan_launch(op.plan, e_->stream()) : op.launch(e_->stream());
+    const cudaError_t err = launch_op(op, e_->stream());
     if (timed) cudaEventRecord(events.back(), e_->stream());
     if (err != cudaSuccess) {
       rc = record_cuda(err);

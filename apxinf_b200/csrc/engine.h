@@ -19,6 +19,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "fmha.h"
 #include "gemm.h"
 
 namespace pi05 {
@@ -68,6 +69,8 @@ struct Op {
   int stage = 0;
   bool is_gemm = false;
   GemmPlan plan;
+  bool is_fmha = false;
+  FmhaPlan fmha;
   std::function<cudaError_t(cudaStream_t)> launch;
 };
 

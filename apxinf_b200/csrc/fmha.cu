@@ -1,0 +1,59 @@
+#include "fmha.h"
+
+#include <algorithm>
+
+#include "fmha_umma.cuh"
+
+namespace pi05 {
+
+bool fmha_supported(int q_rows, int keys, int head_dim) {
+  return q_rows > 0 && keys > 0 && keys <= 1024 && head_dim >= 16 && head_dim <= 256 &&
+         head_dim % 8 == 0;
+}
+
+int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
+  if (plan == nullptr || q.q == nullptr || q.k == nullptr || q.v == nullptr || q.out == nullptr ||
+      q.status == nullptr || q.nb0 <= 0 || q.nb1 <= 0 || 
+      !fmha_supported(q.q_rows, q.keys, q.head_dim)) {
+    return kPi05ErrInvalidValue;
+  }
+  int rc = encode_operand_map(&plan->tmap_q, kOpBf16, q.q, q.head_dim, q.q_rows, q.nb0, q.nb1, q.q_ld,
+                              q.q_sb0, q.q_sb1, 64, 128);
+  if (rc != kPi05Ok) return rc;
+  rc = encode_operand_map(&plan->tmap_k, kOpBf16, q.k, q.head_dim, q.keys, q.nb0, q.nb1, q.k_ld,
+                          q.k_sb0, q.k_sb1, 64, 256);
+  if (rc != kPi05Ok) return rc;
+  rc = encode_operand_map(&plan->tmap_v, kOpBf16, q.v, q.head_dim, q.keys, q.nb0, q.nb1, q.v_ld,
+                          q.v_sb0, q.v_sb1, 64, 64);
+  if (rc != kPi05Ok) return rc;
+  FmhaParams& p = plan->params;
+  p.q_rows = q.q_rows;
+  p.keys = q.keys;
+  p.head_dim = q.head_dim;
+  p.nb0 = q.nb0;
+  p.nb1 = q.nb1;
+  p.scale = q.scale;
+  p.out = q.out;
+  p.out_ld = q.out_ld;
+  p.out_sb0 = q.out_sb0;
+  p.out_sb1 = q.out_sb1;
+  p.out_e4m3 = q.out_e4m3 ? 1 : 0;
+  p.out_inv_scale = q.out_inv_scale;
+  p.status = q.status;
+  p.trace = q.trace;
+  const long long items = (long long)((q.q_rows + 127) / 128) * q.nb0 * q.nb1;
+  int sms = 148, device = 0;
+  if (cudaGetDevice(&device) == cudaSuccess) {
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  }
+  plan->grid = dim3(static_cast<unsigned>(std::min<long long>(items, sms)), 1, 1);
+  cudaFuncSetAttribute(fmha_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFmhaSmemBytes);
+  return kPi05Ok;
+}
+
+cudaError_t fmha_plan_launch(const FmhaPlan& plan, cudaStream_t stream) {
+  return launch_pdl(fmha_umma_kernel, plan.grid, dim3(kFmhaThreads), kFmhaSmemBytes, stream,
+                    plan.tmap_q, plan.tmap_k, plan.tmap_v, plan.params);
+}
+
+}  // namespace pi05

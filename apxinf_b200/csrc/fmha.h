@@ -1,0 +1,58 @@
+// Host side of the fused attention kernel (fmha_umma.cuh): plan = three TMA maps + parameters.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "gemm.h"
+
+namespace pi05 {
+
+enum FmhaStatus : int { kFmhaTimeout = 201 };
+
+struct FmhaParams {
+  int q_rows;      // query rows per batch entry
+  int keys;        // keys per batch entry (<= 1024)
+  int head_dim;    // 72, 128 or 256 (multiple of 8, <= 256)
+  int nb0, nb1;    // batch extents; work items = query tiles x nb0 x nb1
+  float scale;
+  void* out;       // [.., q_rows, head_dim] bf16 or e4m3
+  long long out_ld, out_sb0, out_sb1;
+  int out_e4m3;
+  float out_inv_scale;
+  int* status;
+  unsigned int* trace;  // optional device uint32[16]: SM-clock deltas of CTA (0,0,0) phases
+};
+
+
+// softmax(scale * q k^T) v, batched over nb0 x nb1. q [q_rows, head_dim], k and v
+// [keys, head_dim], all bf16 with contiguous head_dim; leading dimensions and batch strides in
+// elements. out [q_rows, head_dim] bf16 or e4m3 (e4m3(clamp(bf16(o) * out_inv_scale))).
+struct FmhaProblem {
+  const void* q = nullptr;
+  long long q_ld = 0, q_sb0 = 0, q_sb1 = 0;
+  const void* k = nullptr;
+  long long k_ld = 0, k_sb0 = 0, k_sb1 = 0;
+  const void* v = nullptr;
+  long long v_ld = 0, v_sb0 = 0, v_sb1 = 0;
+  void* out = nullptr;
+  long long out_ld = 0, out_sb0 = 0, out_sb1 = 0;
+  int q_rows = 0, keys = 0, head_dim = 0, nb0 = 1, nb1 = 1;
+  float scale = 1.0f;
+  bool out_e4m3 = false;
+  float out_inv_scale = 1.0f;
+  int* status = nullptr;
+  unsigned int* trace = nullptr;
+};
+
+struct FmhaPlan {
+  CUtensorMap tmap_q, tmap_k, tmap_v;
+  FmhaParams params;
+  dim3 grid;
+};
+
+bool fmha_supported(int q_rows, int keys, int head_dim);
+int fmha_plan_build(const FmhaProblem& problem, FmhaPlan* plan);
+cudaError_t fmha_plan_launch(const FmhaPlan& plan, cudaStream_t stream);
+
+}  // namespace pi05

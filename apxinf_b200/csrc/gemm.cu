@@ -36,8 +36,10 @@ EncodeTiledFn encode_tiled_fn() {
 
 int elem_bytes(int op) { return op == kOpBf16 ? 2 : 1; }
 
+}  // namespace
+
 // Rank-4 tiled map {inner, rows, b0, b1}, 128-byte swizzle, zero fill outside.
-int encode_map(CUtensorMap* map, int op, const void* ptr, uint64_t inner, uint64_t rows,
+int encode_operand_map(CUtensorMap* map, int op, const void* ptr, uint64_t inner, uint64_t rows,
                uint64_t nb0, uint64_t nb1, long long ld, long long sb0, long long sb1,
                uint32_t box_inner, uint32_t box_rows) {
   EncodeTiledFn encode = encode_tiled_fn();
@@ -63,6 +65,8 @@ int encode_map(CUtensorMap* map, int op, const void* ptr, uint64_t inner, uint64
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return result == CUDA_SUCCESS ? kPi05Ok : kPi05ErrDriver;
 }
+
+namespace {
 
 template <int OP, int BLOCK_N, int STAGES, bool SWAP, bool B_MN, int EPI_WARPS = 8>
 const void* kernel_ptr(int* smem, int* threads) {
@@ -187,30 +191,30 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   // A-side map = the operand with 128-row tiles.
   int rc;
   if (!swap) {
-    rc = encode_map(&plan->tmap_a, q.op, q.a.ptr, q.K, q.M, q.nb0, q.nb1, q.a.ld, q.a.sb0, q.a.sb1,
+    rc = encode_operand_map(&plan->tmap_a, q.op, q.a.ptr, q.K, q.M, q.nb0, q.nb1, q.a.ld, q.a.sb0, q.a.sb1,
                     block_k, 128);
     if (rc != kPi05Ok) return rc;
     if (q.b_mn_major) {
-      rc = encode_map(&plan->tmap_b, q.op, q.b.ptr, q.N, q.K, q.nb0, q.nb1, q.b.ld, q.b.sb0,
+      rc = encode_operand_map(&plan->tmap_b, q.op, q.b.ptr, q.N, q.K, q.nb0, q.nb1, q.b.ld, q.b.sb0,
                       q.b.sb1, 64, 64);
     } else if (q.b_blocked) {
-      rc = encode_map(&plan->tmap_b, q.op, q.b.ptr, block_k, q.N, (q.K + block_k - 1) / block_k, 1,
+      rc = encode_operand_map(&plan->tmap_b, q.op, q.b.ptr, block_k, q.N, (q.K + block_k - 1) / block_k, 1,
                       block_k, (long long)q.N * block_k, 0, block_k, block_n);
     } else {
-      rc = encode_map(&plan->tmap_b, q.op, q.b.ptr, q.K, q.N, q.nb0, q.nb1, q.b.ld, q.b.sb0,
+      rc = encode_operand_map(&plan->tmap_b, q.op, q.b.ptr, q.K, q.N, q.nb0, q.nb1, q.b.ld, q.b.sb0,
                       q.b.sb1, block_k, block_n);
     }
     if (rc != kPi05Ok) return rc;
   } else {
     if (q.b_blocked) {
-      rc = encode_map(&plan->tmap_a, q.op, q.b.ptr, block_k, q.N, (q.K + block_k - 1) / block_k, 1,
+      rc = encode_operand_map(&plan->tmap_a, q.op, q.b.ptr, block_k, q.N, (q.K + block_k - 1) / block_k, 1,
                       block_k, (long long)q.N * block_k, 0, block_k, 128);
     } else {
-      rc = encode_map(&plan->tmap_a, q.op, q.b.ptr, q.K, q.N, q.nb0, q.nb1, q.b.ld, q.b.sb0,
+      rc = encode_operand_map(&plan->tmap_a, q.op, q.b.ptr, q.K, q.N, q.nb0, q.nb1, q.b.ld, q.b.sb0,
                       q.b.sb1, block_k, 128);
     }
     if (rc != kPi05Ok) return rc;
-    rc = encode_map(&plan->tmap_b, q.op, q.a.ptr, q.K, q.M, q.nb0, q.nb1, q.a.ld, q.a.sb0, q.a.sb1,
+    rc = encode_operand_map(&plan->tmap_b, q.op, q.a.ptr, q.K, q.M, q.nb0, q.nb1, q.a.ld, q.a.sb0, q.a.sb1,
                     block_k, block_n);
     if (rc != kPi05Ok) return rc;
   }

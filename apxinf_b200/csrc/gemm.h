@@ -91,6 +91,12 @@ enum Pi05Error : int {
   kPi05ErrScratchLimit = -7,
 };
 
+// Rank-4 tiled TMA map {inner, rows, b0, b1} of a K-major operand (element strides),
+// 128-byte swizzle, zero fill outside the extents. `op` = OperandType.
+int encode_operand_map(CUtensorMap* map, int op, const void* ptr, uint64_t inner, uint64_t rows,
+                       uint64_t nb0, uint64_t nb1, long long ld, long long sb0, long long sb1,
+                       uint32_t box_inner, uint32_t box_rows);
+
 int gemm_plan_build(const GemmProblem& problem, GemmPlan* plan);
 cudaError_t gemm_plan_launch(const GemmPlan& plan, cudaStream_t stream);
 

@@ -131,6 +131,35 @@ int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream);
 int pi05_gemm_static_scratch(const Pi05GemmArgs* args, void* cuda_stream);
 
 
+/*
+ * Fused attention out = softmax(scale * q k^T) v on the tcgen05 tensor cores, no mask, at most
+ * 1024 keys, head_dim a multiple of 8 up to 256, batched over nb0 x nb1 (element strides).
+ * q [q_rows, head_dim], k / v [keys, head_dim] and out [q_rows, head_dim] are bf16 device
+ * matrices with contiguous head_dim; with out_e4m3 != 0 the output is
+ * e4m3(clamp(bf16(o) * out_inv_scale)). Multi-query attention passes its (token, head) pairs as
+ * query rows over the one shared K/V head. Replaces the reference attention contracts mha_bf16 /
+ * mqa_bf16 / mqa_cached_f16 (crates/apxinf-cuda/src/kernels/attention.rs:627-1261) and the FFI
+ * symbols behind them (ffi/cublas.rs:113-134, ffi/cutlass.rs:9-83, ffi/fa2.rs:9-58).
+ */
+typedef struct Pi05AttentionArgs {
+  const void* q;
+  int64_t q_ld, q_sb0, q_sb1;
+  const void* k;
+  int64_t k_ld, k_sb0, k_sb1;
+  const void* v;
+  int64_t v_ld, v_sb0, v_sb1;
+  void* out;
+  int64_t out_ld, out_sb0, out_sb1;
+  int32_t q_rows, keys, head_dim, nb0, nb1;
+  float scale;
+  int32_t out_e4m3;
+  float out_inv_scale;
+  int32_t* status; /* device int32, 0 before the call */
+  uint32_t* trace; /* optional device uint32[17]: SM-clock phase timestamps of CTA (0,0,0); NULL = off */
+} Pi05AttentionArgs;
+
+int pi05_attention(const Pi05AttentionArgs* args, void* cuda_stream);
+
 /* ------------------------------------------------------------------------- */
 /* Engine level                                                              */
 /* ------------------------------------------------------------------------- */

@@ -1,0 +1,130 @@
+"""Fused tcgen05 attention (pi05_attention) against a float64 softmax(QK^T)V on the CPU, for
+the three attention shapes of PI0.5 and ragged edge cases. Tolerance: the kernel rounds the
+scaled logits and the probabilities to bf16 as the reference's MQA does
+(crates/apxinf-cuda/adapters/cublas_adapter.cu:109-130), so outputs agree to ~1 bf16 ulp of
+the value scale; the reference's own attention test uses |err| < 0.003 on unit-scale data
+(crates/apxinf-cuda/src/tests/fp8.rs:1041-1113)."""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+class AttentionArgs(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("q_ld", C.c_int64), ("q_sb0", C.c_int64), ("q_sb1", C.c_int64),
+                ("k", C.c_void_p), ("k_ld", C.c_int64), ("k_sb0", C.c_int64), ("k_sb1", C.c_int64),
+                ("v", C.c_void_p), ("v_ld", C.c_int64), ("v_sb0", C.c_int64), ("v_sb1", C.c_int64),
+                ("out", C.c_void_p), ("out_ld", C.c_int64), ("out_sb0", C.c_int64), ("out_sb1", C.c_int64),
+                ("q_rows", C.c_int32), ("keys", C.c_int32), ("head_dim", C.c_int32),
+                ("nb0", C.c_int32), ("nb1", C.c_int32), ("scale", C.c_float),
+                ("out_e4m3", C.c_int32), ("out_inv_scale", C.c_float), ("status", C.c_void_p),
+                ("trace", C.c_void_p)]
+
+
+def run(q, k, v, out, scale, nb0=1, nb1=1, strides=None, e4m3=False, inv=1.0, trace=None):
+    """q/k/v/out: torch CUDA tensors; strides: dict name -> (ld, sb0, sb1) in elements."""
+    from apxinf_b200 import lib
+    handle = lib()
+    handle.pi05_attention.argtypes = [C.POINTER(AttentionArgs), C.c_void_p]
+    handle.pi05_attention.restype = C.c_int
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    s = strides
+    args = AttentionArgs(
+        q=q.data_ptr(), q_ld=s["q"][0], q_sb0=s["q"][1], q_sb1=s["q"][2],
+        k=k.data_ptr(), k_ld=s["k"][0], k_sb0=s["k"][1], k_sb1=s["k"][2],
+        v=v.data_ptr(), v_ld=s["v"][0], v_sb0=s["v"][1], v_sb1=s["v"][2],
+        out=out.data_ptr(), out_ld=s["o"][0], out_sb0=s["o"][1], out_sb1=s["o"][2],
+        q_rows=s["rows"], keys=s["keys"], head_dim=s["hd"], nb0=nb0, nb1=nb1, scale=scale,
+        out_e4m3=int(e4m3), out_inv_scale=inv, status=status.data_ptr(),
+        trace=(trace.data_ptr() if trace is not None else None))
+    rc = handle.pi05_attention(C.byref(args), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    return rc, int(status.item())
+
+
+def reference(q, k, v, scale):
+    s = (q.double() @ k.double().transpose(-1, -2)) * scale
+    p = torch.softmax(s, dim=-1)
+    return (p @ v.double()).float()
+
+
+@pytest.mark.parametrize("rows,keys,hd", [(80, 532, 256), (4176, 522, 256), (400, 532, 256),
+                                            (10, 37, 128), (130, 1000, 256), (7, 1, 64), (256, 256, 72)])
+def test_single_batch_shapes(rows, keys, hd):
+    gen = torch.Generator().manual_seed(rows + keys + hd)
+    q = torch.randn(rows, hd, generator=gen).to(torch.bfloat16)
+    k = torch.randn(keys, hd, generator=gen).to(torch.bfloat16)
+    v = torch.randn(keys, hd, generator=gen).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(hd)
+    out = torch.full((rows, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    rc, status = run(q.cuda(), k.cuda(), v.cuda(), out, scale,
+                     strides=dict(q=(hd, 0, 0), k=(hd, 0, 0), v=(hd, 0, 0), o=(hd, 0, 0), rows=rows, keys=keys, hd=hd))
+    assert rc == 0 and status == 0
+    want = reference(q.float(), k.float(), v.float(), scale)
+    err = (out.float().cpu() - want).abs().max().item()
+    assert err <= 0.02, err
+
+
+def test_zero_queries_average_the_values():
+    # crates/apxinf-cuda/src/tests/fp8.rs:735-778
+    rows, keys, hd = 32, 20, 256
+    q = torch.zeros(rows, hd, dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros(keys, hd, dtype=torch.bfloat16, device="cuda")
+    v = torch.arange(keys, dtype=torch.float32)[:, None].repeat(1, hd).to(torch.bfloat16).cuda()
+    out = torch.zeros(rows, hd, dtype=torch.bfloat16, device="cuda")
+    rc, status = run(q, k, v, out, 1 / 16, strides=dict(q=(hd, 0, 0), k=(hd, 0, 0), v=(hd, 0, 0), o=(hd, 0, 0), rows=rows, keys=keys, hd=hd))
+    assert rc == 0 and status == 0
+    assert (out.float() - 9.5).abs().max().item() < 0.05
+
+
+def test_siglip_layout_strided_views_and_e4m3_output():
+    """Per (image, head) attention read in place from the packed q|k|v projection."""
+    images, heads, tokens, hd = 3, 16, 256, 72
+    width = heads * hd
+    gen = torch.Generator().manual_seed(3)
+    qkv = torch.randn(images * tokens, 3 * width, generator=gen).to(torch.bfloat16)
+    d = qkv.cuda()
+    out = torch.zeros(images * tokens, width, dtype=torch.bfloat16, device="cuda")
+    scale = 1.0 / math.sqrt(hd)
+    strides = dict(q=(3 * width, hd, tokens * 3 * width), k=(3 * width, hd, tokens * 3 * width),
+                   v=(3 * width, hd, tokens * 3 * width), o=(width, hd, tokens * width),
+                   rows=tokens, keys=tokens, hd=hd)
+    rc, status = run(d, d[:, width:], d[:, 2 * width:], out, scale, nb0=heads, nb1=images, strides=strides)
+    assert rc == 0 and status == 0
+    x = qkv.float().view(images, tokens, 3, heads, hd)
+    want = reference(x[:, :, 0].permute(0, 2, 1, 3), x[:, :, 1].permute(0, 2, 1, 3),
+                     x[:, :, 2].permute(0, 2, 1, 3), scale)  # [images, heads, tokens, hd]
+    want = want.permute(0, 2, 1, 3).reshape(images * tokens, width)
+    assert (out.float().cpu() - want).abs().max().item() <= 0.02
+    out8 = torch.zeros(images * tokens, width, dtype=torch.float8_e4m3fn, device="cuda")
+    rc, status = run(d, d[:, width:], d[:, 2 * width:], out8, scale, nb0=heads, nb1=images,
+                     strides=strides, e4m3=True, inv=20.0)
+    assert rc == 0 and status == 0
+    got = out8.float().cpu() / 20.0
+    assert (got - want).abs().max().item() <= 0.02 + 0.07 * want.abs().max().item()
+
+
+def test_batched_mqa_over_a_cache_with_row_stride():
+    """Each sample attends over its own [cache_rows, 256] cache of which only `keys` rows count."""
+    batch, q_rows, keys, cache_rows, hd = 5, 80, 532, 540, 256
+    gen = torch.Generator().manual_seed(8)
+    q = torch.randn(batch, q_rows, hd, generator=gen).to(torch.bfloat16)
+    kc = torch.randn(batch, cache_rows, hd, generator=gen).to(torch.bfloat16)
+    vc = torch.randn(batch, cache_rows, hd, generator=gen).to(torch.bfloat16)
+    out = torch.zeros(batch, q_rows, hd, dtype=torch.bfloat16, device="cuda")
+    rc, status = run(q.cuda(), kc.cuda(), vc.cuda(), out, 1 / 16, nb0=batch,
+                     strides=dict(q=(hd, q_rows * hd, 0), k=(hd, cache_rows * hd, 0), v=(hd, cache_rows * hd, 0),
+                                  o=(hd, q_rows * hd, 0), rows=q_rows, keys=keys, hd=hd))
+    assert rc == 0 and status == 0
+    want = reference(q.float(), kc.float()[:, :keys], vc.float()[:, :keys], 1 / 16)
+    assert (out.float().cpu() - want).abs().max().item() <= 0.02
+
+
+def test_rejects_unsupported_shapes():
+    q = torch.zeros(16, 64, dtype=torch.bfloat16, device="cuda")
+    rc, _ = run(q, q, q, q, 1.0, strides=dict(q=(64, 0, 0), k=(64, 0, 0), v=(64, 0, 0), o=(64, 0, 0), rows=16, keys=2000, hd=64))
+    assert rc == -1
