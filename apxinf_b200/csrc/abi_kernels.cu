@@ -82,6 +82,7 @@ extern "C" int pi05_attention(const Pi05AttentionArgs* args, void* cuda_stream) 
   f.out_inv_scale = args->out_inv_scale;
   f.status = args->status;
   f.trace = reinterpret_cast<unsigned int*>(args->trace);
+  f.trace_item = args->trace_item;
   FmhaPlan plan;
   const int rc = fmha_plan_build(f, &plan);
   if (rc != kPi05Ok) return rc;

@@ -422,7 +422,9 @@ int PreparedGraph::attention(const char* name, const void* q, long long q_ld, lo
   const int prec_now = e_->precision();
   // the fused kernel gives one CTA per 128 query rows: with only a few of them (the B=1
   // action expert) the three-launch path, which spreads keys over more CTAs, is quicker
-  const long long fused_ctas = (long long)((q_rows + 127) / 128) * nb0 * nb1;
+  const bool shared_kv = nb0 > 1 && k_sb0 == 0 && v_sb0 == 0 && 128 % nb0 == 0;
+  const long long fused_ctas = shared_kv ? (long long)((q_rows * nb0 + 127) / 128) * nb1
+                                         : (long long)((q_rows + 127) / 128) * nb0 * nb1;
   if (fmha_supported(q_rows, keys, head_dim) && fused_ctas >= 8) {
     if (!measuring_) {
       FmhaProblem f;

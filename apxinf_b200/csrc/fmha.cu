@@ -17,14 +17,24 @@ int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
       !fmha_supported(q.q_rows, q.keys, q.head_dim)) {
     return kPi05ErrInvalidValue;
   }
-  int rc = encode_operand_map(&plan->tmap_q, kOpBf16, q.q, q.head_dim, q.q_rows, q.nb0, q.nb1, q.q_ld,
-                              q.q_sb0, q.q_sb1, 64, 128);
+  // multi-query attention: heads that share one K/V head are packed into the same query tile
+  const bool shared_kv = q.nb0 > 1 && q.k_sb0 == 0 && q.v_sb0 == 0 && 128 % q.nb0 == 0;
+  const int pack = shared_kv ? q.nb0 : 1;
+  int rc;
+  if (pack > 1) {
+    // dims (head_dim, head, token, nb1), box 64 x pack x 128/pack: row = token * pack + head
+    rc = encode_operand_map(&plan->tmap_q, kOpBf16, q.q, q.head_dim, q.nb0, q.q_rows, q.nb1, q.q_sb0,
+                            q.q_ld, q.q_sb1, 64, pack, 128 / pack);
+  } else {
+    rc = encode_operand_map(&plan->tmap_q, kOpBf16, q.q, q.head_dim, q.q_rows, q.nb0, q.nb1, q.q_ld,
+                            q.q_sb0, q.q_sb1, 64, 128);
+  }
   if (rc != kPi05Ok) return rc;
-  rc = encode_operand_map(&plan->tmap_k, kOpBf16, q.k, q.head_dim, q.keys, q.nb0, q.nb1, q.k_ld,
-                          q.k_sb0, q.k_sb1, 64, 256);
+  rc = encode_operand_map(&plan->tmap_k, kOpBf16, q.k, q.head_dim, q.keys, pack > 1 ? 1 : q.nb0, q.nb1,
+                          q.k_ld, q.k_sb0, q.k_sb1, 64, 256);
   if (rc != kPi05Ok) return rc;
-  rc = encode_operand_map(&plan->tmap_v, kOpBf16, q.v, q.head_dim, q.keys, q.nb0, q.nb1, q.v_ld,
-                          q.v_sb0, q.v_sb1, 64, 64);
+  rc = encode_operand_map(&plan->tmap_v, kOpBf16, q.v, q.head_dim, q.keys, pack > 1 ? 1 : q.nb0, q.nb1,
+                          q.v_ld, q.v_sb0, q.v_sb1, 64, 64);
   if (rc != kPi05Ok) return rc;
   FmhaParams& p = plan->params;
   p.q_rows = q.q_rows;
@@ -32,6 +42,7 @@ int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
   p.head_dim = q.head_dim;
   p.nb0 = q.nb0;
   p.nb1 = q.nb1;
+  p.pack = pack;
   p.scale = q.scale;
   p.out = q.out;
   p.out_ld = q.out_ld;
@@ -41,7 +52,10 @@ int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
   p.out_inv_scale = q.out_inv_scale;
   p.status = q.status;
   p.trace = q.trace;
-  const long long items = (long long)((q.q_rows + 127) / 128) * q.nb0 * q.nb1;
+  p.trace_item = q.trace_item;
+  const int tile_tokens = 128 / pack;
+  const long long items =
+      (long long)((q.q_rows + tile_tokens - 1) / tile_tokens) * (pack > 1 ? 1 : q.nb0) * q.nb1;
   int sms = 148, device = 0;
   if (cudaGetDevice(&device) == cudaSuccess) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);

@@ -15,13 +15,15 @@ struct FmhaParams {
   int keys;        // keys per batch entry (<= 1024)
   int head_dim;    // 72, 128 or 256 (multiple of 8, <= 256)
   int nb0, nb1;    // batch extents; work items = query tiles x nb0 x nb1
+  int pack;        // nb0 when all nb0 query heads share one K/V head (tiles mix heads), else 1
   float scale;
   void* out;       // [.., q_rows, head_dim] bf16 or e4m3
   long long out_ld, out_sb0, out_sb1;
   int out_e4m3;
   float out_inv_scale;
   int* status;
-  unsigned int* trace;  // optional device uint32[16]: SM-clock deltas of CTA (0,0,0) phases
+  unsigned int* trace;  // optional device uint32[32]: SM-clock phase stamps of CTA 0's trace_item-th tile
+  int trace_item;
 };
 
 
@@ -43,6 +45,7 @@ struct FmhaProblem {
   float out_inv_scale = 1.0f;
   int* status = nullptr;
   unsigned int* trace = nullptr;
+  int trace_item = 0;
 };
 
 struct FmhaPlan {

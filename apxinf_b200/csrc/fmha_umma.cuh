@@ -35,11 +35,11 @@ constexpr int kFmhaThreads = 64 + kFmhaSoftmaxThreads;
 constexpr int kFmhaKeyBlock = 256;
 constexpr int kFmhaQBytes = 4 * 16384;        // up to 4 head-dim chunks of [128 x 128 B]
 constexpr int kFmhaStageBytes = 256 * 128;    // one K chunk [256 keys x 128 B] or one V sub-block
-constexpr int kFmhaStages = 2;
+constexpr int kFmhaMaxStages = 3;  // two, plus one carved out of the query area when head_dim <= 128
 constexpr int kFmhaPBytes = 4 * 16384;        // P: 4 k-blocks of [128 rows x 64 keys]
 constexpr int kFmhaExchangeBytes = 2 * 4 * 128 * 4;  // per-row partial maxima and sums of the 4 column groups
 constexpr int kFmhaSmemBytes =
-    kFmhaQBytes + kFmhaStages * kFmhaStageBytes + kFmhaPBytes + 1024 + 256 + kFmhaExchangeBytes;
+    kFmhaQBytes + 2 * kFmhaStageBytes + kFmhaPBytes + 1024 + 256 + kFmhaExchangeBytes;
 
 __global__ void __launch_bounds__(kFmhaThreads, 1)
 fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -47,46 +47,57 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   pdl_launch_dependents();
   const long long t_entry = clock64();
   const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-#define PI05_TRACE(slot) do { if (tracing) p.trace[slot] = static_cast<unsigned int>(clock64() - t_entry); } while (0)
+#define PI05_TRACE(slot) do { if (tracing && items_done == p.trace_item) p.trace[slot] = static_cast<unsigned int>(clock64() - t_entry); } while (0)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* q_smem = smem;
-  uint8_t* ring = q_smem + kFmhaQBytes;
-  uint8_t* p_smem = ring + kFmhaStages * kFmhaStageBytes;
+  uint8_t* p_smem = q_smem + kFmhaQBytes + 2 * kFmhaStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + kFmhaPBytes);
   uint64_t* q_full = bars;          // Q tile landed
-  uint64_t* ring_full = bars + 1;   // [2]
-  uint64_t* ring_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;      // S block ready in TMEM
-  uint64_t* s_free = bars + 6;      // softmax warps done reading S (128 arrivals)
-  uint64_t* p_full = bars + 7;      // P block written (128 arrivals)
-  uint64_t* p_free = bars + 8;      // PV MMAs done reading P
-  uint64_t* o_full = bars + 9;      // output accumulator complete
-  uint64_t* q_free = bars + 10;     // every QK^T MMA of the tile has read Q
-  uint64_t* o_free = bars + 11;     // epilogue has read the output accumulator
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* ring_full = bars + 1;   // [kFmhaMaxStages]
+  uint64_t* ring_empty = bars + 4;  // [kFmhaMaxStages]
+  uint64_t* s_full = bars + 7;      // S block ready in TMEM
+  uint64_t* s_free = bars + 8;      // softmax warps done reading S
+  uint64_t* p_full = bars + 9;      // P block written
+  uint64_t* p_free = bars + 10;     // PV MMAs done reading P
+  uint64_t* o_full = bars + 11;     // output accumulator complete
+  uint64_t* q_free = bars + 12;     // every QK^T MMA of the tile has read Q
+  uint64_t* o_free = bars + 13;     // epilogue has read the output accumulator
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   float* x_max = reinterpret_cast<float*>(p_smem + kFmhaPBytes + 256);  // [4][128]
   float* x_sum = x_max + 4 * 128;                                       // [4][128]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int q_tiles = (p.q_rows + 127) / 128;
-  const int total_items = q_tiles * p.nb0 * p.nb1;
+  // pack > 1: the nb0 query heads share one K/V head, so a 128-row tile holds 128 / pack
+  // tokens x pack heads (row = token * pack + head) and K/V are fetched once for all of them
+  const int pack = p.pack;
+  const int tile_tokens = 128 / pack;
+  const int q_tiles = (p.q_rows + tile_tokens - 1) / tile_tokens;
+  const int heads_outer = pack > 1 ? 1 : p.nb0;
+  const int total_items = q_tiles * heads_outer * p.nb1;
   auto decode = [&](int item, int* tile, int* b0, int* b1) {
     *tile = item % q_tiles;
     const int batch = item / q_tiles;
-    *b0 = batch % p.nb0;
-    *b1 = batch / p.nb0;
+    *b0 = batch % heads_outer;
+    *b1 = batch / heads_outer;
   };
   const int hd = p.head_dim;
   const int hd_chunks = (hd + 63) >> 6;
   const int n_blocks = (p.keys + kFmhaKeyBlock - 1) / kFmhaKeyBlock;
+  // with a single key block the scores stay in TMEM between the two passes: no second S product
+  const bool reuse_s = n_blocks == 1;
+  // head_dim <= 128 leaves the upper half of the query area free: a third ring stage
+  const int stages = hd_chunks <= 2 ? 3 : 2;
+  auto stage_ptr = [&](int s) -> uint8_t* {
+    return s < 2 ? q_smem + kFmhaQBytes + s * kFmhaStageBytes : q_smem + 2 * 16384;
+  };
   const int n_pv = (hd + 15) & ~15;  // UMMA N of the PV product
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(q_full, 1);
-    for (int s = 0; s < kFmhaStages; ++s) {
+    for (int s = 0; s < kFmhaMaxStages; ++s) {
       ptx::mbar_init(&ring_full[s], 1);
       ptx::mbar_init(&ring_empty[s], 1);
     }
@@ -110,7 +121,6 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const uint32_t tmem_s = *tmem_slot;        // columns [0, 256): S block
   const uint32_t tmem_o = tmem_s + 256;      // columns [256, 512): output accumulator
   pdl_wait();
-  if (threadIdx.x == 0) PI05_TRACE(0);
 
   auto keys_in_block = [&](int j) { return min(kFmhaKeyBlock, p.keys - j * kFmhaKeyBlock); };
 
@@ -124,36 +134,42 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       int it = 0;
       int items_done = 0;
       auto acquire = [&]() -> uint8_t* {
-        const int s = it % kFmhaStages;
-        const int round = it / kFmhaStages;
+        const int s = it % stages;
+        const int round = it / stages;
         if (round > 0) ok = ok && ptx::mbar_wait(&ring_empty[s], (round - 1) & 1);
-        return ring + s * kFmhaStageBytes;
+        return stage_ptr(s);
       };
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++items_done) {
       int tile, b0, b1;
       decode(item, &tile, &b0, &b1);
       if (items_done > 0) ok = ptx::mbar_wait(q_free, (items_done - 1) & 1);
       if (!ok) break;
+      PI05_TRACE(27);
       ptx::mbar_arrive_expect_tx(q_full, hd_chunks * 16384);
       for (int c = 0; c < hd_chunks; ++c) {
-        ptx::tma_load_4d(q_smem + c * 16384, &tmap_q, q_full, c * 64, tile * 128, b0, b1);
+        if (pack > 1) {
+          ptx::tma_load_4d(q_smem + c * 16384, &tmap_q, q_full, c * 64, 0, tile * tile_tokens, b1);
+        } else {
+          ptx::tma_load_4d(q_smem + c * 16384, &tmap_q, q_full, c * 64, tile * 128, b0, b1);
+        }
       }
       for (int pass = 0; pass < 2 && ok; ++pass) {
         for (int j = 0; j < n_blocks && ok; ++j) {
-          for (int c = 0; c < hd_chunks && ok; ++c, ++it) {  // K chunk: [256 keys x 64 dims]
+          const bool need_s = pass == 0 || !reuse_s;
+          for (int c = 0; c < hd_chunks && ok && need_s; ++c, ++it) {  // K chunk: [256 keys x 64 dims]
             uint8_t* dst = acquire();
             if (!ok) break;
-            ptx::mbar_arrive_expect_tx(&ring_full[it % kFmhaStages], kFmhaStageBytes);
-            ptx::tma_load_4d(dst, &tmap_k, &ring_full[it % kFmhaStages], c * 64, j * kFmhaKeyBlock, b0, b1);
+            ptx::mbar_arrive_expect_tx(&ring_full[it % stages], kFmhaStageBytes);
+            ptx::tma_load_4d(dst, &tmap_k, &ring_full[it % stages], c * 64, j * kFmhaKeyBlock, b0, b1);
           }
           if (pass == 1) {
             const int subs = (keys_in_block(j) + 63) >> 6;
             for (int v = 0; v < subs && ok; ++v, ++it) {  // V sub-block: [64 keys x head_dim]
               uint8_t* dst = acquire();
               if (!ok) break;
-              ptx::mbar_arrive_expect_tx(&ring_full[it % kFmhaStages], hd_chunks * 8192);
+              ptx::mbar_arrive_expect_tx(&ring_full[it % stages], hd_chunks * 8192);
               for (int c = 0; c < hd_chunks; ++c) {
-                ptx::tma_load_4d(dst + c * 8192, &tmap_v, &ring_full[it % kFmhaStages], c * 64,
+                ptx::tma_load_4d(dst + c * 8192, &tmap_v, &ring_full[it % stages], c * 64,
                                  j * kFmhaKeyBlock + v * 64, b0, b1);
               }
             }
@@ -177,18 +193,21 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       int items_done = 0;
       for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++items_done) {
       if (ok) ok = ptx::mbar_wait(q_full, items_done & 1);
-      if (items_done == 0) PI05_TRACE(1);
+      PI05_TRACE(1);
       for (int pass = 0; pass < 2; ++pass) {
         for (int j = 0; j < n_blocks; ++j) {
+          const bool need_s = pass == 0 || !reuse_s;
           // S may be overwritten once the softmax warps have read the previous block
-          if (ok && s_blocks > 0) ok = ptx::mbar_wait(s_free, (s_blocks - 1) & 1);
+          if (ok && need_s && s_blocks > 0) ok = ptx::mbar_wait(s_free, (s_blocks - 1) & 1);
           ptx::tc_fence_after();
-          for (int c = 0; c < hd_chunks && ok; ++c, ++it) {
-            const int s = it % kFmhaStages;
-            ok = ptx::mbar_wait(&ring_full[s], (it / kFmhaStages) & 1);
+          if (pass == 0 && j == 0) PI05_TRACE(26);
+          for (int c = 0; c < hd_chunks && ok && need_s; ++c, ++it) {
+            const int s = it % stages;
+            ok = ptx::mbar_wait(&ring_full[s], (it / stages) & 1);
             if (!ok) break;
             ptx::tc_fence_after();
-            const uint32_t k_addr = ptx::smem_u32(ring + s * kFmhaStageBytes);
+            if (pass == 0 && j == 0 && c == 0) PI05_TRACE(25);
+            const uint32_t k_addr = ptx::smem_u32(stage_ptr(s));
             const int ksteps = min(4, (hd - c * 64 + 15) >> 4);
             for (int ks = 0; ks < ksteps; ++ks) {
               ptx::umma<ptx::MmaKind::kF16>(tmem_s, ptx::make_smem_desc(q_addr + c * 16384 + ks * 32, 16, 1024),
@@ -197,9 +216,11 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             ptx::umma_commit(&ring_empty[s]);
           }
-          ptx::umma_commit(s_full);
-          if (s_blocks == 0) PI05_TRACE(2);
-          ++s_blocks;
+          if (need_s) {
+            ptx::umma_commit(s_full);
+            ++s_blocks;
+          }
+          if (pass == 0 && j == 0) PI05_TRACE(2);
           if (pass == 1 && j == n_blocks - 1) ptx::umma_commit(q_free);  // Q may be replaced
           if (pass == 1) {
             if (ok) ok = ptx::mbar_wait(p_full, pv_blocks & 1);
@@ -208,11 +229,11 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             ptx::tc_fence_after();
             const int subs = (keys_in_block(j) + 63) >> 6;
             for (int v = 0; v < subs && ok; ++v, ++it) {
-              const int s = it % kFmhaStages;
-              ok = ptx::mbar_wait(&ring_full[s], (it / kFmhaStages) & 1);
+              const int s = it % stages;
+              ok = ptx::mbar_wait(&ring_full[s], (it / stages) & 1);
               if (!ok) break;
               ptx::tc_fence_after();
-              const uint32_t v_addr = ptx::smem_u32(ring + s * kFmhaStageBytes);
+              const uint32_t v_addr = ptx::smem_u32(stage_ptr(s));
               for (int ks = 0; ks < 4; ++ks) {
                 ptx::umma<ptx::MmaKind::kF16>(tmem_o, ptx::make_smem_desc(p_addr + v * 16384 + ks * 32, 16, 1024),
                                               ptx::make_smem_desc(v_addr + ks * 2048, 8192, 1024), idesc_o,
@@ -241,7 +262,9 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++items_done) {
     int tile, b0, b1;
     decode(item, &tile, &b0, &b1);
-    const int row = tile * 128 + row_in_tile;
+    // query row (token) and head this thread owns
+    const int row = pack > 1 ? tile * tile_tokens + row_in_tile / pack : tile * 128 + row_in_tile;
+    const int head = pack > 1 ? row_in_tile % pack : b0;
     float raw_max = -3.0e38f;  // maximum of the unscaled scores of this thread's columns
     float row_max = 0.0f;      // scale * max over the whole row, known after pass 1
     float max_log2 = 0.0f;
@@ -258,9 +281,9 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         max_log2 = row_max * 1.4426950408889634f;
       }
       for (int j = 0; j < n_blocks; ++j) {
-        if (ok) ok = ptx::mbar_wait(s_full, s_blocks & 1);
+        if (ok && (pass == 0 || !reuse_s)) ok = ptx::mbar_wait(s_full, s_blocks & 1);
         ptx::tc_fence_after();
-        if (threadIdx.x == 64 && s_blocks < 6) PI05_TRACE(3 + s_blocks);
+        if (threadIdx.x == 64) PI05_TRACE(3 + pass * n_blocks + j);
         const int valid = keys_in_block(j) - group * 64;  // valid keys among this warp's 64 columns
         if (pass == 1 && p_blocks > 0 && ok) ok = ptx::mbar_wait(p_free, (p_blocks - 1) & 1);
         if (valid > 0) {
@@ -329,9 +352,11 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         } else {
           ptx::tc_fence_before();
         }
-        ptx::mbar_arrive(s_free);
-        if (threadIdx.x == 64 && s_blocks < 6) PI05_TRACE(9 + s_blocks);
-        ++s_blocks;
+        if (pass == 1 || !reuse_s) {
+          ptx::mbar_arrive(s_free);
+          ++s_blocks;
+        }
+        if (threadIdx.x == 64) PI05_TRACE(9 + pass * n_blocks + j);
       }
     }
     // row sums of the four column groups
@@ -341,15 +366,17 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         (x_sum[256 + row_in_tile] + x_sum[384 + row_in_tile]);
     if (ok) ok = ptx::mbar_wait(o_full, items_done & 1);
     ptx::tc_fence_after();
-    if (threadIdx.x == 64 && items_done == 0) PI05_TRACE(15);
+    if (threadIdx.x == 64) PI05_TRACE(15);
     if (!ok && lane == 0) atomicCAS(p.status, 0, kFmhaTimeout);
     const float inv = total > 0.0f ? 1.0f / total : 0.0f;
-    const long long out_row = (long long)b0 * p.out_sb0 + (long long)b1 * p.out_sb1 + (long long)row * p.out_ld;
+    if (threadIdx.x == 64) PI05_TRACE(24);
+    const long long out_row = (long long)head * p.out_sb0 + (long long)b1 * p.out_sb1 + (long long)row * p.out_ld;
 #pragma unroll 1
     for (int cc = group; cc < n_pv / 16; cc += 4) {
       uint32_t raw[16];
       ptx::tmem_ld_16(tmem_o + lane_base + cc * 16, raw);
       ptx::tmem_ld_wait();
+      if (threadIdx.x == 64 && cc == 0) PI05_TRACE(23);
       if (row >= p.q_rows) continue;
       const int d0 = cc * 16;
       const int valid = min(16, hd - d0);
@@ -364,8 +391,14 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           const uint32_t byte = static_cast<uint8_t>(__nv_cvt_float_to_fp8(clamped, __NV_SATFINITE, __NV_E4M3));
           w[t >> 2] |= byte << (8 * (t & 3));
         }
-        if (valid == 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        // head_dim is a multiple of 8, so a row's chunk starts on an 8-byte boundary
+        // whenever the head stride and leading dimension do: widest aligned store wins
+        const uintptr_t addr = reinterpret_cast<uintptr_t>(dst);
+        if (valid == 16 && (addr & 15u) == 0) {
           *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        } else if ((addr & 7u) == 0 && (valid & 7) == 0) {
+          *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+          if (valid == 16) *reinterpret_cast<uint2*>(dst + 8) = make_uint2(w[2], w[3]);
         } else {
           for (int t = 0; t < valid; ++t) dst[t] = static_cast<uint8_t>(w[t >> 2] >> (8 * (t & 3)));
         }
@@ -378,9 +411,10 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                                                            __uint_as_float(raw[2 * t + 1]) * inv);
           w[t] = *reinterpret_cast<const uint32_t*>(&pair);
         }
-        if (valid == 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        const uintptr_t addr = reinterpret_cast<uintptr_t>(dst);
+        if ((addr & 15u) == 0 && (valid & 7) == 0) {
           reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-          reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          if (valid == 16) reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
         } else {
           for (int t = 0; t < valid; ++t) {
             dst[t] = reinterpret_cast<const __nv_bfloat16*>(w)[t];
@@ -388,12 +422,12 @@ fmha_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
     }
+    if (threadIdx.x == 64) PI05_TRACE(16);
     ptx::tc_fence_before();
     ptx::mbar_arrive(o_free);
     }  // items
   }
 
-  if (threadIdx.x == 64) PI05_TRACE(16);
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 1) {

@@ -41,7 +41,7 @@ int elem_bytes(int op) { return op == kOpBf16 ? 2 : 1; }
 // Rank-4 tiled map {inner, rows, b0, b1}, 128-byte swizzle, zero fill outside.
 int encode_operand_map(CUtensorMap* map, int op, const void* ptr, uint64_t inner, uint64_t rows,
                uint64_t nb0, uint64_t nb1, long long ld, long long sb0, long long sb1,
-               uint32_t box_inner, uint32_t box_rows) {
+               uint32_t box_inner, uint32_t box_rows, uint32_t box_nb0, int swizzle_bytes) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return kPi05ErrDriver;
   const uint64_t es = elem_bytes(op);
@@ -56,12 +56,15 @@ int encode_operand_map(CUtensorMap* map, int op, const void* ptr, uint64_t inner
   if (s0 % 16 != 0 || s1 % 16 != 0) return kPi05ErrInvalidValue;
   cuuint64_t dims[4] = {inner, rows, nb0 < 1 ? 1 : nb0, nb1 < 1 ? 1 : nb1};
   cuuint64_t strides[3] = {row_bytes, s0, s1};
-  cuuint32_t box[4] = {box_inner, box_rows, 1, 1};
+  cuuint32_t box[4] = {box_inner, box_rows, box_nb0, 1};
   cuuint32_t estrides[4] = {1, 1, 1, 1};
   const CUtensorMapDataType dtype =
       op == kOpBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   CUresult result = encode(map, dtype, 4, const_cast<void*>(ptr), dims, strides, box, estrides,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           swizzle_bytes == 32   ? CU_TENSOR_MAP_SWIZZLE_32B
+                           : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                 : CU_TENSOR_MAP_SWIZZLE_128B,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return result == CUDA_SUCCESS ? kPi05Ok : kPi05ErrDriver;
 }
@@ -81,8 +84,9 @@ const void* kernel_ptr(int* smem, int* threads) {
 
 template <int OP, int BLOCK_N, int STAGES, bool B_MN>
 const void* persistent_ptr(int* smem, int* threads) {
-  auto kernel = &gemm_umma_persistent_kernel<OP, BLOCK_N, STAGES, B_MN>;
-  *threads = gemm_threads(8);
+  constexpr int kEpiWarps = 12;  // 3 warps per scheduler hide the TMEM / residual round trips
+  auto kernel = &gemm_umma_persistent_kernel<OP, BLOCK_N, STAGES, B_MN, kEpiWarps>;
+  *threads = gemm_threads(kEpiWarps);
   *smem = gemm_smem_bytes(BLOCK_N, STAGES);
   cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                        gemm_smem_bytes(BLOCK_N, STAGES));
@@ -278,7 +282,7 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   p.blocked_b = (!swap && q.b_blocked) ? 1 : 0;
   plan->split_k = split;
   plan->grid = dim3(tiles_x, tiles_y, q.nb0 * q.nb1 * split);
-  if (plan->multi_wave_candidate && split == 1 && q.trace == nullptr) {
+  if (plan->multi_wave_candidate && split == 1) {
     const void* persistent = nullptr;
     if (q.op == kOpBf16) persistent = select_persistent<kOpBf16>(block_n, q.b_mn_major, &smem, &threads);
     if (q.op == kOpE4m3) persistent = select_persistent<kOpE4m3>(block_n, q.b_mn_major, &smem, &threads);

@@ -95,7 +95,8 @@ enum Pi05Error : int {
 // 128-byte swizzle, zero fill outside the extents. `op` = OperandType.
 int encode_operand_map(CUtensorMap* map, int op, const void* ptr, uint64_t inner, uint64_t rows,
                        uint64_t nb0, uint64_t nb1, long long ld, long long sb0, long long sb1,
-                       uint32_t box_inner, uint32_t box_rows);
+                       uint32_t box_inner, uint32_t box_rows, uint32_t box_nb0 = 1,
+                       int swizzle_bytes = 128);
 
 int gemm_plan_build(const GemmProblem& problem, GemmPlan* plan);
 cudaError_t gemm_plan_launch(const GemmPlan& plan, cudaStream_t stream);

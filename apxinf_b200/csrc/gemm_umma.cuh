@@ -257,6 +257,58 @@ __device__ __forceinline__ void store_chunk16(const GemmParams& p, long long ind
 }
 
 // 16 consecutive bf16 of one row as floats (vector loads when aligned).
+// Eight consecutive outputs of one row (valid may be <= 0 or > 8).
+__device__ __forceinline__ void store_chunk8(const GemmParams& p, long long index, int valid,
+                                             const float (&o)[8]) {
+  if (valid <= 0) return;
+  if (p.out_type == kOutBf16) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + index;
+    if (valid >= 8 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+      uint32_t w[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        __nv_bfloat162 pair = __floats2bfloat162_rn(o[2 * t], o[2 * t + 1]);
+        w[t] = *reinterpret_cast<uint32_t*>(&pair);
+      }
+      *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        if (t < valid) dst[t] = __float2bfloat16(o[t]);
+      }
+    }
+  } else if (p.out_type == kOutE4m3) {
+    uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + index;
+    if (valid >= 8 && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+      uint32_t w[2];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        w[t] = (uint32_t)to_e4m3(o[4 * t] * p.out_inv_scale) |
+               ((uint32_t)to_e4m3(o[4 * t + 1] * p.out_inv_scale) << 8) |
+               ((uint32_t)to_e4m3(o[4 * t + 2] * p.out_inv_scale) << 16) |
+               ((uint32_t)to_e4m3(o[4 * t + 3] * p.out_inv_scale) << 24);
+      }
+      *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+    } else {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        if (t < valid) dst[t] = to_e4m3(o[t] * p.out_inv_scale);
+      }
+    }
+  } else if (p.out_type == kOutF32) {
+    float* dst = reinterpret_cast<float*>(p.out) + index;
+    if (valid >= 8 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+      reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
+      reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
+    } else {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        if (t < valid) dst[t] = o[t];
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void load_row16(const __nv_bfloat16* src, int valid, float (&x)[16]) {
   if (valid == 16 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
     const uint4 lo = reinterpret_cast<const uint4*>(src)[0];
@@ -375,16 +427,41 @@ struct AccSource {
   }
 };
 
-// Thread = one output row, TMEM columns = output columns. The two warps that share a
-// TMEM lane quarter take alternate 16-column chunks (`half` = 0 / 1).
-template <int OP, int BLOCK_N, int MODE, int HALVES>
+// 16 bf16 of one row as two 16-byte words (zero beyond `valid`), kept packed until use.
+__device__ __forceinline__ void load_row16_packed(const __nv_bfloat16* src, int valid,
+                                                  uint4 (&x)[2]) {
+  if (valid == 16 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+    x[0] = reinterpret_cast<const uint4*>(src)[0];
+    x[1] = reinterpret_cast<const uint4*>(src)[1];
+  } else {
+    uint32_t w[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      const uint32_t lo = 2 * t < valid ? __bfloat16_as_ushort(src[2 * t]) : 0u;
+      const uint32_t hi = 2 * t + 1 < valid ? __bfloat16_as_ushort(src[2 * t + 1]) : 0u;
+      w[t] = lo | (hi << 16);
+    }
+    x[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    x[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
+// Thread = one output row, TMEM columns = output columns. The HALVES warps that share a
+// TMEM lane quarter take the 16-column chunks half, half + HALVES, ... Two chunks go through
+// each TMEM round trip, and the residual (or position) values of the next round are
+// requested before the current one is processed, the first round's even before the
+// accumulator is complete (`wait_acc`), so their latency hides behind the mainloop.
+template <int OP, int BLOCK_N, int MODE, int HALVES, typename WaitAcc>
 __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
                                                 const AccSource<OP, BLOCK_N>& acc, int r,
                                                 int tile_b, long long out_base, float sr, int half,
                                                 const float* s_scale, const float* s_bias,
-                                                const float* s_gate) {
+                                                const float* s_gate, WaitAcc&& wait_acc) {
   constexpr bool kExtra =
       MODE == kEpiBiasResidual || MODE == kEpiBiasPos || MODE == kEpiGateResidual;
+  constexpr int kChunks = BLOCK_N / 16;
+  constexpr int kPerWarp = (kChunks + HALVES - 1) / HALVES;
+  constexpr int kRounds = (kPerWarp + 1) / 2;
   const bool row_ok = r < p.rows_a;
   const bool has_scale = p.col_scale != nullptr;
   const __nv_bfloat16* extra_row = nullptr;
@@ -392,52 +469,80 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
     extra_row = MODE == kEpiBiasPos ? p.pos + (long long)(r % p.pos_rows) * p.pos_ld
                                     : p.residual + out_base + (long long)r * p.ldc;
   }
-#pragma unroll 1
-  for (int cc = half; cc < BLOCK_N / 16; cc += HALVES) {
-    uint32_t raw[16];
-    acc.load16(cc * 16, raw);
+  uint4 ahead[2][2];  // residual / position values (16 bf16 per chunk) of the round to come
+  auto fetch_extra = [&](int round, int u, uint4 (&dst)[2]) {
+    const int cc = half + (2 * round + u) * HALVES;
     const int c0 = tile_b * BLOCK_N + cc * 16;
-    const int valid = row_ok ? min(16, p.rows_b - c0) : 0;
-    float extra[16];
-    if (kExtra && valid > 0) {
-      load_row16(extra_row + c0, valid, extra);
+    if (kExtra && row_ok && cc < kChunks && c0 < p.rows_b) {
+      load_row16_packed(extra_row + c0, min(16, p.rows_b - c0), dst);
     } else {
-#pragma unroll
-      for (int t = 0; t < 16; ++t) extra[t] = 0.0f;
+      dst[0] = make_uint4(0, 0, 0, 0);
+      dst[1] = make_uint4(0, 0, 0, 0);
     }
-    float bias[16], gate[16];
-    lds16(s_bias + cc * 16, bias);
-    if constexpr (MODE == kEpiGateResidual) {
-      lds16(s_gate + cc * 16, gate);
-    } else {
+  };
+  fetch_extra(0, 0, ahead[0]);
+  fetch_extra(0, 1, ahead[1]);
+  wait_acc();
+#pragma unroll 1
+  for (int round = 0; round < kRounds; ++round) {
+    uint32_t raw[2][16];
 #pragma unroll
-      for (int t = 0; t < 16; ++t) gate[t] = 0.0f;
+    for (int u = 0; u < 2; ++u) {
+      // always issued (a conditional TMEM load would push the array to local memory); a slot
+      // beyond the tile re-reads the last chunk and is ignored below
+      acc.load16(min(half + (2 * round + u) * HALVES, kChunks - 1) * 16, raw[u]);
     }
     acc.wait();
-    if (valid <= 0) continue;
-    const long long index = out_base + (long long)r * p.ldc + c0;
-    if (p.out_type == kOutS32) {
-      int* dst = reinterpret_cast<int*>(p.out) + index;
 #pragma unroll
-      for (int t = 0; t < 16; ++t) {
-        if (t < valid) dst[t] = static_cast<int>(raw[t]);
+    for (int u = 0; u < 2; ++u) {
+      const int cc = half + (2 * round + u) * HALVES;
+      const int c0 = tile_b * BLOCK_N + cc * 16;
+      const int valid = row_ok && cc < kChunks ? min(16, p.rows_b - c0) : 0;
+      const long long index = out_base + (long long)r * p.ldc + c0;
+      if (valid > 0 && p.out_type == kOutS32) {
+        int* dst = reinterpret_cast<int*>(p.out) + index;
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+          if (t < valid) dst[t] = static_cast<int>(raw[u][t]);
+        }
+      } else if (valid > 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {  // eight columns at a time keeps the temporaries in registers
+          const int j = cc * 16 + 8 * h;
+          float o[8];
+#pragma unroll
+          for (int t = 0; t < 8; ++t) o[t] = acc_to_float<OP>(raw[u][8 * h + t]) * sr;
+          if (has_scale) {
+            const float4 s0 = reinterpret_cast<const float4*>(s_scale + j)[0];
+            const float4 s1 = reinterpret_cast<const float4*>(s_scale + j)[1];
+            o[0] *= s0.x; o[1] *= s0.y; o[2] *= s0.z; o[3] *= s0.w;
+            o[4] *= s1.x; o[5] *= s1.y; o[6] *= s1.z; o[7] *= s1.w;
+          }
+          if (p.out_type != kOutF32) {
+            const float4 b0 = reinterpret_cast<const float4*>(s_bias + j)[0];
+            const float4 b1 = reinterpret_cast<const float4*>(s_bias + j)[1];
+            const float bias[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            float gate[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+            if constexpr (MODE == kEpiGateResidual) {
+              const float4 g0 = reinterpret_cast<const float4*>(s_gate + j)[0];
+              const float4 g1 = reinterpret_cast<const float4*>(s_gate + j)[1];
+              gate[0] = g0.x; gate[1] = g0.y; gate[2] = g0.z; gate[3] = g0.w;
+              gate[4] = g1.x; gate[5] = g1.y; gate[6] = g1.z; gate[7] = g1.w;
+            }
+            const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&ahead[u][h]);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float2 x = __bfloat1622float2(e[t]);
+              o[2 * t] = epi_apply<MODE>(o[2 * t], bias[2 * t], x.x, gate[2 * t]);
+              o[2 * t + 1] = epi_apply<MODE>(o[2 * t + 1], bias[2 * t + 1], x.y, gate[2 * t + 1]);
+            }
+          }
+          store_chunk8(p, index + 8 * h, valid - 8 * h, o);
+        }
       }
-      continue;
+      // request the values this slot needs in the next round while the other slot is processed
+      if (round + 1 < kRounds) fetch_extra(round + 1, u, ahead[u]);
     }
-    float o[16];
-#pragma unroll
-    for (int t = 0; t < 16; ++t) o[t] = acc_to_float<OP>(raw[t]) * sr;
-    if (has_scale) {
-      float scale[16];
-      lds16(s_scale + cc * 16, scale);
-#pragma unroll
-      for (int t = 0; t < 16; ++t) o[t] *= scale[t];
-    }
-    if (p.out_type != kOutF32) {
-#pragma unroll
-      for (int t = 0; t < 16; ++t) o[t] = epi_apply<MODE>(o[t], bias[t], extra[t], gate[t]);
-    }
-    store_chunk16(p, index, valid, o);
   }
 }
 
@@ -823,7 +928,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #define PI05_EPI_CASE(MODE)                                                                       \
   case MODE:                                                                                      \
     epilogue_normal<OP, BLOCK_N, MODE, kHalves>(p, acc, gi, tile_b, out_base, sr, half, s_scale,  \
-                                                s_bias, s_gate);                                  \
+                                                s_bias, s_gate, [] {});                           \
     break;
       switch (p.mode) {
         PI05_EPI_CASE(kEpiStore)
@@ -874,14 +979,16 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // works on tile i+1 and the TMA warp runs ahead through the shared-memory ring.
 // Normal orientation only (activations on the 128-row side), no split-K.
 // ---------------------------------------------------------------------------
-template <int OP, int BLOCK_N, int STAGES, bool B_MN>
-__global__ void __launch_bounds__(gemm_threads(8), 1)
+template <int OP, int BLOCK_N, int STAGES, bool B_MN, int EPI_WARPS>
+__global__ void __launch_bounds__(gemm_threads(EPI_WARPS), 1)
 gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             const __grid_constant__ CUtensorMap tmap_b, const GemmParams p,
                             const int tiles_a, const int tiles_b, const int total_tiles) {
   using T = OpTraits<OP>;
   static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 256, "bad BLOCK_N");
-  constexpr int kEpilogueThreads = 256;
+  static_assert(EPI_WARPS % 4 == 0 && EPI_WARPS >= 4 && EPI_WARPS <= 16, "whole lane quarters");
+  constexpr int kEpilogueThreads = 32 * EPI_WARPS;
+  constexpr int kHalves = EPI_WARPS / 4;
   constexpr int kBlockK = 128 / T::kElemBytes;
   constexpr int kStageBBytes = BLOCK_N * 128;
   constexpr int kStageBytes = kStageABytes + kStageBBytes;
@@ -894,6 +1001,11 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::make_idesc(T::kCFormat, T::kFormat, T::kFormat, 0, B_MN ? 1 : 0, 128, BLOCK_N);
 
   pdl_launch_dependents();
+  // optional phase stamps (SM clock) of CTA 0's fourth tile, for timeline studies
+  const long long t_entry = clock64();
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0;
+#define PI05_PTRACE(slot, cond) \
+  do { if (tracing && (cond)) p.trace[slot] = static_cast<unsigned int>(clock64() - t_entry); } while (0)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -916,7 +1028,7 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&acc_full[b], 1);
-      ptx::mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+      ptx::mbar_init(&acc_empty[b], EPI_WARPS);  // one arrival per epilogue warp
     }
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_smem();
@@ -955,6 +1067,8 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const long long round = it / STAGES;
           if (round > 0) ok = ptx::mbar_wait(&empty_bar[s], static_cast<uint32_t>((round - 1) & 1));
           if (!ok) break;
+          PI05_PTRACE(0, local == 3 && kb == 0);
+          PI05_PTRACE(1, local == 3 && kb == p.num_kb - 1);
           uint8_t* sa = smem + s * kStageBytes;
           uint8_t* sb = sa + kStageABytes;
           ptx::mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
@@ -984,11 +1098,13 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ok = ptx::mbar_wait(&acc_empty[buf], static_cast<uint32_t>(((local >> 1) - 1) & 1));
           ptx::tc_fence_after();
         }
+        PI05_PTRACE(2, local == 3);
         for (int kb = 0; kb < p.num_kb && ok; ++kb, ++it) {
           const int s = static_cast<int>(it % STAGES);
           ok = ptx::mbar_wait(&full_bar[s], static_cast<uint32_t>((it / STAGES) & 1));
           if (!ok) break;
           ptx::tc_fence_after();
+          PI05_PTRACE(3, local == 3 && kb == 0);
           const uint32_t a_addr = ptx::smem_u32(smem + s * kStageBytes);
           const uint32_t b_addr = a_addr + kStageABytes;
 #pragma unroll
@@ -1003,6 +1119,7 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         // signal the epilogue even after a timeout so that it never waits on a dead pipeline
         ptx::umma_commit(&acc_full[buf]);
+        PI05_PTRACE(4, local == 3);
       }
       if (!ok) atomicCAS(p.status, 0, kGemmTimeoutMma);
     }
@@ -1015,6 +1132,7 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int buf = local & 1;
       int ta, tb, b0, b1;
       decode(local, &ta, &tb, &b0, &b1);
+      PI05_PTRACE(5, local == 3 && threadIdx.x == 64);
       float* s_scale = s_vectors + buf * 768;
       float* s_bias = s_scale + 256;
       float* s_gate = s_bias + 256;
@@ -1032,20 +1150,25 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
       float sr = p.alpha;
       if (row_scale != nullptr && gi < p.rows_a) sr = p.alpha * row_scale[gi];
       asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
+      PI05_PTRACE(6, local == 3 && threadIdx.x == 64);
 
-      const bool ok = ptx::mbar_wait(&acc_full[buf], static_cast<uint32_t>((local >> 1) & 1));
-      if (!ok && lane == 0) atomicCAS(p.status, 0, kGemmTimeoutEpilogue);
-      ptx::tc_fence_after();
+      auto wait_acc = [&] {
+        const bool ok = ptx::mbar_wait(&acc_full[buf], static_cast<uint32_t>((local >> 1) & 1));
+        if (!ok && lane == 0) atomicCAS(p.status, 0, kGemmTimeoutEpilogue);
+        ptx::tc_fence_after();
+        PI05_PTRACE(7, local == 3 && threadIdx.x == 64);
+      };
       const uint32_t taddr_row =
           tmem_base + buf * BLOCK_N + (static_cast<uint32_t>(quarter * 32) << 16);
       AccSource<OP, BLOCK_N> acc{taddr_row, nullptr, 0, 1};
       if (p.mode == kEpiGeglu) {
-        epilogue_geglu_normal<OP, BLOCK_N, 2>(p, acc, gi, tb, out_base, sr, half, s_scale);
+        wait_acc();
+        epilogue_geglu_normal<OP, BLOCK_N, kHalves>(p, acc, gi, tb, out_base, sr, half, s_scale);
       } else {
-#define PI05_EPI_CASE(MODE)                                                                     \
-  case MODE:                                                                                    \
-    epilogue_normal<OP, BLOCK_N, MODE, 2>(p, acc, gi, tb, out_base, sr, half, s_scale, s_bias,  \
-                                          s_gate);                                              \
+#define PI05_EPI_CASE(MODE)                                                                    \
+  case MODE:                                                                                   \
+    epilogue_normal<OP, BLOCK_N, MODE, kHalves>(p, acc, gi, tb, out_base, sr, half, s_scale,   \
+                                                s_bias, s_gate, wait_acc);                     \
     break;
         switch (p.mode) {
           PI05_EPI_CASE(kEpiStore)
@@ -1055,10 +1178,12 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
           PI05_EPI_CASE(kEpiBiasPos)
           PI05_EPI_CASE(kEpiGateResidual)
           default:
+            wait_acc();
             break;
         }
 #undef PI05_EPI_CASE
       }
+      PI05_PTRACE(8, local == 3 && threadIdx.x == 64);
       // this warp has read everything it needs from the accumulator buffer
       ptx::tc_fence_before();
       __syncwarp();

@@ -155,7 +155,8 @@ typedef struct Pi05AttentionArgs {
   int32_t out_e4m3;
   float out_inv_scale;
   int32_t* status; /* device int32, 0 before the call */
-  uint32_t* trace; /* optional device uint32[17]: SM-clock phase timestamps of CTA (0,0,0); NULL = off */
+  uint32_t* trace; /* optional device uint32[32]: SM-clock phase stamps of CTA 0; NULL = off */
+  int32_t trace_item; /* which of CTA 0's query tiles (0 = first) is stamped */
 } Pi05AttentionArgs;
 
 int pi05_attention(const Pi05AttentionArgs* args, void* cuda_stream);

@@ -22,10 +22,10 @@ class AttentionArgs(C.Structure):
                 ("q_rows", C.c_int32), ("keys", C.c_int32), ("head_dim", C.c_int32),
                 ("nb0", C.c_int32), ("nb1", C.c_int32), ("scale", C.c_float),
                 ("out_e4m3", C.c_int32), ("out_inv_scale", C.c_float), ("status", C.c_void_p),
-                ("trace", C.c_void_p)]
+                ("trace", C.c_void_p), ("trace_item", C.c_int32)]
 
 
-def run(q, k, v, out, scale, nb0=1, nb1=1, strides=None, e4m3=False, inv=1.0, trace=None):
+def run(q, k, v, out, scale, nb0=1, nb1=1, strides=None, e4m3=False, inv=1.0, trace=None, trace_item=0):
     """q/k/v/out: torch CUDA tensors; strides: dict name -> (ld, sb0, sb1) in elements."""
     from apxinf_b200 import lib
     handle = lib()
@@ -40,7 +40,7 @@ def run(q, k, v, out, scale, nb0=1, nb1=1, strides=None, e4m3=False, inv=1.0, tr
         out=out.data_ptr(), out_ld=s["o"][0], out_sb0=s["o"][1], out_sb1=s["o"][2],
         q_rows=s["rows"], keys=s["keys"], head_dim=s["hd"], nb0=nb0, nb1=nb1, scale=scale,
         out_e4m3=int(e4m3), out_inv_scale=inv, status=status.data_ptr(),
-        trace=(trace.data_ptr() if trace is not None else None))
+        trace=(trace.data_ptr() if trace is not None else None), trace_item=trace_item)
     rc = handle.pi05_attention(C.byref(args), C.c_void_p(torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     return rc, int(status.item())
@@ -121,6 +121,26 @@ def test_batched_mqa_over_a_cache_with_row_stride():
                                   o=(hd, q_rows * hd, 0), rows=q_rows, keys=keys, hd=hd))
     assert rc == 0 and status == 0
     want = reference(q.float(), kc.float()[:, :keys], vc.float()[:, :keys], 1 / 16)
+    assert (out.float().cpu() - want).abs().max().item() <= 0.02
+
+
+@pytest.mark.parametrize("q_rows,keys,batch", [(50, 572, 3), (522, 522, 2), (5, 200, 1)])
+def test_multi_query_heads_share_one_kv_head(q_rows, keys, batch):
+    """Eight query heads per sample over one K/V head (head stride 0): the kernel packs the
+    heads of a token into the same query tile; layout as the engine's [tokens, heads * 256]."""
+    heads, hd = 8, 256
+    gen = torch.Generator().manual_seed(q_rows + keys)
+    q = torch.randn(batch, q_rows, heads, hd, generator=gen).to(torch.bfloat16)
+    kc = torch.randn(batch, keys, hd, generator=gen).to(torch.bfloat16)
+    vc = torch.randn(batch, keys, hd, generator=gen).to(torch.bfloat16)
+    out = torch.full((batch, q_rows, heads, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    rc, status = run(q.cuda(), kc.cuda(), vc.cuda(), out, 1 / 16, nb0=heads, nb1=batch,
+                     strides=dict(q=(heads * hd, hd, q_rows * heads * hd), k=(hd, 0, keys * hd),
+                                  v=(hd, 0, keys * hd), o=(heads * hd, hd, q_rows * heads * hd),
+                                  rows=q_rows, keys=keys, hd=hd))
+    assert rc == 0 and status == 0
+    want = reference(q.float().permute(0, 2, 1, 3), kc.float()[:, None], vc.float()[:, None], 1 / 16)
+    want = want.permute(0, 2, 1, 3)
     assert (out.float().cpu() - want).abs().max().item() <= 0.02
 
 
