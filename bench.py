@@ -311,7 +311,7 @@ def run_ours(args):
         achieved = flops / (avg_ms * 1e-3) / 1e12
         peak = 2.0 * peaks["bf16_tflops_sustained"]
         roofline = {
-            "kernel": "gemm_umma_kernel<e4m3, 128x256 tile> language.gate_up + GeGLU epilogue",
+            "kernel": "gemm_umma_persistent_kernel<e4m3, 128x256 tile> language.gate_up + GeGLU epilogue",
             "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": achieved / peak, "traffic": None,
             "launch_ms": avg_ms, "launches_timed": count,

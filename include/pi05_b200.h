@@ -136,8 +136,9 @@ int pi05_gemm_static_scratch(const Pi05GemmArgs* args, void* cuda_stream);
  * 1024 keys, head_dim a multiple of 8 up to 256, batched over nb0 x nb1 (element strides).
  * q [q_rows, head_dim], k / v [keys, head_dim] and out [q_rows, head_dim] are bf16 device
  * matrices with contiguous head_dim; with out_e4m3 != 0 the output is
- * e4m3(clamp(bf16(o) * out_inv_scale)). Multi-query attention passes its (token, head) pairs as
- * query rows over the one shared K/V head. Replaces the reference attention contracts mha_bf16 /
+ * e4m3(clamp(bf16(o) * out_inv_scale)). Multi-query attention passes its query heads as nb0
+ * with k_sb0 = v_sb0 = 0 (one shared K/V head): when nb0 divides 128 the kernel packs the heads
+ * of a token into the same 128-row tile and fetches K/V once for all of them. Replaces the reference attention contracts mha_bf16 /
  * mqa_bf16 / mqa_cached_f16 (crates/apxinf-cuda/src/kernels/attention.rs:627-1261) and the FFI
  * symbols behind them (ffi/cublas.rs:113-134, ffi/cutlass.rs:9-83, ffi/fa2.rs:9-58).
  */
