@@ -4,6 +4,7 @@
 #include <mutex>
 
 #include "../../include/pi05_apxinf_static.h"
+#include "fmha.h"
 #include "gemm.h"
 #include "row_kernels.cuh"
 
@@ -150,4 +151,55 @@ extern "C" int apxinf_static_bf16_gemm(const void* activation, const void* weigh
   return pi05::gemm_plan_launch(plan, static_cast<cudaStream_t>(stream)) == cudaSuccess
              ? 0
              : kBlasExecutionFailed;
+}
+
+namespace {
+
+// softmax(q k^T / sqrt(head_dim)) v through the fused attention kernel; strides in elements.
+int static_attention(const void* q, long long q_ld, long long q_sb0, long long q_sb1, const void* k,
+                     const void* v, long long kv_ld, long long kv_sb0, long long kv_sb1, void* output,
+                     int q_rows, int keys, int head_dim, int nb0, int nb1, void* stream) {
+  if (q == nullptr || k == nullptr || v == nullptr || output == nullptr || q_rows <= 0 || keys <= 0 ||
+      nb0 <= 0 || nb1 <= 0 || !pi05::fmha_supported(q_rows, keys, head_dim)) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  int* status = status_for_current_device(true);
+  if (status == nullptr) return static_cast<int>(cudaErrorInitializationError);
+  pi05::FmhaProblem f;
+  f.q = q; f.q_ld = q_ld; f.q_sb0 = q_sb0; f.q_sb1 = q_sb1;
+  f.k = k; f.k_ld = kv_ld; f.k_sb0 = kv_sb0; f.k_sb1 = kv_sb1;
+  f.v = v; f.v_ld = kv_ld; f.v_sb0 = kv_sb0; f.v_sb1 = kv_sb1;
+  f.out = output; f.out_ld = q_ld; f.out_sb0 = q_sb0; f.out_sb1 = q_sb1;
+  f.q_rows = q_rows; f.keys = keys; f.head_dim = head_dim; f.nb0 = nb0; f.nb1 = nb1;
+  f.scale = 1.0f / sqrtf(static_cast<float>(head_dim));
+  f.status = status;
+  pi05::FmhaPlan plan;
+  if (pi05::fmha_plan_build(f, &plan) != pi05::kPi05Ok) return static_cast<int>(cudaErrorInvalidValue);
+  return static_cast<int>(pi05::fmha_plan_launch(plan, static_cast<cudaStream_t>(stream)));
+}
+
+}  // namespace
+
+extern "C" int apxinf_static_mqa_bf16(const void* q, const void* k, const void* v, void* output,
+                                      int query_tokens, int key_tokens, int heads, int head_dim,
+                                      void* stream) {
+  const long long width = static_cast<long long>(heads) * head_dim;
+  return static_attention(q, width, head_dim, 0, k, v, head_dim, 0, 0, output, query_tokens,
+                          key_tokens, head_dim, heads, 1, stream);
+}
+
+extern "C" int apxinf_static_cublas_mqa_bf16(const void* q, const void* k, const void* v, void* output,
+                                             int query_tokens, int key_tokens, int heads,
+                                             int head_dim, void* stream) {
+  const int rc = apxinf_static_mqa_bf16(q, k, v, output, query_tokens, key_tokens, heads, head_dim, stream);
+  return rc == 0 ? 0 : rc == static_cast<int>(cudaErrorInvalidValue) ? kBlasInvalid : kBlasExecutionFailed;
+}
+
+extern "C" int apxinf_static_mha_bf16(const void* q, const void* k, const void* v, void* output,
+                                      int tokens_per_batch, int batches, int heads, int head_dim,
+                                      void* stream) {
+  const long long width = static_cast<long long>(heads) * head_dim;
+  return static_attention(q, width, head_dim, tokens_per_batch * width, k, v, width, head_dim,
+                          tokens_per_batch * width, output, tokens_per_batch, tokens_per_batch,
+                          head_dim, heads, batches, stream);
 }

@@ -83,6 +83,9 @@ extern "C" int pi05_attention(const Pi05AttentionArgs* args, void* cuda_stream) 
   f.status = args->status;
   f.trace = reinterpret_cast<unsigned int*>(args->trace);
   f.trace_item = args->trace_item;
+  f.key_split = args->key_split != 0;
+  f.split_scratch = static_cast<float*>(args->split_scratch);
+  f.split_scratch_bytes = static_cast<size_t>(args->split_scratch_bytes);
   FmhaPlan plan;
   const int rc = fmha_plan_build(f, &plan);
   if (rc != kPi05Ok) return rc;

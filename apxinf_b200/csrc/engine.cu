@@ -423,9 +423,13 @@ int PreparedGraph::attention(const char* name, const void* q, long long q_ld, lo
   // the fused kernel gives one CTA per 128 query rows: with only a few of them (the B=1
   // action expert) the three-launch path, which spreads keys over more CTAs, is quicker
   const bool shared_kv = nb0 > 1 && k_sb0 == 0 && v_sb0 == 0 && 128 % nb0 == 0;
-  const long long fused_ctas = shared_kv ? (long long)((q_rows * nb0 + 127) / 128) * nb1
-                                         : (long long)((q_rows + 127) / 128) * nb0 * nb1;
-  if (fmha_supported(q_rows, keys, head_dim) && fused_ctas >= 8) {
+  const long long fused_ctas = fmha_query_tiles(q_rows, nb0, nb1, shared_kv);
+  // a handful of query tiles (B=1 action expert): one CTA per (tile, 64-key slice) and a
+  // combine launch keep many more SMs pulling the K/V cache
+  const bool key_split = fmha_supported(q_rows, keys, head_dim) && fused_ctas < 32 &&
+                         fmha_split_scratch_bytes(q_rows, keys, head_dim, nb0, nb1, shared_kv) <=
+                             kSplitScratchBytes;
+  if (fmha_supported(q_rows, keys, head_dim) && (fused_ctas >= 8 || key_split)) {
     if (!measuring_) {
       FmhaProblem f;
       f.q = q; f.q_ld = q_ld; f.q_sb0 = q_sb0; f.q_sb1 = q_sb1;
@@ -438,6 +442,9 @@ int PreparedGraph::attention(const char* name, const void* q, long long q_ld, lo
       f.out_e4m3 = prec_now == kPrecFp8;
       f.out_inv_scale = 1.0f / e_->act_scale();
       f.status = e_->status();
+      f.key_split = key_split;
+      f.split_scratch = static_cast<float*>(d_partials_);
+      f.split_scratch_bytes = kSplitScratchBytes;
       Op op;
       op.name = name;
       op.stage = stage_;

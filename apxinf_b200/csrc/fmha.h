@@ -46,15 +46,26 @@ struct FmhaProblem {
   int* status = nullptr;
   unsigned int* trace = nullptr;
   int trace_item = 0;
+  // key-split path (fmha_split.cuh): one CTA per (query tile, 64-key slice) plus a combine
+  // launch; needs fmha_split_scratch_bytes() of device scratch
+  bool key_split = false;
+  float* split_scratch = nullptr;
+  size_t split_scratch_bytes = 0;
 };
 
 struct FmhaPlan {
   CUtensorMap tmap_q, tmap_k, tmap_v;
   FmhaParams params;
   dim3 grid;
+  bool key_split = false;
+  float* split_scratch = nullptr;
+  dim3 combine_grid;
 };
 
 bool fmha_supported(int q_rows, int keys, int head_dim);
+// Query tiles (CTAs of the unsplit kernel) and scratch bytes of the key-split path.
+long long fmha_query_tiles(int q_rows, int nb0, int nb1, bool shared_kv);
+size_t fmha_split_scratch_bytes(int q_rows, int keys, int head_dim, int nb0, int nb1, bool shared_kv);
 int fmha_plan_build(const FmhaProblem& problem, FmhaPlan* plan);
 cudaError_t fmha_plan_launch(const FmhaPlan& plan, cudaStream_t stream);
 

@@ -48,6 +48,21 @@ int apxinf_static_prepare_bf16_gemm(int m, int n, int k);
 int apxinf_static_bf16_gemm(const void* activation, const void* weight, void* output, int m, int n,
                             int k, float alpha, void* stream);
 
+/* adapters/static_bf16_adapter.cu:265-278, kernels/custom/attention.cuh:761-812 — multi-query
+ * attention softmax(q k^T / sqrt(head_dim)) v: q and output [query_tokens, heads, head_dim], k and v
+ * [key_tokens, head_dim], bf16. Here one fused tensor-core launch; key_tokens <= 1024 and head_dim a
+ * multiple of 8 up to 256 (cudaErrorInvalidValue otherwise). Returns a cudaError_t value. */
+int apxinf_static_mqa_bf16(const void* q, const void* k, const void* v, void* output, int query_tokens,
+                           int key_tokens, int heads, int head_dim, void* stream);
+/* adapters/cublas_adapter.cu:89-132 — the same contract behind the reference's cuBLAS path
+ * (QK^T GEMM, softmax, PV GEMM there); returns a cublasStatus_t value. */
+int apxinf_static_cublas_mqa_bf16(const void* q, const void* k, const void* v, void* output,
+                                  int query_tokens, int key_tokens, int heads, int head_dim, void* stream);
+/* adapters/static_bf16_adapter.cu:280-292, kernels/custom/attention.cuh:814-870 — per-batch
+ * multi-head attention: q, k, v and output [batches * tokens_per_batch, heads, head_dim] bf16. */
+int apxinf_static_mha_bf16(const void* q, const void* k, const void* v, void* output, int tokens_per_batch,
+                           int batches, int heads, int head_dim, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -158,6 +158,14 @@ typedef struct Pi05AttentionArgs {
   int32_t* status; /* device int32, 0 before the call */
   uint32_t* trace; /* optional device uint32[32]: SM-clock phase stamps of CTA 0; NULL = off */
   int32_t trace_item; /* which of CTA 0's query tiles (0 = first) is stamped */
+  /* key_split != 0: one CTA per (query tile, 64-key slice) writes partial outputs to
+   * split_scratch and a second launch combines them; for calls with few query tiles.
+   * split_scratch needs tiles * ceil(keys / 64) * 128 * (head_dim + 2) * 4 bytes
+   * (PI05_ERR_SCRATCH_LIMIT if smaller); tiles = ceil(q_rows / 128) * nb0 * nb1, or
+   * ceil(q_rows * nb0 / 128) * nb1 for packed multi-query heads. */
+  int32_t key_split;
+  void* split_scratch;
+  int64_t split_scratch_bytes;
 } Pi05AttentionArgs;
 
 int pi05_attention(const Pi05AttentionArgs* args, void* cuda_stream);

@@ -22,10 +22,11 @@ class AttentionArgs(C.Structure):
                 ("q_rows", C.c_int32), ("keys", C.c_int32), ("head_dim", C.c_int32),
                 ("nb0", C.c_int32), ("nb1", C.c_int32), ("scale", C.c_float),
                 ("out_e4m3", C.c_int32), ("out_inv_scale", C.c_float), ("status", C.c_void_p),
-                ("trace", C.c_void_p), ("trace_item", C.c_int32)]
+                ("trace", C.c_void_p), ("trace_item", C.c_int32),
+                ("key_split", C.c_int32), ("split_scratch", C.c_void_p), ("split_scratch_bytes", C.c_int64)]
 
 
-def run(q, k, v, out, scale, nb0=1, nb1=1, strides=None, e4m3=False, inv=1.0, trace=None, trace_item=0):
+def run(q, k, v, out, scale, nb0=1, nb1=1, strides=None, e4m3=False, inv=1.0, trace=None, trace_item=0, key_split=False):
     """q/k/v/out: torch CUDA tensors; strides: dict name -> (ld, sb0, sb1) in elements."""
     from apxinf_b200 import lib
     handle = lib()
@@ -41,6 +42,9 @@ def run(q, k, v, out, scale, nb0=1, nb1=1, strides=None, e4m3=False, inv=1.0, tr
         q_rows=s["rows"], keys=s["keys"], head_dim=s["hd"], nb0=nb0, nb1=nb1, scale=scale,
         out_e4m3=int(e4m3), out_inv_scale=inv, status=status.data_ptr(),
         trace=(trace.data_ptr() if trace is not None else None), trace_item=trace_item)
+    if key_split:
+        scratch = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+        args.key_split, args.split_scratch, args.split_scratch_bytes = 1, scratch.data_ptr(), scratch.numel()
     rc = handle.pi05_attention(C.byref(args), C.c_void_p(torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     return rc, int(status.item())
@@ -142,6 +146,48 @@ def test_multi_query_heads_share_one_kv_head(q_rows, keys, batch):
     want = reference(q.float().permute(0, 2, 1, 3), kc.float()[:, None], vc.float()[:, None], 1 / 16)
     want = want.permute(0, 2, 1, 3)
     assert (out.float().cpu() - want).abs().max().item() <= 0.02
+
+
+@pytest.mark.parametrize("q_rows,keys,batch,hd,heads", [(10, 532, 1, 256, 8), (50, 572, 2, 256, 8),
+                                                        (7, 1, 1, 64, 1), (130, 200, 1, 72, 3), (3, 1000, 1, 128, 8)])
+@pytest.mark.parametrize("e4m3", [False, True])
+def test_key_split_path_matches_the_exact_softmax(q_rows, keys, batch, hd, heads, e4m3):
+    """One CTA per (query tile, 64-key slice) + combine launch; multi-query when heads == 8."""
+    gen = torch.Generator().manual_seed(q_rows * 7 + keys)
+    shared = heads == 8
+    q = torch.randn(batch, q_rows, heads, hd, generator=gen).to(torch.bfloat16)
+    kv_heads = 1 if shared else heads
+    kc = torch.randn(batch, kv_heads, keys, hd, generator=gen).to(torch.bfloat16)
+    vc = torch.randn(batch, kv_heads, keys, hd, generator=gen).to(torch.bfloat16)
+    dtype = torch.float8_e4m3fn if e4m3 else torch.bfloat16
+    out = torch.zeros(batch, q_rows, heads, hd, dtype=dtype, device="cuda")
+    scale = 1.0 / math.sqrt(hd)
+    kv_sb0 = 0 if shared else keys * hd
+    rc, status = run(q.cuda(), kc.cuda(), vc.cuda(), out, scale, nb0=heads, nb1=batch, e4m3=e4m3, inv=16.0,
+                     key_split=True,
+                     strides=dict(q=(heads * hd, hd, q_rows * heads * hd), k=(hd, kv_sb0, kv_heads * keys * hd),
+                                  v=(hd, kv_sb0, kv_heads * keys * hd), o=(heads * hd, hd, q_rows * heads * hd),
+                                  rows=q_rows, keys=keys, hd=hd))
+    assert rc == 0 and status == 0
+    want = reference(q.float().permute(0, 2, 1, 3), kc.float().expand(batch, heads, keys, hd),
+                     vc.float().expand(batch, heads, keys, hd), scale).permute(0, 2, 1, 3)
+    got = out.float().cpu() / (16.0 if e4m3 else 1.0)
+    tol = 0.02 + (0.07 * want.abs().max().item() if e4m3 else 0.0)
+    assert (got - want).abs().max().item() <= tol
+
+
+def test_key_split_needs_scratch():
+    q = torch.zeros(16, 64, dtype=torch.bfloat16, device="cuda")
+    from apxinf_b200 import lib
+    st = dict(q=(64, 0, 0), k=(64, 0, 0), v=(64, 0, 0), o=(64, 0, 0), rows=16, keys=100, hd=64)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    args = AttentionArgs(q=q.data_ptr(), q_ld=64, k=q.data_ptr(), k_ld=64, v=q.data_ptr(), v_ld=64,
+                         out=q.data_ptr(), out_ld=64, q_rows=16, keys=16, head_dim=64, nb0=1, nb1=1, scale=1.0,
+                         status=status.data_ptr(), key_split=1, split_scratch=None, split_scratch_bytes=0)
+    handle = lib()
+    handle.pi05_attention.argtypes = [C.POINTER(AttentionArgs), C.c_void_p]
+    handle.pi05_attention.restype = C.c_int
+    assert handle.pi05_attention(C.byref(args), None) == -7
 
 
 def test_rejects_unsupported_shapes():

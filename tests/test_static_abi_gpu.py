@@ -132,3 +132,55 @@ def test_bf16_gemm_row_major_weight():
     err = _bf16(out) - want
     assert np.abs(err).max() <= 0.125 and np.sqrt((err ** 2).mean()) <= 0.02
     assert lib.apxinf_static_bf16_gemm(None, _p(wd), _p(out), m, n, k, C.c_float(1.0), _stream()) == 7
+
+
+def _softmax_attention(q, k, v):
+    """float64 restatement of kernels/custom/attention.cuh:761-870 (scores * rsqrt(head_dim),
+    softmax over keys, probabilities times values)."""
+    s = np.einsum("...qd,...kd->...qk", q.astype(np.float64), k.astype(np.float64)) / np.sqrt(q.shape[-1])
+    s -= s.max(axis=-1, keepdims=True)
+    p = np.exp(s)
+    p /= p.sum(axis=-1, keepdims=True)
+    return np.einsum("...qk,...kd->...qd", p, v.astype(np.float64))
+
+
+@pytest.mark.parametrize("symbol", ["apxinf_static_mqa_bf16", "apxinf_static_cublas_mqa_bf16"])
+def test_mqa_bf16_under_the_reference_names(symbol):
+    # crates/apxinf-cuda/src/tests/bf16.rs: MQA over one K/V head, q [tokens, heads, head_dim]
+    tokens, keys, heads, hd = 13, 300, 8, 256
+    rng = np.random.default_rng(5)
+    q = torch.from_numpy(rng.standard_normal((tokens, heads, hd)).astype(np.float32)).to(torch.bfloat16)
+    k = torch.from_numpy(rng.standard_normal((keys, hd)).astype(np.float32)).to(torch.bfloat16)
+    v = torch.from_numpy(rng.standard_normal((keys, hd)).astype(np.float32)).to(torch.bfloat16)
+    out = torch.zeros(tokens, heads, hd, dtype=torch.bfloat16, device="cuda")
+    dq, dk, dv = q.cuda(), k.cuda(), v.cuda()
+    rc = getattr(_lib(), symbol)(_p(dq), _p(dk), _p(dv), _p(out), tokens, keys, heads, hd, _stream())
+    torch.cuda.synchronize()
+    assert rc == 0
+    want = _softmax_attention(_bf16(q).transpose(1, 0, 2), _bf16(k)[None], _bf16(v)[None]).transpose(1, 0, 2)
+    assert np.abs(_bf16(out) - want).max() <= 0.02
+
+
+def test_mha_bf16_under_the_reference_name():
+    tokens, batches, heads, hd = 256, 2, 4, 72
+    rng = np.random.default_rng(6)
+    shape = (batches * tokens, heads, hd)
+    q, k, v = (torch.from_numpy(rng.standard_normal(shape).astype(np.float32)).to(torch.bfloat16) for _ in range(3))
+    out = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+    dq, dk, dv = q.cuda(), k.cuda(), v.cuda()
+    rc = _lib().apxinf_static_mha_bf16(_p(dq), _p(dk), _p(dv), _p(out), tokens, batches, heads, hd, _stream())
+    torch.cuda.synchronize()
+    assert rc == 0
+
+    def split(t):  # [batches, heads, tokens, hd]
+        return _bf16(t).reshape(batches, tokens, heads, hd).transpose(0, 2, 1, 3)
+
+    want = _softmax_attention(split(q), split(k), split(v)).transpose(0, 2, 1, 3).reshape(shape)
+    assert np.abs(_bf16(out) - want).max() <= 0.02
+
+
+def test_static_attention_rejects_what_the_kernel_cannot_do():
+    t = torch.zeros(8, 8, 64, dtype=torch.bfloat16, device="cuda")
+    assert _lib().apxinf_static_mqa_bf16(_p(t), _p(t), _p(t), _p(t), 8, 5000, 8, 64, _stream()) == 1
+    assert _lib().apxinf_static_cublas_mqa_bf16(_p(t), _p(t), _p(t), _p(t), 8, 5000, 8, 64, _stream()) == 7
+    assert _lib().apxinf_static_mha_bf16(None, _p(t), _p(t), _p(t), 8, 1, 8, 64, _stream()) == 1
