@@ -32,6 +32,7 @@ PROTOTYPES = [
     ("pi05_engine_capture", C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.POINTER(_P)]),
     ("pi05_graph_destroy", None, [_P]),
     ("pi05_graph_update_raw_image_inputs", C.c_int, [_P, _P, _P, _P]),
+    ("pi05_graph_update_patch_inputs", C.c_int, [_P, _P, _P, _P]),
     ("pi05_graph_replay", C.c_int, [_P]),
     ("pi05_graph_run_eager", C.c_int, [_P]),
     ("pi05_graph_sync", C.c_int, [_P]),

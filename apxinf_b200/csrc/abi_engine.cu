@@ -111,7 +111,8 @@ extern "C" int pi05_engine_capture(Pi05Engine* engine, int32_t token_count, int3
                                    int32_t batch, Pi05Graph** out) {
   if (engine == nullptr || out == nullptr) return pi05::kPi05ErrInvalidValue;
   *out = nullptr;
-  if (image_layout != PI05_IMAGE_NHWC && image_layout != PI05_IMAGE_NCHW) {
+  if (image_layout != PI05_IMAGE_NHWC && image_layout != PI05_IMAGE_NCHW &&
+      image_layout != PI05_IMAGE_PATCHES) {
     return pi05::kPi05ErrInvalidValue;
   }
   auto* impl = new (std::nothrow) pi05::PreparedGraph(engine->impl, token_count, image_layout, batch);
@@ -135,6 +136,11 @@ extern "C" void pi05_graph_destroy(Pi05Graph* graph) {
 }
 
 #define PI05_GRAPH_CALL(expr) (graph == nullptr ? pi05::kPi05ErrInvalidValue : graph->impl->expr)
+
+extern "C" int pi05_graph_update_patch_inputs(Pi05Graph* graph, const float* patches,
+                                              const uint32_t* token_ids, const uint16_t* noise_bf16) {
+  return PI05_GRAPH_CALL(update_patch_inputs(patches, token_ids, noise_bf16));
+}
 
 extern "C" int pi05_graph_update_raw_image_inputs(Pi05Graph* graph, const uint8_t* images,
                                                   const uint32_t* token_ids,

@@ -278,8 +278,8 @@ int Engine::read_weight(const char* name, void* host, size_t capacity, size_t* a
 // PreparedGraph
 // ---------------------------------------------------------------------------
 
-PreparedGraph::PreparedGraph(Engine* engine, int token_count, int nchw, int batch)
-    : e_(engine), T_(token_count), nchw_(nchw), B_(batch) {
+PreparedGraph::PreparedGraph(Engine* engine, int token_count, int image_layout, int batch)
+    : e_(engine), T_(token_count), nchw_(image_layout), B_(batch) {
   const ModelConfig& c = e_->cfg();
   V_ = c.num_views * c.patches_per_view();
   P_ = V_ + T_;
@@ -536,6 +536,10 @@ int PreparedGraph::build(bool measuring) {
 
   // ---- inputs / persistent buffers ----
   d_images_ = static_cast<uint8_t*>(arena_.alloc((size_t)n_images * c.image_size * c.image_size * 3));
+  if (nchw_ == kLayoutPatches) {
+    d_patches_in_ = static_cast<float*>(arena_.alloc(
+        (size_t)n_images * c.patches_per_view() * 3 * c.patch_size * c.patch_size * sizeof(float)));
+  }
   d_tokens_ = static_cast<uint32_t*>(arena_.alloc((size_t)B_ * T_ * 4));
   d_noise_ = arena_.alloc((size_t)Ra * c.action_dim * 2);
   d_state_ = arena_.alloc((size_t)Ra * c.action_dim * 2);
@@ -606,12 +610,13 @@ int PreparedGraph::build(bool measuring) {
   {
     PatchifyArgs pa{};
     pa.images = d_images_;
+    pa.f32_patches = d_patches_in_;  // null unless the graph takes ready-made patches
     pa.patches = prec == kPrecInt8 ? patches.wide : patches.data;
     pa.n_images = n_images;
     pa.image_size = c.image_size;
     pa.patch_size = c.patch_size;
     pa.ld = static_cast<int>(patch_ld);
-    pa.nchw = nchw_;
+    pa.nchw = nchw_ == 1;
     pa.out = prec == kPrecFp8 ? kRowE4m3 : kRowBf16;
     pa.inv_scale = inv_act;
     add_kernel("patchify", [pa](cudaStream_t s) { return launch_patchify(pa, s); });
@@ -852,10 +857,27 @@ int PreparedGraph::sync() {
   return kPi05Ok;
 }
 
+int PreparedGraph::update_patch_inputs(const float* patches, const uint32_t* tokens,
+                                       const uint16_t* noise_bf16) {
+  const ModelConfig& c = e_->cfg();
+  if (patches == nullptr || tokens == nullptr || noise_bf16 == nullptr || d_patches_in_ == nullptr) {
+    return kPi05ErrInvalidValue;
+  }
+  PI05_CUDA(cudaSetDevice(e_->device()));
+  cudaStream_t s = e_->stream();
+  const size_t patch_floats =
+      (size_t)B_ * c.num_views * c.patches_per_view() * 3 * c.patch_size * c.patch_size;
+  PI05_CUDA(cudaMemcpyAsync(d_patches_in_, patches, patch_floats * sizeof(float), cudaMemcpyHostToDevice, s));
+  PI05_CUDA(cudaMemcpyAsync(d_tokens_, tokens, (size_t)B_ * T_ * 4, cudaMemcpyHostToDevice, s));
+  PI05_CUDA(cudaMemcpyAsync(d_noise_, noise_bf16, (size_t)B_ * H_ * c.action_dim * 2, cudaMemcpyHostToDevice, s));
+  return kPi05Ok;
+}
+
 int PreparedGraph::update_inputs(const uint8_t* images, const uint32_t* tokens,
                                  const uint16_t* noise_bf16) {
   const ModelConfig& c = e_->cfg();
   if (images == nullptr || tokens == nullptr || noise_bf16 == nullptr) return kPi05ErrInvalidValue;
+  if (d_patches_in_ != nullptr) return kPi05ErrInvalidValue;  // this graph takes patches
   PI05_CUDA(cudaSetDevice(e_->device()));
   cudaStream_t s = e_->stream();
   PI05_CUDA(cudaMemcpyAsync(d_images_, images, (size_t)B_ * c.num_views * c.image_size * c.image_size * 3, cudaMemcpyHostToDevice, s));

@@ -74,6 +74,8 @@ struct Op {
   std::function<cudaError_t(cudaStream_t)> launch;
 };
 
+constexpr int kLayoutPatches = 2;
+
 class Arena {
  public:
   void reset(uint8_t* base, size_t capacity) { base_ = base; capacity_ = capacity; used_ = 0; }
@@ -98,7 +100,8 @@ class Engine;
 // One prepared inference: fixed token count, image layout and batch.
 class PreparedGraph {
  public:
-  PreparedGraph(Engine* engine, int token_count, int nchw, int batch);
+  // image_layout: 0 = NHWC u8 images, 1 = NCHW u8 images, 2 = ready-made fp32 patch rows
+  PreparedGraph(Engine* engine, int token_count, int image_layout, int batch);
   ~PreparedGraph();
   int prepare();                       // allocate, plan every launch, compute the styles
   int capture();                       // record the launch list into one CUDA graph
@@ -106,6 +109,8 @@ class PreparedGraph {
   int replay();                        // cudaGraphLaunch
   int sync();                          // stream synchronize + device status word
   int update_inputs(const uint8_t* images, const uint32_t* tokens, const uint16_t* noise_bf16);
+  // graphs captured with the patch layout: fp32 patch rows instead of images
+  int update_patch_inputs(const float* patches, const uint32_t* tokens, const uint16_t* noise_bf16);
   int output(float* host_f32);         // [batch, horizon, action_dim]
   int time_replays(int iterations, float* ms_each);
   int stage_times(float* ms3);
@@ -153,6 +158,7 @@ class PreparedGraph {
   std::unordered_map<std::string, std::pair<void*, size_t>> tensors_;
   // inputs / outputs
   uint8_t* d_images_ = nullptr;
+  float* d_patches_in_ = nullptr;  // patch layout only
   uint32_t* d_tokens_ = nullptr;
   void* d_noise_ = nullptr;
   void* d_state_ = nullptr;

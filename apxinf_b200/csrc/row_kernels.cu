@@ -317,7 +317,8 @@ __global__ void patchify_kernel(PatchifyArgs a) {
       const long long src =
           a.nchw ? (((long long)image * 3 + channel) * a.image_size + yy) * a.image_size + xx
                  : (((long long)image * a.image_size + yy) * a.image_size + xx) * 3 + channel;
-      value = (static_cast<float>(a.images[src]) / 255.0f) * 2.0f - 1.0f;
+      value = a.f32_patches != nullptr ? a.f32_patches[prow * patch_width + col]
+                                       : (static_cast<float>(a.images[src]) / 255.0f) * 2.0f - 1.0f;
     }
     y[i] = value;
   }
@@ -358,7 +359,9 @@ __global__ void patchify_scalar_kernel(PatchifyArgs a) {
   const long long src =
       a.nchw ? (((long long)image * 3 + channel) * a.image_size + yy) * a.image_size + xx
              : (((long long)image * a.image_size + yy) * a.image_size + xx) * 3 + channel;
-  const float value = (static_cast<float>(a.images[src]) / 255.0f) * 2.0f - 1.0f;
+  const float value = a.f32_patches != nullptr
+                          ? a.f32_patches[prow * patch_width + col]
+                          : (static_cast<float>(a.images[src]) / 255.0f) * 2.0f - 1.0f;
   reinterpret_cast<__nv_bfloat16*>(a.patches)[prow * a.ld + col] = __float2bfloat16(value);
 }
 
@@ -495,7 +498,7 @@ cudaError_t launch_softmax(void* scores, int rows_per_batch, int batches, long l
 }
 
 cudaError_t launch_patchify(const PatchifyArgs& a, cudaStream_t stream) {
-  if (a.images == nullptr || a.patches == nullptr || a.n_images <= 0 || a.image_size <= 0 ||
+  if ((a.images == nullptr && a.f32_patches == nullptr) || a.patches == nullptr || a.n_images <= 0 || a.image_size <= 0 ||
       a.patch_size <= 0 || a.image_size % a.patch_size != 0 ||
       a.ld < 3 * a.patch_size * a.patch_size || (a.out != kRowBf16 && a.out != kRowE4m3)) {
     return cudaErrorInvalidValue;

@@ -56,6 +56,9 @@ cudaError_t launch_softmax(void* scores, int rows_per_batch, int batches, long l
 
 struct PatchifyArgs {
   const uint8_t* images;  // [n_images, size, size, 3] (NHWC) or [n_images, 3, size, size]
+  // optional: ready-made patch rows [n_images * pps * pps, 3*ps*ps] fp32 (same column order) to
+  // convert instead of reading `images`
+  const float* f32_patches;
   void* patches;          // [n_images * pps * pps, ld] bf16 or e4m3, columns c*ps*ps + dy*ps + dx
   int n_images, image_size, patch_size;
   int ld;                 // >= 3*ps*ps, multiple of 16; pad columns are written as zero

@@ -211,9 +211,31 @@ class CapturedGraph:
                                            C.byref(size)), f"pi05_graph_read_tensor({name})")
         return out
 
+    def update_patch_inputs(self, patches, token_ids, noise) -> None:
+        """For graphs captured with `capture_infer_patches`: patches float32
+        [batch, views * patches_per_view, 3 * patch_size**2] (VisionObservation::Patches,
+        crates/apxinf-model/src/vla/mod.rs:14-19), token ids and noise as above."""
+        cfg = self._rt.config
+        if isinstance(noise, np.ndarray) and noise.dtype != np.uint16:
+            noise = float_to_bf16_bits(noise)
+        patches = np.ascontiguousarray(patches, dtype=np.float32)
+        assert patches.size == (self.batch * cfg.num_views * cfg.patches_per_view
+                                * 3 * cfg.patch_size ** 2)
+        token_ids = np.ascontiguousarray(token_ids, dtype=np.uint32)
+        assert token_ids.size == self.batch * self.token_count
+        noise = np.ascontiguousarray(noise)
+        assert noise.size == self.batch * cfg.action_horizon * cfg.action_dim
+        self._keep = [patches, token_ids, noise]
+        check(lib().pi05_graph_update_patch_inputs(
+            self._h, patches.ctypes.data, token_ids.ctypes.data, noise.ctypes.data),
+            "pi05_graph_update_patch_inputs")
+
     def infer_host(self, images, token_ids, noise) -> np.ndarray:
         """Host buffers in, host float32 action chunk out (the call a user makes)."""
-        self.update_raw_image_inputs(images, token_ids, noise)
+        if self.raw_image_layout == "patches":
+            self.update_patch_inputs(images, token_ids, noise)
+        else:
+            self.update_raw_image_inputs(images, token_ids, noise)
         self.replay()
         return self.output()
 
@@ -264,3 +286,11 @@ class Pi05Runtime:
         check(lib().pi05_engine_capture(self._h, token_count, LAYOUTS[layout], batch,
                                         C.byref(handle)), "pi05_engine_capture")
         return CapturedGraph(self, handle.value, token_count, layout, batch)
+
+    def capture_infer_patches(self, token_count: int, batch: int = 1) -> CapturedGraph:
+        """The same forward from ready-made fp32 patch rows (the reference's L0 entry
+        `Model._infer_patches`, crates/apxinf-py/src/lib.rs:348-395)."""
+        handle = C.c_void_p()
+        check(lib().pi05_engine_capture(self._h, token_count, 2, batch, C.byref(handle)),
+              "pi05_engine_capture")
+        return CapturedGraph(self, handle.value, token_count, "patches", batch)

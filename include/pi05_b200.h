@@ -175,7 +175,9 @@ int pi05_attention(const Pi05AttentionArgs* args, void* cuda_stream);
 /* ------------------------------------------------------------------------- */
 
 enum { PI05_DTYPE_BF16 = 0, PI05_DTYPE_FP8 = 1, PI05_DTYPE_INT8 = 2 };
-enum { PI05_IMAGE_NHWC = 0, PI05_IMAGE_NCHW = 1 };
+/* PI05_IMAGE_PATCHES: the graph takes ready-made fp32 patch rows (the reference's L0 entry,
+ * crates/apxinf-py/src/lib.rs:348-395) instead of u8 images. */
+enum { PI05_IMAGE_NHWC = 0, PI05_IMAGE_NCHW = 1, PI05_IMAGE_PATCHES = 2 };
 
 /* Architecture constants; field meaning and defaults follow Pi05Config /
  * GemmaVariantConfig (crates/apxinf-model/src/pi05/config.rs:5-109).
@@ -229,6 +231,11 @@ void pi05_graph_destroy(Pi05Graph* graph);
  * stay valid until the next pi05_graph_sync / pi05_graph_output. */
 int pi05_graph_update_raw_image_inputs(Pi05Graph* graph, const uint8_t* images,
                                        const uint32_t* token_ids, const uint16_t* noise_bf16);
+/* The same for a graph captured with PI05_IMAGE_PATCHES: patches fp32
+ * [batch, views * patches_per_view, 3 * patch_size^2], columns ordered channel, dy, dx
+ * (VisionObservation::Patches, crates/apxinf-model/src/vla_runtime.rs). */
+int pi05_graph_update_patch_inputs(Pi05Graph* graph, const float* patches,
+                                   const uint32_t* token_ids, const uint16_t* noise_bf16);
 int pi05_graph_replay(Pi05Graph* graph);     /* cudaGraphLaunch, asynchronous */
 int pi05_graph_run_eager(Pi05Graph* graph);  /* the same launch list without the graph */
 int pi05_graph_sync(Pi05Graph* graph);       /* waits; PI05_ERR_DEVICE_TIMEOUT if a device wait ran out */
