@@ -249,6 +249,7 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   p.pos_ld = q.pos_ld;
   p.mode = q.mode;
   p.out_type = q.out_type;
+  p.group_a = 1;
   p.status = q.status;
 
   const int tiles_x = (p.rows_a + 127) / 128, tiles_y = (p.rows_b + block_n - 1) / block_n;
@@ -297,6 +298,12 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
       plan->threads = threads;
       plan->tiles_a = tiles_x;
       plan->tiles_b = tiles_y;
+      // row tiles per raster group: about 24 MB of A, which stays in L2 while the group
+      // sweeps the column tiles (measured on the batch-64 gate_up launch: HBM reads fell from
+      // 1.45 GB, 10 x the operands, when all 261 row tiles formed one group)
+      const long long a_tile_bytes = 128LL * q.K * es;
+      const long long rows_in_l2 = std::max<long long>(8, (24LL << 20) / std::max<long long>(1, a_tile_bytes));
+      plan->params.group_a = static_cast<int>(std::min<long long>(tiles_x, rows_in_l2));
       plan->total_tiles = static_cast<int>(tiles);
       int sms = 148;
       int device = 0;

@@ -97,6 +97,8 @@ struct GemmParams {
   // operand stored K-block-major ([K/128B][rows][128 B]): every TMA box is one contiguous
   // 128-row x 128-byte run; its map is {128 B, rows, k-blocks}
   int blocked_a, blocked_b;
+  // persistent kernel: row tiles per raster group (>= 1)
+  int group_a;
 };
 
 __device__ __forceinline__ float round_bf16(float x) {
@@ -1066,10 +1068,17 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   auto decode = [&](int local, int* ta, int* tb, int* b0, int* b1) {
     const int tile = static_cast<int>(blockIdx.x) + local * static_cast<int>(gridDim.x);
-    *ta = tile % tiles_a;
-    const int rest = tile / tiles_a;
-    *tb = rest % tiles_b;
-    const int batch = rest / tiles_b;
+    const int per_batch = tiles_a * tiles_b;
+    const int batch = tile / per_batch;
+    const int in_batch = tile - batch * per_batch;
+    // raster order: row tiles in groups of p.group_a; inside a group the row tile runs fastest
+    // (CTAs of a wave share the B tile) and every column tile is visited before the next group,
+    // so a group's A rows (sized to stay in L2) are fetched from HBM once
+    const int group = in_batch / (p.group_a * tiles_b);
+    const int in_group = in_batch - group * p.group_a * tiles_b;
+    const int group_rows = min(p.group_a, tiles_a - group * p.group_a);
+    *tb = in_group / group_rows;
+    *ta = group * p.group_a + in_group - *tb * group_rows;
     *b0 = batch % p.nb0;
     *b1 = batch / p.nb0;
   };

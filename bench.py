@@ -43,6 +43,9 @@ METRIC = "pi05_fp8_action_chunks_per_s"
 UNIT = "action chunks/s"
 
 
+GATE_UP_DRAM_BYTES_BATCH64 = 276.02e6 + 508.51e6
+
+
 def measured_peaks():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -313,7 +316,10 @@ def run_ours(args):
         roofline = {
             "kernel": "gemm_umma_persistent_kernel<e4m3, 128x256 tile> language.gate_up + GeGLU epilogue",
             "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-            "frac": achieved / peak, "traffic": None,
+            "frac": achieved / peak,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the single-pass ncu
+            # capture of this workload summarised under profiles/ (batch 64 only)
+            "traffic": GATE_UP_DRAM_BYTES_BATCH64 if args.batch == 64 else None,
             "launch_ms": avg_ms, "launches_timed": count,
             "flops_per_launch": flops,
             "peak_source": (f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); "
