@@ -63,6 +63,52 @@ int apxinf_static_cublas_mqa_bf16(const void* q, const void* k, const void* v, v
 int apxinf_static_mha_bf16(const void* q, const void* k, const void* v, void* output, int tokens_per_batch,
                            int batches, int heads, int head_dim, void* stream);
 
+/*
+ * The remaining BF16 row operators of adapters/static_bf16_adapter.cu (all tensors bf16,
+ * row-major; `bias` arguments may be NULL; every function returns a cudaError_t value). This
+ * library's own PI0.5 engine performs the same arithmetic inside its GEMM epilogues; these
+ * entry points serve hosts that bind the reference's operators one by one.
+ */
+/* :47-80, activation.cuh:244-256 — output = act(input + bias); activation 0 none, 1 GELU(tanh), 2 SiLU */
+int apxinf_static_bias_activation_bf16(const void* input, const void* bias, void* output, int rows,
+                                       int cols, int activation, void* stream);
+/* :92-102 — output = [first; second] along rows */
+int apxinf_static_concat_rows_bf16(const void* first, const void* second, void* output, int first_rows,
+                                   int second_rows, int cols, void* stream);
+/* :114-138, activation.cuh:332-347 — gate_up [rows, 2 * inner] -> gelu(gate) * up [rows, inner] */
+int apxinf_static_geglu_bf16(const void* gate_up, void* output, int rows, int inner, void* stream);
+/* :140-150, fused.cuh:353-365 — output = projection + residual + bias */
+int apxinf_static_bias_residual_bf16(const void* projection, const void* bias, const void* residual,
+                                     void* output, int rows, int cols, void* stream);
+/* :173-185, fused.cuh:367-391 — hidden = bf16(projection + residual + bias); normalized = RMSNorm(hidden) * weight */
+int apxinf_static_bias_residual_rms_norm_bf16(const void* projection, const void* bias, const void* residual,
+                                              const void* weight, void* hidden, void* normalized, int rows,
+                                              int cols, float eps, void* stream);
+/* :187-201, fused.cuh:393-426 — the same with LayerNorm(hidden) * norm_weight + norm_bias */
+int apxinf_static_bias_residual_layer_norm_bf16(const void* projection, const void* projection_bias,
+                                                const void* residual, const void* norm_weight,
+                                                const void* norm_bias, void* hidden, void* normalized,
+                                                int rows, int cols, float eps, void* stream);
+/* :213-223, fused.cuh:428-441 — output = residual + projection * style[2 * cols + col] (style = scale | shift | gate) */
+int apxinf_static_ada_gate_residual_bf16(const void* projection, const void* residual, const void* style,
+                                         void* output, int rows, int cols, void* stream);
+/* :225-237, fused.cuh:443-469 — hidden as above with gate_style; normalized = adaRMSNorm(hidden; norm_style) */
+int apxinf_static_ada_gate_residual_rms_norm_bf16(const void* projection, const void* residual,
+                                                  const void* gate_style, const void* norm_style, void* hidden,
+                                                  void* normalized, int rows, int cols, float eps, void* stream);
+/* :239-252, fused.cuh:471-525 — splits [tokens, (q_heads + 2 kv_heads) * head_dim] (+ bias), rotates q and k
+ * (rotate-half, position_offset + token, base theta), writes q [tokens, q_heads, head_dim] and k, v
+ * rows at kv_output_offset + token of [*, kv_heads, head_dim] */
+int apxinf_static_qkv_rope_bf16(const void* qkv, const void* bias, void* q, void* k, void* v, int tokens,
+                                int q_heads, int kv_heads, int head_dim, float theta, int position_offset,
+                                int kv_output_offset, void* stream);
+/* :254-263, fused.cuh:527-544 — [tokens, 3 * width] (+ bias) -> q, k, v [tokens, width] */
+int apxinf_static_qkv_split_bias_bf16(const void* qkv, const void* bias, void* q, void* k, void* v, int tokens,
+                                      int projection_width, void* stream);
+/* :294-306, elementwise.cuh:168-182 — output = projection + position[token % tokens_per_view] + bias */
+int apxinf_static_bias_position_bf16(const void* projection, const void* bias, const void* position,
+                                     void* output, int rows, int cols, int tokens_per_view, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -211,3 +211,68 @@ def test_e4m3_codec_reference_kernel_against_the_oracle_for_every_f16_input():
         same = got == want
         # +0 and -0 are distinct bytes with the same value
         assert np.all(same | ((got & 0x7F) == 0) & ((want & 0x7F) == 0))
+
+
+def _both(name, build_args, outputs, tolerance_ulps=0.0):
+    """Runs `name` from the reference library and from this one on the same inputs;
+    `build_args(outs)` returns the argument tuple for a list of output tensors."""
+    results = []
+    for handle in (ref_ops.lib("bf16"), _ours()):
+        outs = [torch.full_like(o, 3.0) for o in outputs]
+        _call(handle, name, *build_args(outs), _stream())
+        results.append([_np(o) for o in outs])
+    for ref, ours in zip(*results):
+        if tolerance_ulps == 0.0:
+            assert np.array_equal(ours, ref), name
+        else:
+            assert _ulps(ours, ref, floor=2.0 ** -6) <= tolerance_ulps, name
+
+
+def test_remaining_static_row_operators_match_the_reference_kernels():
+    rng = np.random.default_rng(9)
+    rows, cols, inner = 37, 1152, 512
+    x, res = _bf16(rng, rows, cols), _bf16(rng, rows, cols)
+    bias, weight, nbias = _bf16(rng, cols), _bf16(rng, cols, scale=0.5), _bf16(rng, cols, scale=0.5)
+    style, style2 = _bf16(rng, 3 * cols, scale=0.3), _bf16(rng, 3 * cols, scale=0.3)
+    out = torch.zeros(rows, cols, dtype=torch.bfloat16, device="cuda")
+    for activation, ulps in ((0, 0.0), (1, 1.0), (2, 1.0)):
+        _both("apxinf_static_bias_activation_bf16",
+              lambda o: (_p(x), _p(bias), _p(o[0]), rows, cols, activation), [out], ulps)
+    _both("apxinf_static_bias_activation_bf16", lambda o: (_p(x), None, _p(o[0]), rows, cols, 0), [out])
+    _both("apxinf_static_bias_residual_bf16", lambda o: (_p(x), _p(bias), _p(res), _p(o[0]), rows, cols), [out])
+    _both("apxinf_static_ada_gate_residual_bf16", lambda o: (_p(x), _p(res), _p(style), _p(o[0]), rows, cols), [out])
+    pos = _bf16(rng, 16, cols)
+    _both("apxinf_static_bias_position_bf16", lambda o: (_p(x), _p(bias), _p(pos), _p(o[0]), rows, cols, 16), [out])
+    gate_up = _bf16(rng, rows, 2 * inner, scale=2.0)
+    _both("apxinf_static_geglu_bf16", lambda o: (_p(gate_up), _p(o[0]), rows, inner),
+          [torch.zeros(rows, inner, dtype=torch.bfloat16, device="cuda")], 1.0)
+    second = _bf16(rng, 5, cols)
+    _both("apxinf_static_concat_rows_bf16", lambda o: (_p(x), _p(second), _p(o[0]), rows, 5, cols),
+          [torch.zeros(rows + 5, cols, dtype=torch.bfloat16, device="cuda")])
+    eps = C.c_float(1e-6)
+    _both("apxinf_static_bias_residual_rms_norm_bf16",
+          lambda o: (_p(x), _p(bias), _p(res), _p(weight), _p(o[0]), _p(o[1]), rows, cols, eps), [out, out], 1.0)
+    _both("apxinf_static_bias_residual_layer_norm_bf16",
+          lambda o: (_p(x), _p(bias), _p(res), _p(weight), _p(nbias), _p(o[0]), _p(o[1]), rows, cols, eps),
+          [out, out], 1.0)
+    _both("apxinf_static_ada_gate_residual_rms_norm_bf16",
+          lambda o: (_p(x), _p(res), _p(style), _p(style2), _p(o[0]), _p(o[1]), rows, cols, eps), [out, out], 1.0)
+
+
+def test_remaining_static_split_operators_match_the_reference_kernels():
+    rng = np.random.default_rng(10)
+    tokens, qh, kvh, hd, offset = 10, 8, 1, 256, 522
+    qkv = _bf16(rng, tokens, (qh + 2 * kvh) * hd)
+    bias = _bf16(rng, (qh + 2 * kvh) * hd, scale=0.1)
+    q = torch.zeros(tokens, qh, hd, dtype=torch.bfloat16, device="cuda")
+    kv = torch.zeros(offset + tokens, kvh, hd, dtype=torch.bfloat16, device="cuda")
+    for b in (None, bias):
+        _both("apxinf_static_qkv_rope_bf16",
+              lambda o: (_p(qkv), _p(b), _p(o[0]), _p(o[1]), _p(o[2]), tokens, qh, kvh, hd, C.c_float(10000.0),
+                         offset, offset), [q, kv, kv], 1.0)
+    width = 1152
+    packed = _bf16(rng, 20, 3 * width)
+    pb = _bf16(rng, 3 * width)
+    third = torch.zeros(20, width, dtype=torch.bfloat16, device="cuda")
+    _both("apxinf_static_qkv_split_bias_bf16",
+          lambda o: (_p(packed), _p(pb), _p(o[0]), _p(o[1]), _p(o[2]), 20, width), [third, third, third])
