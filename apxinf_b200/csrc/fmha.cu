@@ -3,6 +3,7 @@
 #include <algorithm>
 
 #include "fmha_split.cuh"
+#include "fmha_online.cuh"
 #include "fmha_umma.cuh"
 
 namespace pi05 {
@@ -87,6 +88,7 @@ int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
   }
   plan->grid = dim3(static_cast<unsigned>(std::min<long long>(items, sms)), 1, 1);
   cudaFuncSetAttribute(fmha_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFmhaSmemBytes);
+  cudaFuncSetAttribute(fmha_online_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFmhaSmemBytes);
   return kPi05Ok;
 }
 
@@ -97,6 +99,11 @@ cudaError_t fmha_plan_launch(const FmhaPlan& plan, cudaStream_t stream) {
     if (err != cudaSuccess) return err;
     return launch_pdl(fmha_combine_kernel, plan.combine_grid, dim3(256), 0, stream, plan.params,
                       static_cast<const float*>(plan.split_scratch));
+  }
+  if (plan.params.keys > kFmhaKeyBlock) {
+    // more than one key block: one pass with a running maximum (fmha_online.cuh)
+    return launch_pdl(fmha_online_kernel, plan.grid, dim3(kFmhaThreads), kFmhaSmemBytes, stream,
+                      plan.tmap_q, plan.tmap_k, plan.tmap_v, plan.params);
   }
   return launch_pdl(fmha_umma_kernel, plan.grid, dim3(kFmhaThreads), kFmhaSmemBytes, stream,
                     plan.tmap_q, plan.tmap_k, plan.tmap_v, plan.params);
