@@ -339,3 +339,21 @@ def test_gemm_split_k_geglu(M, swap):
     assert st.item() == 0
     err = (out.float().cpu() - want).abs()
     assert (err <= want.abs() * 2 ** -6 + 2e-2).all(), err.max().item()
+
+
+@pytest.mark.parametrize("M,N,Kd,batch", [(2560, 2048, 16384, 1), (2000, 1152, 32768, 1), (700, 640, 256, 3)])
+def test_persistent_kernel_raster_groups_cover_every_tile(M, N, Kd, batch):
+    """More tiles than SMs: the persistent kernel walks row tiles in groups sized to L2 (with
+    the long K ranges here the groups are 8 to 12 row tiles, the last one ragged); INT8
+    accumulators are exact, so a tile visited twice, skipped or swapped shows up."""
+    L, K = _lib()
+    gen = torch.Generator().manual_seed(M + N)
+    a = torch.randint(-8, 9, (batch, M, Kd), generator=gen, dtype=torch.int8)
+    b = torch.randint(-8, 9, (batch, N, Kd), generator=gen, dtype=torch.int8)
+    ad, bd = a.cuda(), b.cuda()
+    out = torch.full((batch, M, N), -7, dtype=torch.int32, device="cuda")
+    st = K.gemm(ad, bd, out, op=L.OP_S8, out_type=L.OUT_S32)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    want = torch.matmul(ad.float(), bd.float().transpose(1, 2)).round().to(torch.int32)  # exact: |sum| < 2^24
+    assert torch.equal(out, want)
