@@ -327,6 +327,9 @@ def run_ours(args):
         }
         # ---- B=1 latency, the other half of the headline ----
         latency = measure_latency(rt_dtype="fp8", device=local)
+        # the other two precisions of the path, same protocol (p50 only)
+        latency["other_precisions_p50_ms"] = {
+            dtype: measure_latency(rt_dtype=dtype, device=local)["p50_ms"] for dtype in ("bf16", "int8")}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": device_seconds / args.steps * 1e3,
@@ -356,7 +359,7 @@ def run_ours(args):
 
 
 def measure_latency(rt_dtype, device):
-    """B=1 two-view FP8 graph-replay latency (pi05_bench protocol: 10 warm-ups, 30 replays)."""
+    """B=1 two-view graph-replay latency (pi05_bench protocol: 10 warm-ups, 30 replays)."""
     from apxinf_b200.engine import Pi05Config, Pi05Runtime
     from apxinf_b200.fixtures import synthetic_observation
     cfg = Pi05Config()
@@ -372,7 +375,7 @@ def measure_latency(rt_dtype, device):
     out = graph.infer_host(images[None], tokens[None], noise[None])
     update_plus_graph = (time.perf_counter() - t0) * 1e3
     stages = graph.stage_times()
-    result = {"workload": "cfg3: FP8, B=1, 2 views, 10 tokens, H=10, 10 flow steps",
+    result = {"workload": f"cfg{dict(bf16=2, fp8=3, int8=3)[rt_dtype]}: {rt_dtype.upper()}, B=1, 2 views, 10 tokens, H=10, 10 flow steps",
               "p50_ms": float(ms[len(ms) // 2]), "p95_ms": float(ms[int(round(0.95 * (len(ms) - 1)))]),
               "min_ms": float(ms[0]), "max_ms": float(ms[-1]),
               "input_update_plus_graph_ms": update_plus_graph, "launches": graph.num_launches(),
