@@ -44,7 +44,8 @@ int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
   }
   if (rc != kPi05Ok) return rc;
   rc = encode_operand_map(&plan->tmap_k, kOpBf16, q.k, q.head_dim, q.keys, pack > 1 ? 1 : q.nb0, q.nb1,
-                          q.k_ld, q.k_sb0, q.k_sb1, 64, q.key_split ? kSplitKeys : 256);
+                          q.k_ld, q.k_sb0, q.k_sb1, 64,
+                          q.key_split ? kSplitKeys : q.keys > kFmhaKeyBlock ? kOnlineKeyBlock : kFmhaKeyBlock);
   if (rc != kPi05Ok) return rc;
   rc = encode_operand_map(&plan->tmap_v, kOpBf16, q.v, q.head_dim, q.keys, pack > 1 ? 1 : q.nb0, q.nb1,
                           q.v_ld, q.v_sb0, q.v_sb1, 64, 64);
@@ -88,7 +89,7 @@ int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
   }
   plan->grid = dim3(static_cast<unsigned>(std::min<long long>(items, sms)), 1, 1);
   cudaFuncSetAttribute(fmha_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFmhaSmemBytes);
-  cudaFuncSetAttribute(fmha_online_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFmhaSmemBytes);
+  cudaFuncSetAttribute(fmha_online_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kOnlineSmemBytes);
   return kPi05Ok;
 }
 
@@ -102,7 +103,7 @@ cudaError_t fmha_plan_launch(const FmhaPlan& plan, cudaStream_t stream) {
   }
   if (plan.params.keys > kFmhaKeyBlock) {
     // more than one key block: one pass with a running maximum (fmha_online.cuh)
-    return launch_pdl(fmha_online_kernel, plan.grid, dim3(kFmhaThreads), kFmhaSmemBytes, stream,
+    return launch_pdl(fmha_online_kernel, plan.grid, dim3(kFmhaThreads), kOnlineSmemBytes, stream,
                       plan.tmap_q, plan.tmap_k, plan.tmap_v, plan.params);
   }
   return launch_pdl(fmha_umma_kernel, plan.grid, dim3(kFmhaThreads), kFmhaSmemBytes, stream,

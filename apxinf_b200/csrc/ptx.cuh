@@ -166,6 +166,20 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
   }
 }
 
+// kind::f16 MMA whose A operand sits in TMEM (128 lanes = rows, two 16-bit K elements per
+// 32-bit column, 8 columns per K step of 16); B from shared memory as usual.
+__device__ __forceinline__ void umma_f16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // TMEM -> registers: this warp's 32 lanes x 16 consecutive 32-bit columns.
 __device__ __forceinline__ void tmem_ld_16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
