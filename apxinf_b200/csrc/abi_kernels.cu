@@ -81,8 +81,6 @@ extern "C" int pi05_attention(const Pi05AttentionArgs* args, void* cuda_stream) 
   f.out_e4m3 = args->out_e4m3 != 0;
   f.out_inv_scale = args->out_inv_scale;
   f.status = args->status;
-  f.trace = reinterpret_cast<unsigned int*>(args->trace);
-  f.trace_item = args->trace_item;
   f.key_split = args->key_split != 0;
   f.split_scratch = static_cast<float*>(args->split_scratch);
   f.split_scratch_bytes = static_cast<size_t>(args->split_scratch_bytes);

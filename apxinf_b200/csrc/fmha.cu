@@ -4,7 +4,6 @@
 
 #include "fmha_split.cuh"
 #include "fmha_online.cuh"
-#include "fmha_umma.cuh"
 
 namespace pi05 {
 
@@ -45,7 +44,7 @@ int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
   if (rc != kPi05Ok) return rc;
   rc = encode_operand_map(&plan->tmap_k, kOpBf16, q.k, q.head_dim, q.keys, pack > 1 ? 1 : q.nb0, q.nb1,
                           q.k_ld, q.k_sb0, q.k_sb1, 64,
-                          q.key_split ? kSplitKeys : q.keys > kFmhaKeyBlock ? kOnlineKeyBlock : kFmhaKeyBlock);
+                          q.key_split ? kSplitKeys : kOnlineKeyBlock);
   if (rc != kPi05Ok) return rc;
   rc = encode_operand_map(&plan->tmap_v, kOpBf16, q.v, q.head_dim, q.keys, pack > 1 ? 1 : q.nb0, q.nb1,
                           q.v_ld, q.v_sb0, q.v_sb1, 64, 64);
@@ -65,8 +64,6 @@ int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
   p.out_e4m3 = q.out_e4m3 ? 1 : 0;
   p.out_inv_scale = q.out_inv_scale;
   p.status = q.status;
-  p.trace = q.trace;
-  p.trace_item = q.trace_item;
   const int tile_tokens = 128 / pack;
   const long long items =
       (long long)((q.q_rows + tile_tokens - 1) / tile_tokens) * (pack > 1 ? 1 : q.nb0) * q.nb1;
@@ -88,7 +85,6 @@ int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
     return kPi05Ok;
   }
   plan->grid = dim3(static_cast<unsigned>(std::min<long long>(items, sms)), 1, 1);
-  cudaFuncSetAttribute(fmha_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFmhaSmemBytes);
   cudaFuncSetAttribute(fmha_online_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kOnlineSmemBytes);
   return kPi05Ok;
 }
@@ -101,12 +97,7 @@ cudaError_t fmha_plan_launch(const FmhaPlan& plan, cudaStream_t stream) {
     return launch_pdl(fmha_combine_kernel, plan.combine_grid, dim3(256), 0, stream, plan.params,
                       static_cast<const float*>(plan.split_scratch));
   }
-  if (plan.params.keys > kFmhaKeyBlock) {
-    // more than one key block: one pass with a running maximum (fmha_online.cuh)
-    return launch_pdl(fmha_online_kernel, plan.grid, dim3(kFmhaThreads), kOnlineSmemBytes, stream,
-                      plan.tmap_q, plan.tmap_k, plan.tmap_v, plan.params);
-  }
-  return launch_pdl(fmha_umma_kernel, plan.grid, dim3(kFmhaThreads), kFmhaSmemBytes, stream,
+  return launch_pdl(fmha_online_kernel, plan.grid, dim3(kFmhaThreads), kOnlineSmemBytes, stream,
                     plan.tmap_q, plan.tmap_k, plan.tmap_v, plan.params);
 }
 

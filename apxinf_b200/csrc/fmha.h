@@ -1,4 +1,4 @@
-// Host side of the fused attention kernel (fmha_umma.cuh): plan = three TMA maps + parameters.
+// Host side of the fused attention kernels (fmha_online.cuh, fmha_split.cuh): plan = TMA maps + parameters.
 #pragma once
 
 #include <cuda.h>
@@ -22,8 +22,6 @@ struct FmhaParams {
   int out_e4m3;
   float out_inv_scale;
   int* status;
-  unsigned int* trace;  // optional device uint32[32]: SM-clock phase stamps of CTA 0's trace_item-th tile
-  int trace_item;
 };
 
 
@@ -44,8 +42,6 @@ struct FmhaProblem {
   bool out_e4m3 = false;
   float out_inv_scale = 1.0f;
   int* status = nullptr;
-  unsigned int* trace = nullptr;
-  int trace_item = 0;
   // key-split path (fmha_split.cuh): one CTA per (query tile, 64-key slice) plus a combine
   // launch; needs fmha_split_scratch_bytes() of device scratch
   bool key_split = false;

@@ -1,9 +1,19 @@
-// Fused attention for more than 256 keys (prefix and batched action-expert MQA: 522 to 572
-// keys, head_dim 256): one pass over 128-key blocks with a running row maximum, the
-// probabilities kept in TENSOR MEMORY.
+// Fused attention for the PI0.5 forward on tcgen05 tensor cores: softmax(scale * Q K^T) V in one
+// launch, for the three attention shapes of the model
+//   SigLIP       per (image, head): 256 queries x 256 keys, head_dim 72
+//   prefix MQA   per sample: (tokens x 8 heads) query rows share one K/V head, head_dim 256
+//   action MQA   per sample: (horizon x 8 heads) rows over the prefix + action KV cache
+// No mask; at most 1024 keys. Replaces the QK^T GEMM -> row softmax -> PV GEMM chain (and with it
+// the logits round trip through HBM) that the reference runs through cuBLAS
+// (crates/apxinf-cuda/adapters/cublas_adapter.cu:89-132) or its FMHA / FA2 kernels
+// (crates/apxinf-cuda/kernels/cutlass/fmha_sm100.cu, fa2_bf16_sm80.cu).
 //
-// Same tiles, operands, packing and warp roles as fmha_umma_kernel (which keeps the single-block
-// case). TMEM: two 128-column score buffers and the 256-column output accumulator. Per block j
+// CTAs are persistent (one per SM) and walk 128-row query tiles; multi-query heads that share a
+// K/V head are packed into one tile (row = token * heads + head). One pass over 128-key blocks
+// with a running row maximum, the probabilities kept in TENSOR MEMORY. Warp roles: 0 = TMA
+// producer, 1 = MMA issuer, 2..17 = softmax / epilogue: four warps per TMEM lane quarter
+// (thread = query row), each owning 32 key columns of every block and 64 output columns.
+// TMEM: two 128-column score buffers and the 256-column output accumulator. Per block j
 // (buffer b = j & 1):
 //   MMA warp      S_j = Q K_j^T (UMMA 128 x 128) into buffer b; S_{j+2} follows PV_j
 //   softmax warps pull their 32 score columns into registers, exchange the block maximum
@@ -14,15 +24,16 @@
 //   MMA warp      O += P_j V_j with the A operand read from TMEM and V MN-major from the
 //                 [keys, head_dim] cache
 // With no probability tile in shared memory the K/V ring has four 32 KB stages beside the 64 KB
-// query tile (two in the version that staged P in shared memory): bytes in flight through TMA
-// are what bounds this kernel.
+// query tile: bytes in flight through TMA are what bounds this kernel. (Earlier forms: two
+// passes with the probabilities staged in shared memory and a two-stage ring, then one pass
+// with them still in shared memory.)
 #pragma once
 
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
 #include "fmha.h"
-#include "fmha_umma.cuh"
+#include "fmha_common.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
 

@@ -7,13 +7,14 @@
 // Two dependent launches of a few microseconds replace the QK^T GEMM -> softmax -> PV GEMM
 // chain, and nine times as many SMs pull the K/V cache as the unsplit kernel would use.
 // Same operands, tile packing (multi-query heads share a tile) and output conventions as
-// fmha_umma_kernel.
+// fmha_online_kernel.
 #pragma once
 
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
 #include "fmha.h"
+#include "fmha_common.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
 

@@ -156,8 +156,8 @@ typedef struct Pi05AttentionArgs {
   int32_t out_e4m3;
   float out_inv_scale;
   int32_t* status; /* device int32, 0 before the call */
-  uint32_t* trace; /* optional device uint32[32]: SM-clock phase stamps of CTA 0; NULL = off */
-  int32_t trace_item; /* which of CTA 0's query tiles (0 = first) is stamped */
+  uint32_t* trace;    /* reserved (phase stamps of an earlier kernel): pass NULL */
+  int32_t trace_item; /* reserved: pass 0 */
   /* key_split != 0: one CTA per (query tile, 64-key slice) writes partial outputs to
    * split_scratch and a second launch combines them; for calls with few query tiles.
    * split_scratch needs tiles * ceil(keys / 64) * 128 * (head_dim + 2) * 4 bytes
