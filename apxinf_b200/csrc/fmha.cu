@@ -64,6 +64,7 @@ int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
   p.out_e4m3 = q.out_e4m3 ? 1 : 0;
   p.out_inv_scale = q.out_inv_scale;
   p.status = q.status;
+  p.rescale_threshold = 8.0f;
   const int tile_tokens = 128 / pack;
   const long long items =
       (long long)((q.q_rows + tile_tokens - 1) / tile_tokens) * (pack > 1 ? 1 : q.nb0) * q.nb1;

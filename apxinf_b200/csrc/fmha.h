@@ -22,6 +22,7 @@ struct FmhaParams {
   int out_e4m3;
   float out_inv_scale;
   int* status;
+  float rescale_threshold;  // running maximum moves only past this many powers of two (fused kernel)
 };
 
 

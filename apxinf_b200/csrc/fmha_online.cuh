@@ -299,8 +299,13 @@ fmha_online_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         ptx::tc_fence_after();
         const float block_max = fmaxf(fmaxf(xm[row_in_tile], xm[128 + row_in_tile]),
                                       fmaxf(xm[256 + row_in_tile], xm[384 + row_in_tile]));
-        const float new_max = fmaxf(run_max, block_max);
-        // block 0 always has a valid key, so run_max is finite from block 1 on
+        // The reference maximum only moves when the block maximum exceeds it by more than 2^8 in
+        // the exponent (probabilities then stay below 256, well inside bf16 and fp32 range, and
+        // the final division by the row sum cancels the choice exactly): most blocks need no
+        // rescaling of O. Every column group of a row sees the same numbers and decides alike.
+        // Block 0 always has a valid key, so run_max is finite from block 1 on.
+        const bool keep = j > 0 && (block_max - run_max) * scale_log2 <= p.rescale_threshold;
+        const float new_max = keep ? run_max : fmaxf(run_max, block_max);
         const float alpha = j == 0 ? 0.0f : exp2f((run_max - new_max) * scale_log2);
         run_max = new_max;
         const float max_log2 = new_max * scale_log2;
@@ -321,10 +326,11 @@ fmha_online_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
         row_sum = row_sum * alpha + partial;
         ptx::tmem_st_16(buf + group * 16, packed);
-        // PV_{j-1} (of this tile or the last one of the previous tile) must be done before O is rescaled
-        if (p_blocks > 0 && ok) ok = ptx::mbar_wait(p_free, (p_blocks - 1) & 1);
-        ptx::tc_fence_after();
         if (j > 0 && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+          // PV_{j-1} must be done before O is rescaled (no other reason to wait for it: P_j sits
+          // in the other score buffer and PV products accumulate in issue order)
+          if (ok) ok = ptx::mbar_wait(p_free, (p_blocks - 1) & 1);
+          ptx::tc_fence_after();
 #pragma unroll 1
           for (int cc = 4 * group; cc < min(4 * group + 4, n_pv / 16); cc += 2) {
             uint32_t o[2][16];
