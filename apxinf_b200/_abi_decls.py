@@ -19,6 +19,12 @@ class ModelConfig(C.Structure):
         + [("language", Gemma), ("action_expert", Gemma)])
 
 
+class EngineOptions(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("device", C.c_int32), ("seed", C.c_uint64),
+                ("act_scale", C.c_float), ("weight_dist", C.c_int32),
+                ("int8_activations", C.c_int32)]
+
+
 _P = C.c_void_p
 _SZ = C.c_size_t
 
@@ -26,6 +32,10 @@ PROTOTYPES = [
     ("pi05_default_config", None, [C.POINTER(ModelConfig)]),
     ("pi05_engine_create", C.c_int,
      [C.POINTER(ModelConfig), C.c_int32, C.c_int32, C.c_uint64, C.c_float, C.POINTER(_P)]),
+    ("pi05_engine_create_ex", C.c_int,
+     [C.POINTER(ModelConfig), C.POINTER(EngineOptions), C.POINTER(_P)]),
+    ("pi05_engine_set_activation_scale", C.c_int, [_P, C.c_char_p, C.c_float]),
+    ("pi05_engine_activation_scale", C.c_float, [_P, C.c_char_p]),
     ("pi05_engine_destroy", None, [_P]),
     ("pi05_engine_weight_bytes", _SZ, [_P]),
     ("pi05_engine_read_weight", C.c_int, [_P, C.c_char_p, _P, _SZ, C.POINTER(_SZ)]),

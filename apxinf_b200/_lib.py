@@ -53,7 +53,7 @@ class GemmArgs(C.Structure):
         ("force_swap", C.c_int32), ("force_block_n", C.c_int32),
         ("partials", C.c_void_p), ("partials_bytes", C.c_uint64),
         ("tile_counters", C.c_void_p), ("max_tiles", C.c_int32), ("force_split_k", C.c_int32),
-        ("trace", C.c_void_p), ("b_blocked", C.c_int32),
+        ("b_blocked", C.c_int32),
     ]
 
 

@@ -71,16 +71,28 @@ extern "C" void pi05_default_config(Pi05ModelConfig* c) {
   c->action_expert = gemma(m.action);
 }
 
-extern "C" int pi05_engine_create(const Pi05ModelConfig* config, int32_t dtype, int32_t device,
-                                  uint64_t seed, float fp8_act_scale, Pi05Engine** out) {
-  if (config == nullptr || out == nullptr || device < 0) return pi05::kPi05ErrInvalidValue;
+extern "C" int pi05_engine_create_ex(const Pi05ModelConfig* config, const Pi05EngineOptions* options,
+                                     Pi05Engine** out) {
+  if (config == nullptr || options == nullptr || out == nullptr || options->device < 0) {
+    return pi05::kPi05ErrInvalidValue;
+  }
   *out = nullptr;
   int count = 0;
-  if (cudaGetDeviceCount(&count) != cudaSuccess || device >= count) {
+  if (cudaGetDeviceCount(&count) != cudaSuccess || options->device >= count) {
     return pi05::record_cuda(cudaErrorNoDevice);
   }
-  auto* impl = new (std::nothrow) pi05::Engine(to_internal(*config), dtype, device, seed,
-                                               dtype == PI05_DTYPE_FP8 ? fp8_act_scale : 1.0f);
+  pi05::EngineOptions o;
+  o.precision = options->dtype;
+  o.device = options->device;
+  o.seed = options->seed;
+  o.weight_dist = options->weight_dist;
+  o.int8_activations = options->int8_activations;
+  // the uniform scale matters to the precisions with static activation scales only
+  const bool uses_scale = options->dtype == PI05_DTYPE_FP8 ||
+                          (options->dtype == PI05_DTYPE_INT8 &&
+                           options->int8_activations == PI05_INT8_ACT_STATIC);
+  o.act_scale = uses_scale ? options->act_scale : 1.0f;
+  auto* impl = new (std::nothrow) pi05::Engine(to_internal(*config), o);
   if (impl == nullptr) return pi05::kPi05ErrInvalidValue;
   const int rc = impl->init();
   if (rc != pi05::kPi05Ok) {
@@ -89,6 +101,28 @@ extern "C" int pi05_engine_create(const Pi05ModelConfig* config, int32_t dtype, 
   }
   *out = new Pi05Engine{impl};
   return pi05::kPi05Ok;
+}
+
+extern "C" int pi05_engine_create(const Pi05ModelConfig* config, int32_t dtype, int32_t device,
+                                  uint64_t seed, float fp8_act_scale, Pi05Engine** out) {
+  Pi05EngineOptions options = {};
+  options.dtype = dtype;
+  options.device = device;
+  options.seed = seed;
+  options.act_scale = fp8_act_scale;
+  options.weight_dist = PI05_WEIGHTS_LCG;
+  options.int8_activations = PI05_INT8_ACT_DYNAMIC;
+  return pi05_engine_create_ex(config, &options, out);
+}
+
+extern "C" int pi05_engine_set_activation_scale(Pi05Engine* engine, const char* site, float scale) {
+  if (engine == nullptr || site == nullptr) return pi05::kPi05ErrInvalidValue;
+  return engine->impl->set_scale(site, scale);
+}
+
+extern "C" float pi05_engine_activation_scale(const Pi05Engine* engine, const char* site) {
+  if (engine == nullptr || site == nullptr) return 0.0f;
+  return engine->impl->scale_of(site);
 }
 
 extern "C" void pi05_engine_destroy(Pi05Engine* engine) {

@@ -59,7 +59,6 @@ extern "C" int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream) {
   q.tile_counters = args->tile_counters;
   q.max_tiles = args->max_tiles;
   q.force_split_k = args->force_split_k;
-  q.trace = args->trace;
   q.b_blocked = args->b_blocked != 0;
   GemmPlan plan;
   const int rc = gemm_plan_build(q, &plan);

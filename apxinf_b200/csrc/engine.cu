@@ -77,8 +77,30 @@ int ModelConfig::validate() const {
 // Engine: weights
 // ---------------------------------------------------------------------------
 
-Engine::Engine(const ModelConfig& cfg, int precision, int device, uint64_t seed, float act_scale)
-    : cfg_(cfg), prec_(precision), device_(device), seed_(seed), act_scale_(act_scale) {}
+Engine::Engine(const ModelConfig& cfg, const EngineOptions& options)
+    : cfg_(cfg), prec_(options.precision), device_(options.device), seed_(options.seed),
+      act_scale_(options.act_scale), weight_dist_(options.weight_dist),
+      int8_static_(options.int8_activations == kInt8Static) {}
+
+cudaError_t Engine::fill(void* dst_bf16, long long count) {
+  const cudaError_t err = weight_dist_ == kWeightsNormal
+                              ? launch_normal_fill(dst_bf16, seed_, cursor_, count, stream_)
+                              : launch_lcg_fill(dst_bf16, seed_, cursor_, count, stream_);
+  cursor_ += static_cast<uint64_t>(count);
+  return err;
+}
+
+float Engine::scale_of(const std::string& site) const {
+  auto it = site_scales_.find(site);
+  return it == site_scales_.end() ? act_scale_ : it->second;
+}
+
+int Engine::set_scale(const std::string& site, float value) {
+  auto it = site_scales_.find(site);
+  if (it == site_scales_.end() || !(value > 0.0f) || !std::isfinite(value)) return kPi05ErrInvalidValue;
+  it->second = value;
+  return kPi05Ok;
+}
 
 Engine::~Engine() {
   cudaSetDevice(device_);
@@ -93,6 +115,13 @@ void* Engine::dmalloc(size_t bytes) {
   allocations_.push_back(p);
   weight_bytes_ += bytes;
   return p;
+}
+
+void Engine::release(void* p) {
+  if (p == nullptr) return;
+  auto it = std::find(allocations_.begin(), allocations_.end(), p);
+  if (it != allocations_.end()) allocations_.erase(it);
+  cudaFree(p);
 }
 
 int Engine::make_linear(const std::string& prefix, const std::vector<std::string>& parts, int k,
@@ -118,14 +147,11 @@ int Engine::make_linear(const std::string& prefix, const std::vector<std::string
   for (size_t i = 0; i < parts.size(); ++i) {
     const long long count = static_cast<long long>(k) * ns[i];
     if (static_cast<size_t>(count) * 2 > tmp_src_bytes_) return kPi05ErrInvalidValue;
-    PI05_CUDA(launch_lcg_fill(tmp_src_, seed_, cursor_, count, stream_));
-    cursor_ += static_cast<uint64_t>(count);
+    PI05_CUDA(fill(tmp_src_, count));
     PI05_CUDA(launch_transpose_pack(tmp_src_, stage, k, ns[i], ldk, row_offset,
                                     interleave ? 1 : 0, static_cast<int>(i), stream_));
     if (bias) {
-      PI05_CUDA(launch_lcg_fill(static_cast<uint16_t*>(out->bias) + row_offset, seed_, cursor_,
-                                ns[i], stream_));
-      cursor_ += static_cast<uint64_t>(ns[i]);
+      PI05_CUDA(fill(static_cast<uint16_t*>(out->bias) + row_offset, ns[i]));
     }
     row_offset += ns[i];
   }
@@ -144,6 +170,24 @@ int Engine::make_linear(const std::string& prefix, const std::vector<std::string
 int Engine::init() {
   PI05_TRY(cfg_.validate());
   if (prec_ < kPrecBf16 || prec_ > kPrecInt8 || !(act_scale_ > 0.0f)) return kPi05ErrInvalidValue;
+  if (weight_dist_ != kWeightsLcg && weight_dist_ != kWeightsNormal) return kPi05ErrInvalidValue;
+  // every activation-scale site starts at the uniform scale
+  site_scales_.clear();
+  const char* kLayerSites[4] = {"attention_norm", "attention_output", "mlp_norm", "mlp_activation"};
+  auto add_layers = [&](const char* prefix, int depth) {
+    for (int i = 0; i < depth; ++i) {
+      for (const char* part : kLayerSites) {
+        site_scales_[std::string(prefix) + ".layers." + std::to_string(i) + "." + part] = act_scale_;
+      }
+    }
+  };
+  add_layers("vision", cfg_.vision_depth);
+  add_layers("language", cfg_.language.depth);
+  add_layers("action", cfg_.action.depth);
+  for (const char* name : {"vision.patch_input", "vision.post_norm", "action.input", "time.input",
+                           "time.hidden", "action.conditioning", "action.final_norm"}) {
+    site_scales_[name] = act_scale_;
+  }
   PI05_CUDA(cudaSetDevice(device_));
   PI05_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
   status_ = static_cast<int*>(dmalloc(256));
@@ -195,12 +239,17 @@ int Engine::init() {
   consider(ac.width, 3 * ac.width, 3 * ac.width);
   consider(cfg_.action_dim, ac.width, ac.width);
   consider(ac.width, cfg_.action_dim, cfg_.action_dim);
-  PI05_CUDA(cudaMalloc(&tmp_src_, max_src));
+  // generation scratch is tracked like every other allocation, so a failed init frees it
+  // with the engine; the success path releases it early (see the end of this function)
+  tmp_src_ = dmalloc(max_src);
+  if (tmp_src_ == nullptr) return record_cuda(cudaErrorMemoryAllocation);
   tmp_src_bytes_ = max_src;
   if (prec_ != kPrecBf16) {
-    PI05_CUDA(cudaMalloc(&tmp_stage_, max_stage));
+    tmp_stage_ = dmalloc(max_stage);
+    if (tmp_stage_ == nullptr) return record_cuda(cudaErrorMemoryAllocation);
     tmp_stage_bytes_ = max_stage;
   }
+  weight_bytes_ -= max_src + (prec_ != kPrecBf16 ? max_stage : 0);
 
   // Generation order = Pi05Weights::synthetic (crates/apxinf-model/src/pi05/weights.rs:255-330).
   cursor_ = 0;
@@ -217,8 +266,7 @@ int Engine::init() {
     const long long count = static_cast<long long>(cfg_.patches_per_view()) * vw;
     position_embedding = dmalloc(count * 2);
     if (position_embedding == nullptr) return record_cuda(cudaErrorMemoryAllocation);
-    PI05_CUDA(launch_lcg_fill(position_embedding, seed_, cursor_, count, stream_));
-    cursor_ += count;
+    PI05_CUDA(fill(position_embedding, count));
     named_["vision.position_embedding"] = {position_embedding, (size_t)count * 2};
   }
   PI05_TRY(make_linear("vision.projector", {"w"}, vw, {lg.width}, true, false, &projector));
@@ -226,8 +274,7 @@ int Engine::init() {
     const long long count = static_cast<long long>(cfg_.vocab_size) * lg.width;
     token_embedding = dmalloc(count * 2);
     if (token_embedding == nullptr) return record_cuda(cudaErrorMemoryAllocation);
-    PI05_CUDA(launch_lcg_fill(token_embedding, seed_, cursor_, count, stream_));
-    cursor_ += count;
+    PI05_CUDA(fill(token_embedding, count));
     named_["token_embedding"] = {token_embedding, (size_t)count * 2};
   }
   language.resize(lg.depth);
@@ -256,9 +303,9 @@ int Engine::init() {
   PI05_TRY(make_linear("time_mlp_in", {"w"}, ac.width, {ac.width}, true, false, &time_in));
   PI05_TRY(make_linear("time_mlp_out", {"w"}, ac.width, {ac.width}, true, false, &time_out));
   PI05_CUDA(cudaStreamSynchronize(stream_));
-  cudaFree(tmp_src_);
+  release(tmp_src_);
   tmp_src_ = nullptr;
-  if (tmp_stage_ != nullptr) cudaFree(tmp_stage_);
+  release(tmp_stage_);
   tmp_stage_ = nullptr;
   return kPi05Ok;
 }
@@ -328,7 +375,8 @@ Act PreparedGraph::make_act(int rows, long long ld) {
   const int prec = e_->precision();
   a.data = arena_.alloc(static_cast<size_t>(rows) * ld * elem_size(prec));
   if (prec == kPrecInt8) {
-    a.row_scale = static_cast<float*>(arena_.alloc(static_cast<size_t>(rows) * 4));
+    a.row_scale = e_->static_int8() ? nullptr
+                                    : static_cast<float*>(arena_.alloc(static_cast<size_t>(rows) * 4));
     a.wide = arena_.alloc(static_cast<size_t>(rows) * ld * 2);
   }
   return a;
@@ -356,13 +404,13 @@ int PreparedGraph::linear(const char* name, const Act& in, int rows, const Linea
   q.residual = residual;
   q.bias = w.bias;
   q.col_scale = w.col_scale;
-  q.row_scale = prec == kPrecInt8 ? in.row_scale : nullptr;
+  q.row_scale = prec == kPrecInt8 && !e_->static_int8() ? in.row_scale : nullptr;
   q.row_scale_sb0 = nb0 > 1 ? rows : 0;
   q.pos = pos;
   q.pos_rows = pos_rows;
   q.pos_ld = w.n;
   q.gate = gate;
-  q.alpha = prec == kPrecFp8 ? e_->act_scale() : 1.0f;
+  q.alpha = e_->static_scales() ? in.scale : 1.0f;
   q.out_inv_scale = out_inv_scale;
   q.status = e_->status();
   q.b_static = true;
@@ -371,14 +419,19 @@ int PreparedGraph::linear(const char* name, const Act& in, int rows, const Linea
 
 // GEMM whose result feeds another GEMM: written in the precision's operand form.
 int PreparedGraph::linear_to_act(const char* name, const Act& in, int rows, const Linear& w,
-                                 int mode, Act* out) {
+                                 int mode, Act* out, const std::string& site) {
   const int prec = e_->precision();
-  const float inv = 1.0f / e_->act_scale();
+  out->scale = e_->scale_of(site);
+  const float inv = 1.0f / out->scale;
   if (prec == kPrecBf16) {
     return linear(name, in, rows, w, mode, out->data, out->ld, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f);
   }
   if (prec == kPrecFp8) {
     return linear(name, in, rows, w, mode, out->data, out->ld, kOutE4m3, nullptr, nullptr, nullptr, 1, inv);
+  }
+  if (e_->static_int8()) {
+    // static scale: the quantiser is part of the epilogue, like the FP8 path's
+    return linear(name, in, rows, w, mode, out->data, out->ld, kOutS8, nullptr, nullptr, nullptr, 1, inv);
   }
   PI05_TRY(linear(name, in, rows, w, mode, out->wide, out->ld, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
   const void* wide = out->wide;
@@ -391,8 +444,31 @@ int PreparedGraph::linear_to_act(const char* name, const Act& in, int rows, cons
   return kPi05Ok;
 }
 
+// bf16 tensor -> the precision's GEMM-input form (bf16: `out` aliases the source).
+void PreparedGraph::quantize_to_act(const char* name, const void* src, int rows, int cols, Act* out,
+                                    const std::string& site) {
+  const int prec = e_->precision();
+  out->scale = e_->scale_of(site);
+  const float inv = 1.0f / out->scale;
+  const long long count = static_cast<long long>(rows) * cols;
+  if (prec == kPrecBf16) {
+    out->data = const_cast<void*>(src);
+  } else if (prec == kPrecFp8) {
+    uint8_t* dst = static_cast<uint8_t*>(out->data);
+    add_kernel(name, [=](cudaStream_t s) { return launch_quantize_e4m3(src, dst, count, inv, s); });
+  } else if (e_->static_int8()) {
+    int8_t* dst = static_cast<int8_t*>(out->data);
+    add_kernel(name, [=](cudaStream_t s) { return launch_quantize_s8(src, dst, count, inv, s); });
+  } else {
+    int8_t* dst = static_cast<int8_t*>(out->data);
+    float* rs = out->row_scale;
+    add_kernel(name, [=](cudaStream_t s) { return launch_quantize_rows_int8(src, dst, rs, rows, cols, cols, cols, s); });
+  }
+}
+
 int PreparedGraph::norm_to_act(const char* name, const void* x, int rows, int cols, int kind,
-                               const void* style, float eps, Act* out) {
+                               const void* style, float eps, Act* out, const std::string& site) {
+  out->scale = e_->scale_of(site);
   NormArgs a{};
   a.input = x;
   a.output = out->data;
@@ -401,10 +477,13 @@ int PreparedGraph::norm_to_act(const char* name, const void* x, int rows, int co
   a.rows = rows;
   a.cols = cols;
   a.eps = eps;
-  a.inv_scale = 1.0f / e_->act_scale();
+  a.inv_scale = 1.0f / out->scale;
   a.kind = kind;
   const int prec = e_->precision();
-  a.out = prec == kPrecBf16 ? kRowBf16 : prec == kPrecFp8 ? kRowE4m3 : kRowInt8;
+  a.out = prec == kPrecBf16 ? kRowBf16
+          : prec == kPrecFp8 ? kRowE4m3
+          : e_->static_int8() ? kRowInt8Static
+                              : kRowInt8;
   add_kernel(name, [a](cudaStream_t s) { return launch_norm(a, s); });
   return kPi05Ok;
 }
@@ -440,7 +519,7 @@ int PreparedGraph::attention(const char* name, const void* q, long long q_ld, lo
       f.q_rows = q_rows; f.keys = keys; f.head_dim = head_dim; f.nb0 = nb0; f.nb1 = nb1;
       f.scale = scale;
       f.out_e4m3 = prec_now == kPrecFp8;
-      f.out_inv_scale = 1.0f / e_->act_scale();
+      f.out_inv_scale = 1.0f / out->scale;
       f.status = e_->status();
       f.key_split = key_split;
       f.split_scratch = static_cast<float*>(d_partials_);
@@ -452,15 +531,7 @@ int PreparedGraph::attention(const char* name, const void* q, long long q_ld, lo
       PI05_TRY(fmha_plan_build(f, &op.fmha));
       ops_.push_back(std::move(op));
     }
-    if (prec_now == kPrecInt8) {
-      const void* wide = out->wide;
-      int8_t* data = static_cast<int8_t*>(out->data);
-      float* rs = out->row_scale;
-      const int rows = out->rows, cols = static_cast<int>(out->ld);
-      add_kernel("quantize_rows_int8", [=](cudaStream_t st) {
-        return launch_quantize_rows_int8(wide, data, rs, rows, cols, cols, cols, st);
-      });
-    }
+    if (prec_now == kPrecInt8) quantize_attention_output(out);
     return kPi05Ok;
   }
   const long long ld_s = round_up(keys, 8);
@@ -502,19 +573,29 @@ int PreparedGraph::attention(const char* name, const void* q, long long q_ld, lo
   pv.out_sb0 = out_sb0;
   pv.out_sb1 = out_sb1;
   pv.out_type = prec == kPrecFp8 ? kOutE4m3 : kOutBf16;
-  pv.out_inv_scale = 1.0f / e_->act_scale();
+  pv.out_inv_scale = 1.0f / out->scale;
   pv.status = e_->status();
   PI05_TRY(add_gemm((std::string(name) + ".pv").c_str(), pv));
-  if (prec == kPrecInt8) {
-    const void* wide = out->wide;
-    int8_t* data = static_cast<int8_t*>(out->data);
+  if (prec == kPrecInt8) quantize_attention_output(out);
+  return kPi05Ok;
+}
+
+// INT8: the attention kernels leave bf16 in `wide`; one more launch makes the int8 operand
+// (per-row scales, or the tensor's static scale).
+void PreparedGraph::quantize_attention_output(Act* out) {
+  const void* wide = out->wide;
+  int8_t* data = static_cast<int8_t*>(out->data);
+  const int rows = out->rows, cols = static_cast<int>(out->ld);
+  if (e_->static_int8()) {
+    const float inv = 1.0f / out->scale;
+    const long long count = static_cast<long long>(rows) * cols;
+    add_kernel("quantize_s8", [=](cudaStream_t st) { return launch_quantize_s8(wide, data, count, inv, st); });
+  } else {
     float* rs = out->row_scale;
-    const int rows = out->rows, cols = static_cast<int>(out->ld);
     add_kernel("quantize_rows_int8", [=](cudaStream_t st) {
       return launch_quantize_rows_int8(wide, data, rs, rows, cols, cols, cols, st);
     });
   }
-  return kPi05Ok;
 }
 
 int PreparedGraph::build(bool measuring) {
@@ -523,7 +604,6 @@ int PreparedGraph::build(bool measuring) {
   tensors_.clear();
   const ModelConfig& c = e_->cfg();
   const int prec = e_->precision();
-  const float inv_act = 1.0f / e_->act_scale();
   const GemmaDims& lg = c.language;
   const GemmaDims& ac = c.action;
   const int vw = c.vision_width, pp = c.patches_per_view(), heads_v = c.vision_heads,
@@ -566,21 +646,9 @@ int PreparedGraph::build(bool measuring) {
     // time embedding -> conditioning -> 2*depth+1 style vectors, all steps as GEMM rows
     // (crates/apxinf-model/src/pi05/bf16_runtime.rs:258-303).
     stage_ = 3;
-    const void* emb = d_time_emb_;
-    if (prec == kPrecBf16) {
-      time_in_act.data = d_time_emb_;
-    } else if (prec == kPrecFp8) {
-      uint8_t* dst = static_cast<uint8_t*>(time_in_act.data);
-      const long long count = (long long)S_ * ac.width;
-      add_kernel("quantize_time", [=](cudaStream_t s) { return launch_quantize_e4m3(emb, dst, count, inv_act, s); });
-    } else {
-      int8_t* dst = static_cast<int8_t*>(time_in_act.data);
-      float* rs = time_in_act.row_scale;
-      const int rows = S_, cols = ac.width;
-      add_kernel("quantize_time", [=](cudaStream_t s) { return launch_quantize_rows_int8(emb, dst, rs, rows, cols, cols, cols, s); });
-    }
-    PI05_TRY(linear_to_act("time_mlp_in", time_in_act, S_, e_->time_in, kEpiBiasSilu, &time_hidden));
-    PI05_TRY(linear_to_act("time_mlp_out", time_hidden, S_, e_->time_out, kEpiBiasSilu, &cond));
+    quantize_to_act("quantize_time", d_time_emb_, S_, ac.width, &time_in_act, "time.input");
+    PI05_TRY(linear_to_act("time_mlp_in", time_in_act, S_, e_->time_in, kEpiBiasSilu, &time_hidden, "time.hidden"));
+    PI05_TRY(linear_to_act("time_mlp_out", time_hidden, S_, e_->time_out, kEpiBiasSilu, &cond, "action.conditioning"));
     for (int idx = 0; idx <= 2 * ac.depth; ++idx) {
       const Linear& w = idx == 2 * ac.depth ? e_->final_style
                         : (idx % 2 == 0 ? e_->action[idx / 2].input_style
@@ -608,6 +676,7 @@ int PreparedGraph::build(bool measuring) {
   note("vision.hidden", xv, (size_t)Rv * vw * 2);
   note("prefix", xp, (size_t)Rp * lg.width * 2);
   {
+    patches.scale = e_->scale_of("vision.patch_input");
     PatchifyArgs pa{};
     pa.images = d_images_;
     pa.f32_patches = d_patches_in_;  // null unless the graph takes ready-made patches
@@ -618,31 +687,34 @@ int PreparedGraph::build(bool measuring) {
     pa.ld = static_cast<int>(patch_ld);
     pa.nchw = nchw_ == 1;
     pa.out = prec == kPrecFp8 ? kRowE4m3 : kRowBf16;
-    pa.inv_scale = inv_act;
+    pa.inv_scale = 1.0f / patches.scale;
     add_kernel("patchify", [pa](cudaStream_t s) { return launch_patchify(pa, s); });
     if (prec == kPrecInt8) {
-      const void* wide = patches.wide;
-      int8_t* data = static_cast<int8_t*>(patches.data);
-      float* rs = patches.row_scale;
-      const int cols = static_cast<int>(patch_ld);
-      add_kernel("quantize_rows_int8", [=](cudaStream_t s) { return launch_quantize_rows_int8(wide, data, rs, Rv, cols, cols, cols, s); });
+      Act q = patches;
+      quantize_to_act("quantize_patches", patches.wide, Rv, static_cast<int>(patch_ld), &q, "vision.patch_input");
     }
   }
   PI05_TRY(linear("vision.patch_embed", patches, Rv, e_->patch, kEpiBiasPos, xv, vw, kOutBf16, nullptr, nullptr, e_->position_embedding, pp, 1.0f));
-  PI05_TRY(norm_to_act("vision.ln1", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv));
+  auto vsite = [](int i, const char* part) { return "vision.layers." + std::to_string(i) + "." + part; };
+  auto lsite = [](int i, const char* part) { return "language.layers." + std::to_string(i) + "." + part; };
+  auto asite = [](int i, const char* part) { return "action.layers." + std::to_string(i) + "." + part; };
+  PI05_TRY(norm_to_act("vision.ln1", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv,
+                       c.vision_depth > 0 ? vsite(0, "attention_norm") : std::string("vision.post_norm")));
   const float scale_v = static_cast<float>(1.0 / std::sqrt(static_cast<double>(hd_v)));
   for (int i = 0; i < c.vision_depth; ++i) {
     const Engine::VisionBlock& w = e_->vision[i];
     PI05_TRY(linear("vision.qkv", nv, Rv, w.qkv, kEpiStore, qkv_v, 3 * vw, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
     const uint16_t* base = static_cast<const uint16_t*>(qkv_v);
+    attn_v.scale = e_->scale_of(vsite(i, "attention_output"));
     PI05_TRY(attention("vision.attn", base, 3 * vw, hd_v, (long long)pp * 3 * vw, base + vw, 3 * vw, hd_v,
                        (long long)pp * 3 * vw, base + 2 * vw, 3 * vw, hd_v, (long long)pp * 3 * vw, pp, pp,
                        hd_v, heads_v, n_images, scale_v, logits_v, &attn_v, vw, hd_v, (long long)pp * vw));
     PI05_TRY(linear("vision.o", attn_v, Rv, w.o, kEpiBiasResidual, xv, vw, kOutBf16, xv, nullptr, nullptr, 1, 1.0f));
-    PI05_TRY(norm_to_act("vision.ln2", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv));
-    PI05_TRY(linear_to_act("vision.fc1", nv, Rv, w.fc1, kEpiBiasGelu, &act_v));
+    PI05_TRY(norm_to_act("vision.ln2", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv, vsite(i, "mlp_norm")));
+    PI05_TRY(linear_to_act("vision.fc1", nv, Rv, w.fc1, kEpiBiasGelu, &act_v, vsite(i, "mlp_activation")));
     PI05_TRY(linear("vision.fc2", act_v, Rv, w.fc2, kEpiBiasResidual, xv, vw, kOutBf16, xv, nullptr, nullptr, 1, 1.0f));
-    PI05_TRY(norm_to_act(i + 1 < c.vision_depth ? "vision.ln1" : "vision.post_ln", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv));
+    PI05_TRY(norm_to_act(i + 1 < c.vision_depth ? "vision.ln1" : "vision.post_ln", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv,
+                         i + 1 < c.vision_depth ? vsite(i + 1, "attention_norm") : std::string("vision.post_norm")));
   }
   // projector writes the image tokens straight into rows [0, V) of each sample's prefix
   PI05_TRY(linear("vision.projector", nv, V_, e_->projector, kEpiStore, xp, lg.width, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f, B_, (long long)V_ * vw, (long long)P_ * lg.width));
@@ -662,7 +734,7 @@ int PreparedGraph::build(bool measuring) {
   Act attn_p = make_act(Rp, qw);
   Act act_p = make_act(Rp, lg.mlp_dim);
   const float scale_g = static_cast<float>(1.0 / std::sqrt(static_cast<double>(hd)));
-  PI05_TRY(norm_to_act("language.norm", xp, Rp, lg.width, kNormRms, nullptr, c.rms_norm_eps, &np_));
+  PI05_TRY(norm_to_act("language.norm", xp, Rp, lg.width, kNormRms, nullptr, c.rms_norm_eps, &np_, lsite(0, "attention_norm")));
   for (int l = 0; l < lg.depth; ++l) {
     const Engine::LanguageLayer& w = e_->language[l];
     PI05_TRY(linear("language.qkv", np_, Rp, w.qkv, kEpiStore, qkv_p, qw + 2 * hd, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
@@ -681,14 +753,15 @@ int PreparedGraph::build(bool measuring) {
     ra.cache_rows = cache_rows;
     add_kernel("language.rope", [ra](cudaStream_t s) { return launch_rope(ra, s); });
     if (l + 1 == lg.depth) break;  // the last layer only contributes K/V (bf16_runtime.rs:233)
+    attn_p.scale = e_->scale_of(lsite(l, "attention_output"));
     PI05_TRY(attention("language.attn", qbuf_p, hd, (long long)P_ * qw, 0, k_cache[l], hd, (long long)cache_rows * hd, 0,
                        v_cache[l], hd, (long long)cache_rows * hd, 0, P_ * qh, P_, hd, B_, 1, scale_g,
                        logits_p, &attn_p, hd, (long long)P_ * qw, 0));
     PI05_TRY(linear("language.o", attn_p, Rp, w.o, kEpiBiasResidual, xp, lg.width, kOutBf16, xp, nullptr, nullptr, 1, 1.0f));
-    PI05_TRY(norm_to_act("language.norm", xp, Rp, lg.width, kNormRms, nullptr, c.rms_norm_eps, &np_));
-    PI05_TRY(linear_to_act("language.gate_up", np_, Rp, w.gate_up, kEpiGeglu, &act_p));
+    PI05_TRY(norm_to_act("language.norm", xp, Rp, lg.width, kNormRms, nullptr, c.rms_norm_eps, &np_, lsite(l, "mlp_norm")));
+    PI05_TRY(linear_to_act("language.gate_up", np_, Rp, w.gate_up, kEpiGeglu, &act_p, lsite(l, "mlp_activation")));
     PI05_TRY(linear("language.down", act_p, Rp, w.down, kEpiBiasResidual, xp, lg.width, kOutBf16, xp, nullptr, nullptr, 1, 1.0f));
-    PI05_TRY(norm_to_act("language.norm", xp, Rp, lg.width, kNormRms, nullptr, c.rms_norm_eps, &np_));
+    PI05_TRY(norm_to_act("language.norm", xp, Rp, lg.width, kNormRms, nullptr, c.rms_norm_eps, &np_, lsite(l + 1, "attention_norm")));
   }
 
   // ---- stage 2: flow-matching denoise loop of the action expert ----
@@ -711,21 +784,9 @@ int PreparedGraph::build(bool measuring) {
   }
   const float dt = -1.0f / static_cast<float>(S_);
   for (int step = 0; step < S_; ++step) {
-    const void* state = d_state_;
-    if (prec == kPrecBf16) {
-      state_act.data = d_state_;
-    } else if (prec == kPrecFp8) {
-      uint8_t* dst = static_cast<uint8_t*>(state_act.data);
-      const long long count = (long long)Ra * c.action_dim;
-      add_kernel("quantize_state", [=](cudaStream_t s) { return launch_quantize_e4m3(state, dst, count, inv_act, s); });
-    } else {
-      int8_t* dst = static_cast<int8_t*>(state_act.data);
-      float* rs = state_act.row_scale;
-      const int cols = c.action_dim;
-      add_kernel("quantize_state", [=](cudaStream_t s) { return launch_quantize_rows_int8(state, dst, rs, Ra, cols, cols, cols, s); });
-    }
+    quantize_to_act("quantize_state", d_state_, Ra, c.action_dim, &state_act, "action.input");
     PI05_TRY(linear("action.in", state_act, Ra, e_->action_in, kEpiStore, ha, ac.width, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
-    PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, style_ptr(0, step), c.rms_norm_eps, &na));
+    PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, style_ptr(0, step), c.rms_norm_eps, &na, asite(0, "attention_norm")));
     for (int l = 0; l < ac.depth; ++l) {
       const Engine::ActionLayer& w = e_->action[l];
       const uint16_t* attn_style = static_cast<const uint16_t*>(style_ptr(2 * l, step));
@@ -746,14 +807,16 @@ int PreparedGraph::build(bool measuring) {
       ra.position_offset = P_;
       ra.cache_rows = cache_rows;
       add_kernel("action.rope", [ra](cudaStream_t s) { return launch_rope(ra, s); });
+      attn_a.scale = e_->scale_of(asite(l, "attention_output"));
       PI05_TRY(attention("action.attn", qbuf_a, hd, (long long)H_ * qw, 0, k_cache[l], hd, (long long)cache_rows * hd, 0,
                          v_cache[l], hd, (long long)cache_rows * hd, 0, H_ * qh, cache_rows, hd, B_, 1, scale_g,
                          logits_a, &attn_a, hd, (long long)H_ * qw, 0));
       PI05_TRY(linear("action.o", attn_a, Ra, w.o, kEpiGateResidual, ha, ac.width, kOutBf16, ha, attn_style + 2 * ac.width, nullptr, 1, 1.0f));
-      PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, mlp_style, c.rms_norm_eps, &na));
-      PI05_TRY(linear_to_act("action.gate_up", na, Ra, w.gate_up, kEpiGeglu, &act_a));
+      PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, mlp_style, c.rms_norm_eps, &na, asite(l, "mlp_norm")));
+      PI05_TRY(linear_to_act("action.gate_up", na, Ra, w.gate_up, kEpiGeglu, &act_a, asite(l, "mlp_activation")));
       PI05_TRY(linear("action.down", act_a, Ra, w.down, kEpiGateResidual, ha, ac.width, kOutBf16, ha, mlp_style + 2 * ac.width, nullptr, 1, 1.0f));
-      PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, next_style, c.rms_norm_eps, &na));
+      PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, next_style, c.rms_norm_eps, &na,
+                           l + 1 < ac.depth ? asite(l + 1, "attention_norm") : std::string("action.final_norm")));
     }
     PI05_TRY(linear("action.out", na, Ra, e_->action_out, kEpiStore, velocity, c.action_dim, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
     {

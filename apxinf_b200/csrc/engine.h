@@ -58,10 +58,11 @@ struct Linear {
 // A GEMM input as the active precision wants it.
 struct Act {
   void* data = nullptr;       // bf16 | e4m3 | int8 [rows, ld]
-  float* row_scale = nullptr; // int8: per-row dynamic scale
+  float* row_scale = nullptr; // int8 with dynamic scales: one per row
   void* wide = nullptr;       // int8 only: bf16 staging the quantiser reads
   long long ld = 0;
   int rows = 0;
+  float scale = 1.0f;         // static activation scale of this tensor (fp8, static int8)
 };
 
 struct Op {
@@ -132,10 +133,15 @@ class PreparedGraph {
              long long ldc, int out_type, const void* residual, const void* gate,
              const void* pos, int pos_rows, float out_inv_scale, int nb0 = 1,
              long long a_sb0 = 0, long long out_sb0 = 0);
+  // `site` names the static activation scale of the produced tensor (Engine::scale_of)
   int linear_to_act(const char* name, const Act& in, int rows, const Linear& w, int mode,
-                    Act* out);
+                    Act* out, const std::string& site);
   int norm_to_act(const char* name, const void* x, int rows, int cols, int kind,
-                  const void* style, float eps, Act* out);
+                  const void* style, float eps, Act* out, const std::string& site);
+  // quantises a bf16 tensor (or passes it through) into the precision's operand form
+  void quantize_to_act(const char* name, const void* bf16_src, int rows, int cols, Act* out,
+                       const std::string& site);
+  void quantize_attention_output(Act* out);
   Act make_act(int rows, long long ld);
   int attention(const char* name, const void* q, long long q_ld, long long q_sb0, long long q_sb1,
                 const void* k, long long k_ld, long long k_sb0, long long k_sb1, const void* v,
@@ -169,9 +175,21 @@ class PreparedGraph {
   uint16_t* h_out_ = nullptr;  // pinned
 };
 
+enum WeightDist : int { kWeightsLcg = 0, kWeightsNormal = 1 };
+enum Int8Activations : int { kInt8Dynamic = 0, kInt8Static = 1 };
+
+struct EngineOptions {
+  int precision = kPrecBf16;
+  int device = 0;
+  uint64_t seed = 0;
+  float act_scale = 1.0f;          // uniform static activation scale (sites not set by name)
+  int weight_dist = kWeightsLcg;   // reference LCG (uniform +-0.02) | seeded N(0, 0.02)
+  int int8_activations = kInt8Dynamic;  // per-row dynamic (reference) | static per-tensor
+};
+
 class Engine {
  public:
-  Engine(const ModelConfig& cfg, int precision, int device, uint64_t seed, float act_scale);
+  Engine(const ModelConfig& cfg, const EngineOptions& options);
   ~Engine();
   int init();  // stream, status word, rope tables, synthetic weights
   const ModelConfig& cfg() const { return cfg_; }
@@ -180,6 +198,16 @@ class Engine {
   int* status() const { return status_; }
   int device() const { return device_; }
   float act_scale() const { return act_scale_; }
+  // Static activation scale of a GEMM-input site, named as the reference's calibration table
+  // (crates/apxinf-model/src/pi05/runtime.rs:35-81): "vision.patch_input",
+  // "vision.layers.<i>.{attention_norm,attention_output,mlp_norm,mlp_activation}",
+  // "vision.post_norm", "language.layers.<i>.<...>", "action.input", "time.input",
+  // "time.hidden", "action.conditioning", "action.layers.<i>.<...>", "action.final_norm".
+  float scale_of(const std::string& site) const;
+  int set_scale(const std::string& site, float value);  // before capture; unknown names are refused
+  bool static_int8() const { return prec_ == kPrecInt8 && int8_static_; }
+  // the precision takes byte operands with one static scale per tensor
+  bool static_scales() const { return prec_ == kPrecFp8 || static_int8(); }
   size_t weight_bytes() const { return weight_bytes_; }
   int read_weight(const char* name, void* host, size_t capacity, size_t* actual);
 
@@ -202,10 +230,15 @@ class Engine {
   int make_linear(const std::string& prefix, const std::vector<std::string>& parts, int k,
                   const std::vector<int>& ns, bool bias, bool interleave, Linear* out);
   void* dmalloc(size_t bytes);
+  void release(void* p);  // frees one tracked allocation early
+  cudaError_t fill(void* dst_bf16, long long count);  // next `count` stream elements
   ModelConfig cfg_;
   int prec_, device_;
   uint64_t seed_;
   float act_scale_;
+  int weight_dist_ = kWeightsLcg;
+  bool int8_static_ = false;
+  std::unordered_map<std::string, float> site_scales_;  // every valid site, current value
   cudaStream_t stream_ = nullptr;
   int* status_ = nullptr;
   uint64_t cursor_ = 0;  // element offset in the synthetic stream

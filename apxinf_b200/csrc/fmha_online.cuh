@@ -211,8 +211,7 @@ fmha_online_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       };
       for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++items_done) {
         if (ok) ok = ptx::mbar_wait(q_full, items_done & 1);
-        // both score buffers are free: the previous tile's last two PV products have completed
-        // (p_free of the last one was waited for below, and MMAs complete in order)
+        // both score buffers are free: every PV product of the previous tile was waited for below
         issue_s(0);
         if (n_blocks > 1) issue_s(1);
         for (int j = 0; j < n_blocks; ++j) {
@@ -240,12 +239,12 @@ fmha_online_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           }
           ptx::umma_commit(p_free);
           ++pv_blocks;
-          // the last tile's PV, or the one whose buffer the next S product overwrites, must be
-          // complete before going on
-          if (j + 2 < n_blocks || j == n_blocks - 1) {
-            if (ok) ok = ptx::mbar_wait(p_free, (pv_blocks - 1) & 1);
-            ptx::tc_fence_after();
-          }
+          // Every PV product is waited for before going on: S_{j+2} overwrites the buffer PV_j
+          // reads its probabilities from, and the next tile's S_0 / S_1 overwrite the buffers of
+          // this tile's last two products. Waiting on each phase in turn also keeps the parity
+          // wait exact (a phase is never more than one behind the one asked for).
+          if (ok) ok = ptx::mbar_wait(p_free, (pv_blocks - 1) & 1);
+          ptx::tc_fence_after();
           if (j + 2 < n_blocks) issue_s(j + 2);
         }
         ptx::umma_commit(o_full);

@@ -138,6 +138,7 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
     return kPi05ErrInvalidValue;
   }
   if (q.op != kOpBf16 && q.op != kOpE4m3 && q.op != kOpS8) return kPi05ErrInvalidValue;
+  if (q.out_type < kOutBf16 || q.out_type > kOutS8) return kPi05ErrInvalidValue;
   if (q.out_type == kOutS32 && q.op != kOpS8) return kPi05ErrInvalidValue;
   if (q.mode == kEpiGeglu && (q.N % 128 != 0 || q.b_mn_major)) return kPi05ErrInvalidValue;
   if ((q.mode == kEpiBiasResidual || q.mode == kEpiGateResidual) && q.residual == nullptr)
@@ -280,7 +281,6 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   p.split_k = split;
   p.partials = reinterpret_cast<uint32_t*>(q.partials);
   p.tile_counters = q.tile_counters;
-  p.trace = q.trace;
   p.static_a = (swap && q.b_static) ? 1 : 0;
   p.static_b = (!swap && q.b_static) ? 1 : 0;
   p.blocked_a = (swap && q.b_blocked) ? 1 : 0;

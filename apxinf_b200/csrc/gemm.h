@@ -52,7 +52,6 @@ struct GemmProblem {
   int* tile_counters = nullptr;
   int max_tiles = 0;
   int force_split_k = 0;  // 0 = automatic, 1 = off, n = exactly n (clamped to the K blocks)
-  unsigned int* trace = nullptr;  // optional device uint32[6], see GemmParams::trace
   // the b operand is a weight matrix no kernel of the stream writes (enables early TMA loads)
   bool b_static = false;
   // b (weights) is stored K-block-major: [ceil(K / kb)][N][kb] with kb = 128 bytes of K

@@ -59,6 +59,21 @@ extern "C" int pi05_gemm_static_scratch(const Pi05GemmArgs* args, void* cuda_str
     g_last_cuda_error = "pi05_gemm_static_scratch is the split-K variant: force_split_k must be >= 2";
     return kPi05ErrInvalidValue;
   }
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  // The scratch address is the current device's copy: a stream of another device would run
+  // the kernel there with this device's pointer.
+  if (stream != nullptr && stream != cudaStreamLegacy && stream != cudaStreamPerThread) {
+    int current = -1, stream_device = -1;
+    cudaError_t err = cudaGetDevice(&current);
+    if (err == cudaSuccess) err = cudaStreamGetDevice(stream, &stream_device);
+    if (err != cudaSuccess) return record_cuda(err);
+    if (current != stream_device) {
+      g_last_cuda_error = "pi05_gemm_static_scratch: the stream belongs to device " +
+                          std::to_string(stream_device) + " but device " + std::to_string(current) +
+                          " is current";
+      return kPi05ErrInvalidValue;
+    }
+  }
   StaticScratch* scratch = nullptr;
   int rc = scratch_for_current_device(&scratch);
   if (rc != kPi05Ok) return rc;
@@ -94,7 +109,6 @@ extern "C" int pi05_gemm_static_scratch(const Pi05GemmArgs* args, void* cuda_str
   q.force_swap = args->force_swap;
   q.force_block_n = args->force_block_n;
   q.force_split_k = args->force_split_k;
-  q.trace = args->trace;
   q.b_blocked = args->b_blocked != 0;
   q.partials = scratch->partials;
   q.partials_bytes = PI05_STATIC_SCRATCH_BYTES;
@@ -111,7 +125,6 @@ extern "C" int pi05_gemm_static_scratch(const Pi05GemmArgs* args, void* cuda_str
     return rc;
   }
   if (rc != kPi05Ok) return rc;
-  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   // The array keeps whatever the last call left; the arrival counters must start at zero.
   cudaError_t err = cudaMemsetAsync(scratch->counters, 0, sizeof(scratch->counters), stream);
   if (err != cudaSuccess) return record_cuda(err);

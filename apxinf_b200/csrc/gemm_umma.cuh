@@ -49,6 +49,7 @@ enum OutType : int {
   kOutE4m3 = 1,  // e4m3(clamp(o * out_inv_scale, +-448))
   kOutF32 = 2,   // raw scaled accumulator (no epilogue rounding), for tests / partial sums
   kOutS32 = 3,   // raw int32 accumulator (kOpS8 only), for bit-exact checks
+  kOutS8 = 4,    // static per-tensor int8: clamp(round_half_away(bf16(o) * out_inv_scale), -128, 127)
 };
 
 enum GemmStatus : int {
@@ -74,7 +75,7 @@ struct GemmParams {
   const __nv_bfloat16* pos;       // [pos_rows, N]
   const __nv_bfloat16* gate;      // [N]
   float alpha;                    // scalar scale applied with row_scale
-  float out_inv_scale;            // for kOutE4m3
+  float out_inv_scale;            // for kOutE4m3 / kOutS8
   int pos_rows;
   long long pos_ld;
   int mode;
@@ -87,10 +88,6 @@ struct GemmParams {
   int kb_per_split;
   uint32_t* partials;             // [tiles][split_k][128][BLOCK_N] raw 32-bit accumulators
   int* tile_counters;             // [tiles], zero between launches
-  // optional: CTA (0,0,0) writes SM-clock deltas from kernel entry to
-  // {setup done, first operands landed, last MMA issued, accumulator ready,
-  //  epilogue done, TMEM freed} for latency breakdowns
-  unsigned int* trace;
   // operands that no kernel of the stream writes (weights): their TMA loads may be issued
   // before the programmatic-dependency wait
   int static_a, static_b;
@@ -133,6 +130,11 @@ __device__ __forceinline__ uint8_t to_e4m3(float scaled) {
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(clamped, __NV_SATFINITE, __NV_E4M3));
 }
 
+__device__ __forceinline__ uint8_t to_s8(float scaled) {
+  const float q = fminf(127.0f, fmaxf(-128.0f, roundf(scaled)));
+  return static_cast<uint8_t>(static_cast<int8_t>(static_cast<int>(q)));
+}
+
 template <int OP>
 struct OpTraits;
 template <>
@@ -170,11 +172,10 @@ __host__ __device__ constexpr int gemm_smem_bytes(int block_n, int stages) {
   return stages * gemm_stage_bytes(block_n) + 1024 /*alignment slack*/ + 512 /*barriers*/ +
          2 * 3 * 256 * 4 /*epilogue vectors (double-buffered in the persistent kernel)*/;
 }
-// (Measured: rotating over several accumulators does not shorten the ~140-cycle issue
-// interval of 128-row MMAs, so one accumulator per tile is used.)
-__host__ __device__ constexpr int accumulators_for(int block_n) { return block_n > 0 ? 1 : 1; }
+// One accumulator per tile (measured: rotating MMAs over several accumulators does not shorten
+// the ~140-cycle issue interval of 128-row MMAs).
 __host__ __device__ constexpr uint32_t tmem_cols_for(int block_n) {
-  const int cols = block_n * accumulators_for(block_n);
+  const int cols = block_n;
   return cols <= 32 ? 32u : cols <= 64 ? 64u : cols <= 128 ? 128u : cols <= 256 ? 256u : 512u;
 }
 
@@ -211,11 +212,21 @@ __device__ __forceinline__ float epi_apply(float v, float bias, float extra, flo
   }
 }
 
+// One-byte outputs: e4m3 straight from the fp32 value (the FP8 path fuses the quantiser into
+// the producer), int8 from the bf16-rounded value (the W8A8 path stores bf16 first).
+__device__ __forceinline__ bool out_is_byte(const GemmParams& p) {
+  return p.out_type == kOutE4m3 || p.out_type == kOutS8;
+}
+__device__ __forceinline__ uint8_t out_byte(const GemmParams& p, float o) {
+  return p.out_type == kOutS8 ? to_s8(round_bf16(o) * p.out_inv_scale)
+                              : to_e4m3(o * p.out_inv_scale);
+}
+
 __device__ __forceinline__ void store_one(const GemmParams& p, long long index, float o) {
   if (p.out_type == kOutBf16) {
     reinterpret_cast<__nv_bfloat16*>(p.out)[index] = __float2bfloat16(o);
-  } else if (p.out_type == kOutE4m3) {
-    reinterpret_cast<uint8_t*>(p.out)[index] = to_e4m3(o * p.out_inv_scale);
+  } else if (out_is_byte(p)) {
+    reinterpret_cast<uint8_t*>(p.out)[index] = out_byte(p, o);
   } else {
     reinterpret_cast<float*>(p.out)[index] = o;
   }
@@ -242,22 +253,22 @@ __device__ __forceinline__ void store_chunk16(const GemmParams& p, long long ind
         if (t < valid) dst[t] = __float2bfloat16(o[t]);
       }
     }
-  } else if (p.out_type == kOutE4m3) {
+  } else if (out_is_byte(p)) {
     uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + index;
     if (valid == 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
       uint32_t w[4];
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
-        w[t] = (uint32_t)to_e4m3(o[4 * t] * p.out_inv_scale) |
-               ((uint32_t)to_e4m3(o[4 * t + 1] * p.out_inv_scale) << 8) |
-               ((uint32_t)to_e4m3(o[4 * t + 2] * p.out_inv_scale) << 16) |
-               ((uint32_t)to_e4m3(o[4 * t + 3] * p.out_inv_scale) << 24);
+        w[t] = (uint32_t)out_byte(p, o[4 * t]) |
+               ((uint32_t)out_byte(p, o[4 * t + 1]) << 8) |
+               ((uint32_t)out_byte(p, o[4 * t + 2]) << 16) |
+               ((uint32_t)out_byte(p, o[4 * t + 3]) << 24);
       }
       *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
     } else {
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
-        if (t < valid) dst[t] = to_e4m3(o[t] * p.out_inv_scale);
+        if (t < valid) dst[t] = out_byte(p, o[t]);
       }
     }
   } else {
@@ -290,22 +301,22 @@ __device__ __forceinline__ void store_chunk8(const GemmParams& p, long long inde
         if (t < valid) dst[t] = __float2bfloat16(o[t]);
       }
     }
-  } else if (p.out_type == kOutE4m3) {
+  } else if (out_is_byte(p)) {
     uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + index;
     if (valid >= 8 && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
       uint32_t w[2];
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
-        w[t] = (uint32_t)to_e4m3(o[4 * t] * p.out_inv_scale) |
-               ((uint32_t)to_e4m3(o[4 * t + 1] * p.out_inv_scale) << 8) |
-               ((uint32_t)to_e4m3(o[4 * t + 2] * p.out_inv_scale) << 16) |
-               ((uint32_t)to_e4m3(o[4 * t + 3] * p.out_inv_scale) << 24);
+        w[t] = (uint32_t)out_byte(p, o[4 * t]) |
+               ((uint32_t)out_byte(p, o[4 * t + 1]) << 8) |
+               ((uint32_t)out_byte(p, o[4 * t + 2]) << 16) |
+               ((uint32_t)out_byte(p, o[4 * t + 3]) << 24);
       }
       *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
     } else {
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
-        if (t < valid) dst[t] = to_e4m3(o[t] * p.out_inv_scale);
+        if (t < valid) dst[t] = out_byte(p, o[t]);
       }
     }
   } else if (p.out_type == kOutF32) {
@@ -360,7 +371,6 @@ __device__ __forceinline__ void lds16(const float* src, float (&x)[16]) {
 // so the result does not depend on which split arrived last.
 template <int OP, int BLOCK_N>
 struct AccSource {
-  static constexpr int kAccs = accumulators_for(BLOCK_N);
   uint32_t taddr_row;
   const uint32_t* partial_row;  // this thread's row in split 0, or null
   long long split_stride;       // elements between splits
@@ -369,24 +379,6 @@ struct AccSource {
   __device__ __forceinline__ void load16(int col0, uint32_t (&raw)[16]) const {
     if (partial_row == nullptr) {
       ptx::tmem_ld_16(taddr_row + col0, raw);
-      if constexpr (kAccs > 1) {
-        // successive MMAs rotate over kAccs independent accumulators; add them up here
-        uint32_t more[kAccs - 1][16];
-#pragma unroll
-        for (int a = 1; a < kAccs; ++a) ptx::tmem_ld_16(taddr_row + a * BLOCK_N + col0, more[a - 1]);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int a = 1; a < kAccs; ++a) {
-#pragma unroll
-          for (int t = 0; t < 16; ++t) {
-            if constexpr (OP == kOpS8) {
-              raw[t] = static_cast<uint32_t>(static_cast<int>(raw[t]) + static_cast<int>(more[a - 1][t]));
-            } else {
-              raw[t] = __float_as_uint(__uint_as_float(raw[t]) + __uint_as_float(more[a - 1][t]));
-            }
-          }
-        }
-      }
       return;
     }
     float facc[16];
@@ -684,8 +676,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::make_idesc(T::kCFormat, T::kFormat, T::kFormat, 0, B_MN ? 1 : 0, 128, BLOCK_N);
 
   pdl_launch_dependents();
-  const long long t_entry = clock64();
-  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -727,7 +717,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (tracing && threadIdx.x == 0) p.trace[0] = static_cast<unsigned int>(clock64() - t_entry);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -804,7 +793,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int s = kb % STAGES;
         ok = ptx::mbar_wait(&full_bar[s], (kb / STAGES) & 1);
         if (!ok) break;
-        if (tracing && kb == 0) p.trace[1] = static_cast<unsigned int>(clock64() - t_entry);
         ptx::tc_fence_after();
         const uint32_t a_addr = ptx::smem_u32(smem + s * kStageBytes);
         const uint32_t b_addr = a_addr + kStageABytes;
@@ -813,18 +801,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint64_t adesc = ptx::make_smem_desc(a_addr + k * 32, 16, 1024);
           const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b_addr + k * 2048, 8192, 1024)
                                       : ptx::make_smem_desc(b_addr + k * 32, 16, 1024);
-          constexpr int kAccs = accumulators_for(BLOCK_N);
-          const int which = k % kAccs;
-          const bool first_touch = kb == 0 && k < kAccs;
-          ptx::umma<T::kKind>(tmem_base + which * BLOCK_N, adesc, bdesc, kIdesc,
-                              first_touch ? 0u : 1u);
+          ptx::umma<T::kKind>(tmem_base, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
         }
         ptx::umma_commit(&empty_bar[s]);
       }
       if (!ok) atomicCAS(p.status, 0, kGemmTimeoutMma);
       // Always signal the epilogue so that it never waits on a dead pipeline.
       ptx::umma_commit(accum_bar);
-      if (tracing) p.trace[2] = static_cast<unsigned int>(clock64() - t_entry);
     }
   } else {
     // ---------------- epilogue (warps 2..9) ----------------
@@ -837,8 +820,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const float* row_scale =
         p.row_scale != nullptr ? p.row_scale + (long long)b0 * p.row_scale_sb0 : nullptr;
 
-    // Per-column vectors of this tile (weights-side, static) go to shared memory while the
-    // main loop runs; anything an earlier kernel wrote is read after the dependency wait.
+    // Per-column vectors of this tile (scale, bias, gate) go to shared memory while the main
+    // loop runs. When the caller declared its weights static (the engine: these vectors are
+    // written once, before the replayed stream) they are read ahead of the dependency wait;
+    // otherwise an earlier kernel of the stream may have produced them, so the wait comes first.
+    if (!(p.static_a | p.static_b)) pdl_wait();
     float sw_scale = 1.0f, sw_bias = 0.0f, sw_gate = 0.0f;
     if constexpr (!SWAP) {
       for (int j = ep_tid; j < BLOCK_N; j += kEpilogueThreads) {
@@ -871,7 +857,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const bool ok = ptx::mbar_wait(accum_bar, 0);
     if (!ok && lane == 0) atomicCAS(p.status, 0, kGemmTimeoutEpilogue);
     ptx::tc_fence_after();
-    if (tracing && ep_tid == 0) p.trace[3] = static_cast<unsigned int>(clock64() - t_entry);
     const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
 
     AccSource<OP, BLOCK_N> acc{taddr_row, nullptr, 0, 1};
@@ -1001,13 +986,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
-  if (tracing && threadIdx.x == 64) p.trace[4] = static_cast<unsigned int>(clock64() - t_entry);
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
-    if (tracing && lane == 0) p.trace[5] = static_cast<unsigned int>(clock64() - t_entry);
   }
 }
 
@@ -1041,11 +1024,6 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::make_idesc(T::kCFormat, T::kFormat, T::kFormat, 0, B_MN ? 1 : 0, 128, BLOCK_N);
 
   pdl_launch_dependents();
-  // optional phase stamps (SM clock) of CTA 0's fourth tile, for timeline studies
-  const long long t_entry = clock64();
-  const bool tracing = p.trace != nullptr && blockIdx.x == 0;
-#define PI05_PTRACE(slot, cond) \
-  do { if (tracing && (cond)) p.trace[slot] = static_cast<unsigned int>(clock64() - t_entry); } while (0)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -1114,8 +1092,6 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const long long round = it / STAGES;
           if (round > 0) ok = ptx::mbar_wait(&empty_bar[s], static_cast<uint32_t>((round - 1) & 1));
           if (!ok) break;
-          PI05_PTRACE(0, local == 3 && kb == 0);
-          PI05_PTRACE(1, local == 3 && kb == p.num_kb - 1);
           uint8_t* sa = smem + s * kStageBytes;
           uint8_t* sb = sa + kStageABytes;
           ptx::mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
@@ -1145,13 +1121,11 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ok = ptx::mbar_wait(&acc_empty[buf], static_cast<uint32_t>(((local >> 1) - 1) & 1));
           ptx::tc_fence_after();
         }
-        PI05_PTRACE(2, local == 3);
         for (int kb = 0; kb < p.num_kb && ok; ++kb, ++it) {
           const int s = static_cast<int>(it % STAGES);
           ok = ptx::mbar_wait(&full_bar[s], static_cast<uint32_t>((it / STAGES) & 1));
           if (!ok) break;
           ptx::tc_fence_after();
-          PI05_PTRACE(3, local == 3 && kb == 0);
           const uint32_t a_addr = ptx::smem_u32(smem + s * kStageBytes);
           const uint32_t b_addr = a_addr + kStageABytes;
 #pragma unroll
@@ -1166,7 +1140,6 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         // signal the epilogue even after a timeout so that it never waits on a dead pipeline
         ptx::umma_commit(&acc_full[buf]);
-        PI05_PTRACE(4, local == 3);
       }
       if (!ok) atomicCAS(p.status, 0, kGemmTimeoutMma);
     }
@@ -1179,7 +1152,6 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int buf = local & 1;
       int ta, tb, b0, b1;
       decode(local, &ta, &tb, &b0, &b1);
-      PI05_PTRACE(5, local == 3 && threadIdx.x == 64);
       float* s_scale = s_vectors + buf * 768;
       float* s_bias = s_scale + 256;
       float* s_gate = s_bias + 256;
@@ -1197,13 +1169,11 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
       float sr = p.alpha;
       if (row_scale != nullptr && gi < p.rows_a) sr = p.alpha * row_scale[gi];
       asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
-      PI05_PTRACE(6, local == 3 && threadIdx.x == 64);
 
       auto wait_acc = [&] {
         const bool ok = ptx::mbar_wait(&acc_full[buf], static_cast<uint32_t>((local >> 1) & 1));
         if (!ok && lane == 0) atomicCAS(p.status, 0, kGemmTimeoutEpilogue);
         ptx::tc_fence_after();
-        PI05_PTRACE(7, local == 3 && threadIdx.x == 64);
       };
       const uint32_t taddr_row =
           tmem_base + buf * BLOCK_N + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -1230,7 +1200,6 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
 #undef PI05_EPI_CASE
       }
-      PI05_PTRACE(8, local == 3 && threadIdx.x == 64);
       // this warp has read everything it needs from the accumulator buffer
       ptx::tc_fence_before();
       __syncwarp();

@@ -14,6 +14,11 @@ __device__ __forceinline__ uint8_t e4m3_of(float scaled) {
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(clamped, __NV_SATFINITE, __NV_E4M3));
 }
 
+__device__ __forceinline__ uint32_t s8_of(float scaled) {
+  const float q = fminf(127.0f, fmaxf(-128.0f, roundf(scaled)));
+  return static_cast<uint32_t>(static_cast<int>(q)) & 0xffu;
+}
+
 __device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
   const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
@@ -141,6 +146,17 @@ __global__ void norm_rows_kernel(NormArgs a) {
       }
       reinterpret_cast<uint2*>(out)[vec] = make_uint2(lo, hi);
     }
+  } else if (OUT == kRowInt8Static) {
+    if (active) {
+      int8_t* out = reinterpret_cast<int8_t*>(a.output) + (long long)row * a.cols;
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        lo |= s8_of(rb(y[i]) * a.inv_scale) << (8 * i);
+        hi |= s8_of(rb(y[4 + i]) * a.inv_scale) << (8 * i);
+      }
+      reinterpret_cast<uint2*>(out)[vec] = make_uint2(lo, hi);
+    }
   } else {
     float amax = 0.0f;
 #pragma unroll
@@ -175,6 +191,8 @@ cudaError_t launch_norm_kind(const NormArgs& a, int threads, cudaStream_t stream
       return launch_pdl(norm_rows_kernel<KIND, kRowE4m3>, dim3(a.rows), dim3(threads), 0, stream, a);
     case kRowInt8:
       return launch_pdl(norm_rows_kernel<KIND, kRowInt8>, dim3(a.rows), dim3(threads), 0, stream, a);
+    case kRowInt8Static:
+      return launch_pdl(norm_rows_kernel<KIND, kRowInt8Static>, dim3(a.rows), dim3(threads), 0, stream, a);
     default:
       return cudaErrorInvalidValue;
   }
@@ -440,6 +458,17 @@ __global__ void quantize_e4m3_kernel(const __nv_bfloat16* input, uint8_t* output
   }
 }
 
+__global__ void quantize_s8_kernel(const __nv_bfloat16* input, int8_t* output, long long count,
+                                   float inv_scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)blockDim.x * gridDim.x;
+  for (; index < count; index += stride) {
+    output[index] = static_cast<int8_t>(s8_of(__bfloat162float(input[index]) * inv_scale));
+  }
+}
+
 __global__ void euler_kernel(__nv_bfloat16* state, const __nv_bfloat16* velocity, long long count,
                              float dt) {
   pdl_launch_dependents();
@@ -554,6 +583,16 @@ cudaError_t launch_quantize_e4m3(const void* input, uint8_t* output, long long c
   const int threads = 256;
   const long long blocks = (count + threads - 1) / threads;
   return launch_pdl(quantize_e4m3_kernel, dim3(static_cast<unsigned>(blocks > 1184 ? 1184 : blocks)),
+                    dim3(threads), 0, stream, reinterpret_cast<const __nv_bfloat16*>(input), output,
+                    count, inv_scale);
+}
+
+cudaError_t launch_quantize_s8(const void* input, int8_t* output, long long count, float inv_scale,
+                               cudaStream_t stream) {
+  if (input == nullptr || output == nullptr || count <= 0) return cudaErrorInvalidValue;
+  const int threads = 256;
+  const long long blocks = (count + threads - 1) / threads;
+  return launch_pdl(quantize_s8_kernel, dim3(static_cast<unsigned>(blocks > 1184 ? 1184 : blocks)),
                     dim3(threads), 0, stream, reinterpret_cast<const __nv_bfloat16*>(input), output,
                     count, inv_scale);
 }

@@ -18,7 +18,9 @@
 namespace pi05 {
 
 enum NormKind : int { kNormLayer = 0, kNormRms = 1, kNormAda = 2 };
-enum RowOut : int { kRowBf16 = 0, kRowE4m3 = 1, kRowInt8 = 2 };
+// kRowInt8: dynamic per-row scale (written to row_scale); kRowInt8Static: one given scale,
+// q = clamp(round_half_away(bf16(y) * inv_scale), -128, 127).
+enum RowOut : int { kRowBf16 = 0, kRowE4m3 = 1, kRowInt8 = 2, kRowInt8Static = 3 };
 
 struct NormArgs {
   const void* input;    // bf16 [rows, cols]
@@ -29,7 +31,7 @@ struct NormArgs {
   const void* style;    // bf16 [>= 2*cols]: scale | shift (adaptive RMSNorm)
   int rows, cols;
   float eps;
-  float inv_scale;      // 1 / activation scale for kRowE4m3
+  float inv_scale;      // 1 / activation scale for kRowE4m3 and kRowInt8Static
   int kind, out;
 };
 cudaError_t launch_norm(const NormArgs& args, cudaStream_t stream);
@@ -81,6 +83,10 @@ cudaError_t launch_quantize_rows_int8(const void* input, int8_t* output, float* 
 // Static per-tensor E4M3: e4m3(clamp(x * inv_scale)).
 cudaError_t launch_quantize_e4m3(const void* input, uint8_t* output, long long count,
                                  float inv_scale, cudaStream_t stream);
+
+// Static per-tensor INT8: clamp(round_half_away(x * inv_scale), -128, 127).
+cudaError_t launch_quantize_s8(const void* input, int8_t* output, long long count, float inv_scale,
+                               cudaStream_t stream);
 
 // state <- bf16(state + dt * velocity)
 cudaError_t launch_euler(void* state, const void* velocity, long long count, float dt,

@@ -44,6 +44,34 @@ __global__ void lcg_fill_kernel(__nv_bfloat16* dst, uint64_t state0, uint64_t of
   }
 }
 
+// Seeded N(0, 0.02): element i = (sum of the twelve 16-bit fields of SplitMix64 outputs at
+// counters 3i+1..3i+3, minus 393210) * (0.02 / 65536), an Irwin-Hall sum with unit variance in
+// units of 65536. Integer arithmetic and one float multiply, so any host restatement matches
+// bit for bit.
+__device__ __forceinline__ uint64_t splitmix64(uint64_t z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+__global__ void normal_fill_kernel(__nv_bfloat16* dst, uint64_t key, uint64_t offset,
+                                   long long count) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)blockDim.x * gridDim.x;
+  for (; i < count; i += stride) {
+    const uint64_t index = offset + static_cast<uint64_t>(i);
+    int total = 0;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      const uint64_t z = splitmix64(key + (index * 3ull + static_cast<uint64_t>(j + 1)) * kSeedXor);
+      total += static_cast<int>(z & 0xFFFFu) + static_cast<int>((z >> 16) & 0xFFFFu) +
+               static_cast<int>((z >> 32) & 0xFFFFu) + static_cast<int>((z >> 48) & 0xFFFFu);
+    }
+    const float value = __fmul_rn(static_cast<float>(total - 393210), 0.02f / 65536.0f);
+    dst[i] = __float2bfloat16(value);
+  }
+}
+
 __global__ void transpose_pack_kernel(const __nv_bfloat16* src, __nv_bfloat16* dst, int k, int n,
                                       long long ldk, int row_offset, int interleave, int slot) {
   __shared__ __nv_bfloat16 tile[32][33];
@@ -111,6 +139,16 @@ cudaError_t launch_lcg_fill(void* dst_bf16, uint64_t seed, uint64_t offset, long
   const int threads = 128;
   lcg_fill_kernel<<<static_cast<unsigned>((chunks + threads - 1) / threads), threads, 0, stream>>>(
       reinterpret_cast<__nv_bfloat16*>(dst_bf16), seed ^ kSeedXor, offset, count);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_normal_fill(void* dst_bf16, uint64_t seed, uint64_t offset, long long count,
+                               cudaStream_t stream) {
+  if (dst_bf16 == nullptr || count <= 0) return cudaErrorInvalidValue;
+  const int threads = 256;
+  const long long blocks = (count + threads - 1) / threads;
+  normal_fill_kernel<<<static_cast<unsigned>(blocks > 148 * 16 ? 148 * 16 : blocks), threads, 0, stream>>>(
+      reinterpret_cast<__nv_bfloat16*>(dst_bf16), seed ^ 0xD1B54A32D192ED03ull, offset, count);
   return cudaGetLastError();
 }
 

@@ -15,6 +15,12 @@ namespace pi05 {
 cudaError_t launch_lcg_fill(void* dst_bf16, uint64_t seed, uint64_t offset, long long count,
                             cudaStream_t stream);
 
+// dst[i] = bf16 of element (offset + i) of the seeded N(0, 0.02) stream: a counter-based
+// generator (SplitMix64 keyed by the seed, twelve 16-bit fields summed), the distribution the
+// benchmark configurations name; same element order as the stream above.
+cudaError_t launch_normal_fill(void* dst_bf16, uint64_t seed, uint64_t offset, long long count,
+                               cudaStream_t stream);
+
 // src bf16 [k, n] row-major  ->  dst bf16 [*, ldk] rows map(n), columns 0..k-1.
 // map(n) = row_offset + n, or with interleave != 0:
 //          (n / 64) * 128 + slot * 64 + n % 64   (gate/up interleave for fused GeGLU).

@@ -18,11 +18,13 @@ from typing import Dict, List, Optional
 import numpy as np
 
 from . import _lib
-from ._abi_decls import Gemma, ModelConfig
+from ._abi_decls import EngineOptions, Gemma, ModelConfig
 from ._lib import check, lib
 
 DTYPES = {"bf16": 0, "fp8": 1, "int8": 2, "w8a8": 2}
 LAYOUTS = {"nhwc": 0, "nchw": 1}
+WEIGHT_DISTS = {"lcg": 0, "normal": 1}
+INT8_ACTIVATIONS = {"dynamic": 0, "static": 1}
 
 
 @dataclass(frozen=True)
@@ -251,15 +253,41 @@ class Pi05Runtime:
 
     @classmethod
     def random(cls, config=None, dtype: str = "bf16", seed: int = 0, device: int = 0,
-               fp8_act_scale: float = 1.0) -> "Pi05Runtime":
+               fp8_act_scale: float = 1.0, weights_dist: str = "lcg",
+               int8_activations: str = "dynamic",
+               activation_scales: Optional[Dict[str, float]] = None) -> "Pi05Runtime":
+        """Seeded random weights. `weights_dist`: "lcg" (the reference generator, uniform
+        +-0.02) or "normal" (N(0, 0.02)); `int8_activations`: "dynamic" (per-row, the
+        reference) or "static" (per-tensor); `fp8_act_scale`: the uniform static activation
+        scale (FP8, static INT8); `activation_scales`: per-site overrides by the reference's
+        calibration names."""
         config = Pi05Config() if config is None else Pi05Config.from_any(config)
         if dtype not in DTYPES:
             raise ValueError(f"--dtype must be bf16, fp8 or int8, got {dtype}")
+        if weights_dist not in WEIGHT_DISTS:
+            raise ValueError(f"weights_dist must be lcg or normal, got {weights_dist}")
+        if int8_activations not in INT8_ACTIVATIONS:
+            raise ValueError(f"int8_activations must be dynamic or static, got {int8_activations}")
         c = config.to_c()
+        options = EngineOptions(dtype=DTYPES[dtype], device=device, seed=seed,
+                                act_scale=fp8_act_scale, weight_dist=WEIGHT_DISTS[weights_dist],
+                                int8_activations=INT8_ACTIVATIONS[int8_activations])
         handle = C.c_void_p()
-        check(lib().pi05_engine_create(C.byref(c), DTYPES[dtype], device, seed, fp8_act_scale,
-                                       C.byref(handle)), "pi05_engine_create")
-        return cls(config, "int8" if dtype == "w8a8" else dtype, handle.value, device)
+        check(lib().pi05_engine_create_ex(C.byref(c), C.byref(options), C.byref(handle)),
+              "pi05_engine_create_ex")
+        runtime = cls(config, "int8" if dtype == "w8a8" else dtype, handle.value, device)
+        for site, scale in (activation_scales or {}).items():
+            runtime.set_activation_scale(site, scale)
+        return runtime
+
+    def set_activation_scale(self, site: str, scale: float) -> None:
+        """Static activation scale of one GEMM-input site (reference calibration names,
+        crates/apxinf-model/src/pi05/runtime.rs:35-81); applies to graphs captured afterwards."""
+        check(lib().pi05_engine_set_activation_scale(self._h, site.encode(), float(scale)),
+              f"pi05_engine_set_activation_scale({site})")
+
+    def activation_scale(self, site: str) -> float:
+        return float(lib().pi05_engine_activation_scale(self._h, site.encode()))
 
     def close(self) -> None:
         if self._h:

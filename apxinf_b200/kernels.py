@@ -41,7 +41,7 @@ def new_status(device="cuda") -> torch.Tensor:
 def gemm(a, b, out, *, op, mode=_lib.EPI_STORE, out_type=_lib.OUT_BF16, bias=None,
          residual=None, col_scale=None, row_scale=None, pos=None, gate=None, alpha=1.0,
          out_inv_scale=1.0, b_mn_major=False, status=None, stream=None, force_swap=-1,
-         force_block_n=0, partials=None, tile_counters=None, force_split_k=0, trace=None,
+         force_block_n=0, partials=None, tile_counters=None, force_split_k=0,
          static_scratch=False, b_blocked=None):
     """out[.., M, N'] = epilogue(a[.., M, K] @ b[.., N, K]^T); see Pi05GemmArgs."""
     m, k, lda, nb0, nb1, a_sb0, a_sb1 = _operand(a)
@@ -73,7 +73,7 @@ def gemm(a, b, out, *, op, mode=_lib.EPI_STORE, out_type=_lib.OUT_BF16, bias=Non
         partials_bytes=(partials.numel() * partials.element_size() if partials is not None else 0),
         tile_counters=_ptr(tile_counters),
         max_tiles=(tile_counters.numel() if tile_counters is not None else 0),
-        force_split_k=force_split_k, trace=_ptr(trace),
+        force_split_k=force_split_k,
         b_blocked=int(b_blocked is not None))
     if static_scratch:
         check(lib().pi05_gemm_static_scratch(C.byref(args), _stream_ptr(stream)),

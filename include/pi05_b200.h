@@ -34,7 +34,8 @@ typedef enum Pi05Status {
 
 /* Operand / output element types and fused epilogues of pi05_gemm. */
 enum { PI05_OP_BF16 = 0, PI05_OP_E4M3 = 1, PI05_OP_S8 = 2 };
-enum { PI05_OUT_BF16 = 0, PI05_OUT_E4M3 = 1, PI05_OUT_F32 = 2, PI05_OUT_S32 = 3 };
+/* PI05_OUT_S8: static per-tensor int8, clamp(round_half_away(bf16(o) * out_inv_scale), -128, 127) */
+enum { PI05_OUT_BF16 = 0, PI05_OUT_E4M3 = 1, PI05_OUT_F32 = 2, PI05_OUT_S32 = 3, PI05_OUT_S8 = 4 };
 enum {
   PI05_EPI_STORE = 0,
   PI05_EPI_BIAS_GELU = 1,
@@ -77,6 +78,8 @@ typedef struct Pi05GemmArgs {
   int32_t pos_rows;
   int64_t pos_ld;
   const void* gate;       /* bf16 [n] */
+  /* bias, col_scale and gate may be produced by an earlier kernel on the same stream: the
+   * kernel reads them after its stream-order dependency is resolved. */
   float alpha;
   float out_inv_scale;
   int32_t* status;        /* device int32, must be 0 before the call; set on device timeouts */
@@ -90,10 +93,6 @@ typedef struct Pi05GemmArgs {
   int32_t* tile_counters;
   int32_t max_tiles;
   int32_t force_split_k;  /* 0 auto, 1 off, n = n splits */
-  /* Optional device uint32[6]: SM-clock deltas from kernel entry of CTA (0,0,0) to {setup
-   * done, first operands landed, last MMA issued, accumulator ready, epilogue done, TMEM
-   * freed}. NULL = off. */
-  uint32_t* trace;
   /* != 0: `b` is stored K-block-major, [ceil(k / kb)][n][kb] with kb = 128 bytes of K (64 bf16
    * or 128 one-byte elements, the tail block zero padded), so each tile load is one
    * contiguous run; ldb and the batch strides of b are ignored. */
@@ -118,7 +117,9 @@ int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream);
  * status word are still the caller's. A request whose tiles x splits need more than the fixed
  * scratch is refused with PI05_ERR_SCRATCH_LIMIT before anything is launched (detail text in
  * pi05_last_cuda_error()). The call performs no cudaMalloc / cudaFree and uses no allocating
- * library routine.
+ * library routine. `cuda_stream` must belong to the current device (PI05_ERR_INVALID_VALUE
+ * otherwise). Requests that cannot be split (PI05_OUT_S32 output, or K within one 128-byte
+ * block) run as a single pass and leave the scratch untouched.
  *
  * The first call on each device looks up the array's device address (with that device
  * current) and remembers it; make that first call during set-up, before any stream capture.
@@ -156,8 +157,6 @@ typedef struct Pi05AttentionArgs {
   int32_t out_e4m3;
   float out_inv_scale;
   int32_t* status; /* device int32, 0 before the call */
-  uint32_t* trace;    /* reserved (phase stamps of an earlier kernel): pass NULL */
-  int32_t trace_item; /* reserved: pass 0 */
   /* key_split != 0: one CTA per (query tile, 64-key slice) writes partial outputs to
    * split_scratch and a second launch combines them; for calls with few query tiles.
    * split_scratch needs tiles * ceil(keys / 64) * 128 * (head_dim + 2) * 4 bytes
@@ -209,6 +208,40 @@ void pi05_default_config(Pi05ModelConfig* config);
  * Allocates device memory. Replaces Pi05{Bf16,,Int8}CudaRuntime::new. */
 int pi05_engine_create(const Pi05ModelConfig* config, int32_t dtype, int32_t device, uint64_t seed,
                        float fp8_act_scale, Pi05Engine** out);
+
+/* The same with the two choices the benchmark configurations word differently from the
+ * reference code:
+ *   weight_dist       PI05_WEIGHTS_LCG: the reference generator, uniform in [-0.02, 0.02)
+ *                     (weights.rs:332-357); PI05_WEIGHTS_NORMAL: seeded N(0, 0.02) from a
+ *                     counter-based generator (SplitMix64 keyed by the seed; element order as
+ *                     the reference's tensor order).
+ *   int8_activations  PI05_INT8_ACT_DYNAMIC: one scale per activation row, computed on the fly
+ *                     (crates/apxinf-cuda/src/kernels/gemm/w8a8.rs:86-98);
+ *                     PI05_INT8_ACT_STATIC: one fixed scale per GEMM input, the quantiser
+ *                     fused into the norm kernels and GEMM epilogues like the FP8 path's.
+ * act_scale is the uniform static activation scale (FP8, static INT8); single sites are set by
+ * name with pi05_engine_set_activation_scale. */
+enum { PI05_WEIGHTS_LCG = 0, PI05_WEIGHTS_NORMAL = 1 };
+enum { PI05_INT8_ACT_DYNAMIC = 0, PI05_INT8_ACT_STATIC = 1 };
+typedef struct Pi05EngineOptions {
+  int32_t dtype;   /* PI05_DTYPE_* */
+  int32_t device;
+  uint64_t seed;
+  float act_scale;
+  int32_t weight_dist;
+  int32_t int8_activations;
+} Pi05EngineOptions;
+int pi05_engine_create_ex(const Pi05ModelConfig* config, const Pi05EngineOptions* options,
+                          Pi05Engine** out);
+/* Static activation scale of one GEMM-input site, named as the reference's calibration table
+ * (Pi05ActivationScales::from_calibration, crates/apxinf-model/src/pi05/runtime.rs:35-81):
+ * "vision.patch_input", "vision.layers.<i>.attention_norm" / ".attention_output" / ".mlp_norm" /
+ * ".mlp_activation", "vision.post_norm", "language.layers.<i>.<same four>", "action.input",
+ * "time.input", "time.hidden", "action.conditioning", "action.layers.<i>.<same four>",
+ * "action.final_norm". Takes effect for graphs captured afterwards. Unknown names and
+ * non-positive scales return PI05_ERR_INVALID_VALUE. */
+int pi05_engine_set_activation_scale(Pi05Engine* engine, const char* site, float scale);
+float pi05_engine_activation_scale(const Pi05Engine* engine, const char* site); /* 0 if unknown */
 void pi05_engine_destroy(Pi05Engine* engine);
 size_t pi05_engine_weight_bytes(const Pi05Engine* engine);
 /* Copies a device weight tensor ("language.3.qkv.weight", ".scale", ".bias", ...) to the host;

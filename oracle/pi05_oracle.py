@@ -139,6 +139,15 @@ def quantize_rows_int8(x: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
     return q, scale
 
 
+def quantize_int8_static(x: np.ndarray, scale: float) -> np.ndarray:
+    """Static per-tensor INT8 (the benchmark's W8A8 wording): x * (1/scale), half-away
+    rounding, clamp to [-128, 127]."""
+    inv = F32(1.0) / F32(scale)
+    t = np.asarray(x, F32) * inv
+    q = np.sign(t) * np.floor(np.abs(t) + F32(0.5))
+    return np.clip(q, -128.0, 127.0).astype(F32)
+
+
 def quantize_int8_channels(w_in_out: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
     """Per-output-channel INT8 weights of an [in, out] matrix (int8_weights.rs:92-123)."""
     w = np.asarray(w_in_out, F32)
@@ -323,6 +332,53 @@ def lcg_values(seed: int, offset: int, count: int) -> np.ndarray:
     return out
 
 
+# Seeded N(0, 0.02) weights (the benchmark configurations' wording; the reference generator
+# above is uniform). Counter-based so that any element can be produced anywhere: element i of
+# the stream is the sum of twelve 16-bit fields of three SplitMix64 outputs (counters 3i,
+# 3i+1, 3i+2 keyed by the seed) - an Irwin-Hall sum with mean 393210 and standard deviation
+# 65536 - centred and scaled by 0.02 / 65536. Integer sums and one float32 multiply: the GPU
+# generator (weights.cu, normal_fill_kernel) reproduces it bit for bit.
+NORMAL_KEY_XOR = 0xD1B54A32D192ED03
+SPLITMIX_GAMMA = 0x9E3779B97F4A7C15
+
+
+def _splitmix64(x: np.ndarray) -> np.ndarray:
+    with np.errstate(over="ignore"):
+        z = x
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        return z ^ (z >> np.uint64(31))
+
+
+def _normal_block(key: int, start: int, out: np.ndarray) -> None:
+    idx = np.arange(start, start + out.shape[0], dtype=np.uint64)
+    total = np.zeros(out.shape[0], dtype=np.int64)
+    with np.errstate(over="ignore"):
+        for j in range(3):
+            counter = idx * np.uint64(3) + np.uint64(j + 1)
+            z = _splitmix64(np.uint64(key) + counter * np.uint64(SPLITMIX_GAMMA))
+            for field in range(4):
+                total += ((z >> np.uint64(16 * field)) & np.uint64(0xFFFF)).astype(np.int64)
+    centred = (total - 393210).astype(F32)
+    out[:] = round_bf16(centred * F32(0.02 / 65536.0))
+
+
+def normal_values(seed: int, offset: int, count: int) -> np.ndarray:
+    """Elements [offset, offset+count) of the seeded N(0, 0.02) stream, bf16-rounded float32."""
+    key = (seed ^ NORMAL_KEY_XOR) & MASK64
+    out = np.empty(count, dtype=F32)
+    starts = list(range(0, count, _LCG_BLOCK))
+    if len(starts) <= 2:
+        for b in starts:
+            _normal_block(key, offset + b, out[b:b + _LCG_BLOCK])
+    else:
+        import concurrent.futures
+        import os
+        with concurrent.futures.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
+            list(pool.map(lambda b: _normal_block(key, offset + b, out[b:b + _LCG_BLOCK]), starts))
+    return out
+
+
 def synthetic_layout(cfg: Pi05Config) -> Dict[str, Tuple[int, Tuple[int, ...]]]:
     """name -> (element offset in the LCG stream, shape) in generation order."""
     table: Dict[str, Tuple[int, Tuple[int, ...]]] = {}
@@ -385,9 +441,12 @@ class SyntheticWeights:
     """Lazily generated `Pi05Weights::synthetic(config, seed)`; tensors are float32 holding
     bf16 values, linear weights in the reference's [in, out] orientation."""
 
-    def __init__(self, cfg: Pi05Config, seed: int = 0):
+    def __init__(self, cfg: Pi05Config, seed: int = 0, dist: str = "lcg"):
+        assert dist in ("lcg", "normal")
         self.cfg = cfg
         self.seed = seed
+        self.dist = dist  # "lcg": the reference's uniform +-0.02 stream; "normal": N(0, 0.02)
+        self._values = lcg_values if dist == "lcg" else normal_values
         self.layout = synthetic_layout(cfg)
         self._cache: Dict[str, np.ndarray] = {}
         self.cache_prefixes = ("action", "time_mlp", "vision.patch", "vision.position", "vision.projector")
@@ -396,7 +455,7 @@ class SyntheticWeights:
         if name in self._cache:
             return self._cache[name]
         offset, shape = self.layout[name]
-        value = lcg_values(self.seed, offset, int(np.prod(shape))).reshape(shape)
+        value = self._values(self.seed, offset, int(np.prod(shape))).reshape(shape)
         if name.startswith(self.cache_prefixes):
             self._cache[name] = value
         return value
@@ -405,7 +464,7 @@ class SyntheticWeights:
         """Selected rows of a 2-D tensor without generating the rest (token embedding)."""
         offset, shape = self.layout[name]
         width = shape[1]
-        return np.stack([lcg_values(self.seed, offset + int(r) * width, width) for r in row_ids])
+        return np.stack([self._values(self.seed, offset + int(r) * width, width) for r in row_ids])
 
     def packed(self, names) -> np.ndarray:
         return np.concatenate([self.get(n + ".weight") for n in names], axis=1)
@@ -502,6 +561,12 @@ class OracleOptions:
     vision_round_scores: bool = False  # round SigLIP logits/probabilities to storage
     mqa_round_scores: bool = True      # cublas_adapter.cu:109-130 rounds both
     collect: bool = False              # keep named intermediates
+    int8_act: str = "dynamic"          # "dynamic": per-row absmax/127 (w8a8.rs:86-98) | "static"
+    # static activation scale per GEMM-input site, named as the reference's calibration table
+    # (runtime.rs:35-81: "vision.layers.3.mlp_norm", "action.input", ...); sites not listed use
+    # `act_scale`. Applies to FP8 and to INT8 with int8_act == "static".
+    act_scales: Optional[Dict[str, float]] = None
+    calibrate: bool = False            # record the absmax of every site's input in `amax`
 
 
 class Pi05Oracle:
@@ -513,6 +578,13 @@ class Pi05Oracle:
         self.trace: Dict[str, np.ndarray] = {}
         self._prepared: Dict[str, tuple] = {}
         self.int32_trace: Dict[str, np.ndarray] = {}
+        self.amax: Dict[str, float] = {}
+
+    def site_scale(self, site: Optional[str]) -> float:
+        table = self.o.act_scales
+        if table is not None and site is not None and site in table:
+            return float(table[site])
+        return float(self.o.act_scale)
 
     # ---- linear layers -----------------------------------------------------
     def _prepare(self, key: str, names) -> tuple:
@@ -530,21 +602,32 @@ class Pi05Oracle:
             self._prepared[key] = prepared
         return prepared
 
-    def linear(self, pre: np.ndarray, names, *, direct: bool = False, key: Optional[str] = None):
+    def linear(self, pre: np.ndarray, names, *, direct: bool = False, key: Optional[str] = None,
+               site: Optional[str] = None):
         """GEMM output rounded to storage (no bias). `pre` is the float32 producer value;
         `direct` says the FP8 path quantises it straight from float32 (fused producer) instead
-        of from the storage-rounded tensor."""
+        of from the storage-rounded tensor. `site` names the input's static activation scale."""
         if isinstance(names, str):
             names = [names]
         key = key or "+".join(names)
         w, ws = self._prepare(key, names)
+        if self.o.calibrate and site is not None:
+            self.amax[site] = max(self.amax.get(site, 0.0), float(np.max(np.abs(self.rs(pre)))))
         if self.o.dtype == "bf16":
             out = self.rs(pre) @ w
         elif self.o.dtype == "fp8":
+            scale = self.site_scale(site)
             src = pre if direct else self.rs(pre)
-            xq = quantize_e4m3_static(src, self.o.act_scale)
+            xq = quantize_e4m3_static(src, scale)
             acc = xq @ w
-            out = (acc * F32(self.o.act_scale)) * ws[None, :]
+            out = (acc * F32(scale)) * ws[None, :]
+        elif self.o.int8_act == "static":
+            scale = self.site_scale(site)
+            xq = quantize_int8_static(self.rs(pre), scale)
+            acc = _chunked_int_matmul(xq, w)
+            if self.o.collect:
+                self.int32_trace[key] = acc.astype(np.int64)
+            out = (acc.astype(F32) * F32(scale)) * ws[None, :]
         else:
             xq, rs_ = quantize_rows_int8(self.rs(pre))
             acc = _chunked_int_matmul(xq, w)
@@ -620,7 +703,7 @@ class Pi05Oracle:
         cfg, rs = self.cfg, self.rs
         patches = patchify(images_u8, cfg)
         self._keep("patches", rs(patches))
-        x = self.linear(patches, "vision.patch_embedding")
+        x = self.linear(patches, "vision.patch_embedding", site="vision.patch_input")
         pos = self.w.get("vision.position_embedding")
         reps = cfg.num_views
         x = rs((x + np.tile(pos, (reps, 1))) + self.bias("vision.patch_embedding")[None, :])
@@ -631,7 +714,7 @@ class Pi05Oracle:
         for i in range(cfg.vision_depth):
             p = f"vision.{i}"
             names = [p + ".q", p + ".k", p + ".v"]
-            qkv = self.linear(n, names, direct=True)
+            qkv = self.linear(n, names, direct=True, site=f"vision.layers.{i}.attention_norm")
             qkv = rs(qkv + self.bias(names)[None, :])
             vw = cfg.vision_width
             attn = np.empty((x.shape[0], vw), dtype=F32)
@@ -641,16 +724,16 @@ class Pi05Oracle:
                 k = qkv[rows, vw:2 * vw].reshape(pp, heads, hd)
                 v = qkv[rows, 2 * vw:].reshape(pp, heads, hd)
                 attn[rows] = self.attention(q, k, v, scale, self.o.vision_round_scores)
-            proj = self.linear(attn, p + ".o")
+            proj = self.linear(attn, p + ".o", site=f"vision.layers.{i}.attention_output")
             h = rs((proj + x) + self.bias(p + ".o")[None, :])
             n2 = self.layer_norm(h)
-            f1 = self.linear(n2, p + ".fc1", direct=True)
+            f1 = self.linear(n2, p + ".fc1", direct=True, site=f"vision.layers.{i}.mlp_norm")
             act = gelu_tanh(f1 + self.bias(p + ".fc1")[None, :])
-            f2 = self.linear(act, p + ".fc2", direct=True)
+            f2 = self.linear(act, p + ".fc2", direct=True, site=f"vision.layers.{i}.mlp_activation")
             x = rs((f2 + h) + self.bias(p + ".fc2")[None, :])
             self._keep(f"vision.{i}.hidden", x)
             n = self.layer_norm(x)
-        proj = self.linear(n, "vision.projector", direct=True)
+        proj = self.linear(n, "vision.projector", direct=True, site="vision.post_norm")
         out = rs(proj + self.bias("vision.projector")[None, :])
         self._keep("vision.tokens", out)
         return out
@@ -675,18 +758,21 @@ class Pi05Oracle:
         for i in range(g.depth):
             p = f"language.{i}"
             n = self.rms_norm(x)
-            qkv = self.linear(n, [p + ".q", p + ".k", p + ".v"], direct=True)
+            qkv = self.linear(n, [p + ".q", p + ".k", p + ".v"], direct=True,
+                              site=f"language.layers.{i}.attention_norm")
             q, k, v = self.rope_split(qkv, g, positions)
             keys.append(k)
             values.append(v)
             if i + 1 < g.depth:
                 attn = self.attention(q, k, v, scale, self.o.mqa_round_scores)
-                proj = self.linear(attn, p + ".o")
+                proj = self.linear(attn, p + ".o", site=f"language.layers.{i}.attention_output")
                 h = rs(proj + x)
                 n2 = self.rms_norm(h)
-                gu = self.linear(n2, [p + ".gate", p + ".up"], direct=True)
+                gu = self.linear(n2, [p + ".gate", p + ".up"], direct=True,
+                                 site=f"language.layers.{i}.mlp_norm")
                 act = gelu_tanh(gu[:, :g.mlp_dim]) * gu[:, g.mlp_dim:]
-                down = self.linear(act, p + ".down", direct=True)
+                down = self.linear(act, p + ".down", direct=True,
+                                   site=f"language.layers.{i}.mlp_activation")
                 x = rs(down + h)
                 self._keep(f"language.{i}.hidden", x)
         return keys, values
@@ -696,13 +782,13 @@ class Pi05Oracle:
         aw = cfg.action_expert.width
         emb = sinusoidal_time_embedding(step_time, aw, cfg.time_min_period, cfg.time_max_period)
         emb = rs(emb)[None, :]
-        hidden = self.linear(emb, "time_mlp_in")
+        hidden = self.linear(emb, "time_mlp_in", site="time.input")
         hidden = silu(hidden + self.bias("time_mlp_in")[None, :])
-        out = self.linear(hidden, "time_mlp_out", direct=True)
+        out = self.linear(hidden, "time_mlp_out", direct=True, site="time.hidden")
         cond = silu(out + self.bias("time_mlp_out")[None, :])
 
         def style(name):
-            proj = self.linear(cond, name, direct=True)
+            proj = self.linear(cond, name, direct=True, site="action.conditioning")
             return rs(proj + self.bias(name)[None, :])[0]
 
         attention = [style(f"action.{i}.input_style") for i in range(cfg.action_expert.depth)]
@@ -718,26 +804,29 @@ class Pi05Oracle:
         scale = 1.0 / math.sqrt(g.head_dim)
         for step, t in enumerate(flow_times(cfg.num_flow_steps)):
             style_attn, style_mlp, style_final = self.step_styles(float(t))
-            h = self.linear(x, "action_in")
+            h = self.linear(x, "action_in", site="action.input")
             h = rs(h + self.bias("action_in")[None, :])
             n = self.ada_rms_norm(h, style_attn[0])
             for i in range(g.depth):
                 p = f"action.{i}"
-                qkv = self.linear(n, [p + ".q", p + ".k", p + ".v"], direct=True)
+                qkv = self.linear(n, [p + ".q", p + ".k", p + ".v"], direct=True,
+                                  site=f"action.layers.{i}.attention_norm")
                 q, k, v = self.rope_split(qkv, g, positions)
                 kk = np.concatenate([keys[i], k], axis=0)
                 vv = np.concatenate([values[i], v], axis=0)
                 attn = self.attention(q, kk, vv, scale, self.o.mqa_round_scores)
-                proj = self.linear(attn, p + ".o")
+                proj = self.linear(attn, p + ".o", site=f"action.layers.{i}.attention_output")
                 h = rs(h + proj * style_attn[i][None, 2 * aw:])
                 n = self.ada_rms_norm(h, style_mlp[i])
-                gu = self.linear(n, [p + ".gate", p + ".up"], direct=True)
+                gu = self.linear(n, [p + ".gate", p + ".up"], direct=True,
+                                 site=f"action.layers.{i}.mlp_norm")
                 act = gelu_tanh(gu[:, :g.mlp_dim]) * gu[:, g.mlp_dim:]
-                down = self.linear(act, p + ".down", direct=True)
+                down = self.linear(act, p + ".down", direct=True,
+                                   site=f"action.layers.{i}.mlp_activation")
                 h = rs(h + down * style_mlp[i][None, 2 * aw:])
                 nxt = style_attn[i + 1] if i + 1 < g.depth else style_final
                 n = self.ada_rms_norm(h, nxt)
-            vel = self.linear(n, "action_out", direct=True)
+            vel = self.linear(n, "action_out", direct=True, site="action.final_norm")
             vel = rs(vel + self.bias("action_out")[None, :])
             x = rs(x + dt * vel)
             self._keep(f"action.step{step}", x)
@@ -755,9 +844,10 @@ class Pi05Oracle:
         return self.denoise(noise, keys, values, prefix.shape[0])
 
 
-def infer(cfg: Pi05Config, seed: int, images_u8, token_ids, noise, **options) -> np.ndarray:
+def infer(cfg: Pi05Config, seed: int, images_u8, token_ids, noise, weights_dist: str = "lcg",
+          **options) -> np.ndarray:
     """One PI0.5 policy forward with `Pi05Weights::synthetic(cfg, seed)` weights: [H, action_dim]."""
-    oracle = Pi05Oracle(cfg, SyntheticWeights(cfg, seed), OracleOptions(**options))
+    oracle = Pi05Oracle(cfg, SyntheticWeights(cfg, seed, weights_dist), OracleOptions(**options))
     return oracle.infer(images_u8, token_ids, noise)
 
 

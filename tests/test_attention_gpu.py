@@ -22,11 +22,10 @@ class AttentionArgs(C.Structure):
                 ("q_rows", C.c_int32), ("keys", C.c_int32), ("head_dim", C.c_int32),
                 ("nb0", C.c_int32), ("nb1", C.c_int32), ("scale", C.c_float),
                 ("out_e4m3", C.c_int32), ("out_inv_scale", C.c_float), ("status", C.c_void_p),
-                ("trace", C.c_void_p), ("trace_item", C.c_int32),
                 ("key_split", C.c_int32), ("split_scratch", C.c_void_p), ("split_scratch_bytes", C.c_int64)]
 
 
-def run(q, k, v, out, scale, nb0=1, nb1=1, strides=None, e4m3=False, inv=1.0, trace=None, trace_item=0, key_split=False):
+def run(q, k, v, out, scale, nb0=1, nb1=1, strides=None, e4m3=False, inv=1.0, key_split=False):
     """q/k/v/out: torch CUDA tensors; strides: dict name -> (ld, sb0, sb1) in elements."""
     from apxinf_b200 import lib
     handle = lib()
@@ -40,8 +39,7 @@ def run(q, k, v, out, scale, nb0=1, nb1=1, strides=None, e4m3=False, inv=1.0, tr
         v=v.data_ptr(), v_ld=s["v"][0], v_sb0=s["v"][1], v_sb1=s["v"][2],
         out=out.data_ptr(), out_ld=s["o"][0], out_sb0=s["o"][1], out_sb1=s["o"][2],
         q_rows=s["rows"], keys=s["keys"], head_dim=s["hd"], nb0=nb0, nb1=nb1, scale=scale,
-        out_e4m3=int(e4m3), out_inv_scale=inv, status=status.data_ptr(),
-        trace=(trace.data_ptr() if trace is not None else None), trace_item=trace_item)
+        out_e4m3=int(e4m3), out_inv_scale=inv, status=status.data_ptr())
     if key_split:
         scratch = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
         args.key_split, args.split_scratch, args.split_scratch_bytes = 1, scratch.data_ptr(), scratch.numel()
@@ -174,6 +172,49 @@ def test_key_split_path_matches_the_exact_softmax(q_rows, keys, batch, hd, heads
     got = out.float().cpu() / (16.0 if e4m3 else 1.0)
     tol = 0.02 + (0.07 * want.abs().max().item() if e4m3 else 0.0)
     assert (got - want).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("pattern", ["increasing", "decreasing", "some_rows"])
+@pytest.mark.parametrize("layout", ["mqa_hd256", "heads_hd72"])
+def test_running_maximum_moves_between_key_blocks(pattern, layout):
+    """The fused kernel moves its running row maximum only when a 128-key block exceeds it by
+    more than 2^8, and then rescales the output accumulator in tensor memory. Random scores
+    never do that, so here every block's scores are shifted by a multiple of 8 nats (11.5
+    powers of two) through one query/key component: growing from block to block (a rescale at
+    every block), falling (never), and growing for every other query row only (rows of one
+    warp disagree). Checked against the float64 softmax with a relative tolerance."""
+    gen = torch.Generator().manual_seed(11)
+    if layout == "mqa_hd256":
+        heads, hd, q_rows, keys, shared = 8, 256, 37, 600, True   # packed multi-query tiles
+    else:
+        heads, hd, q_rows, keys, shared = 3, 72, 200, 300, False  # odd head_dim, ragged last block
+    scale = 1.0 / math.sqrt(hd)
+    q = torch.randn(1, q_rows, heads, hd, generator=gen)
+    kv_heads = 1 if shared else heads
+    k = torch.randn(1, kv_heads, keys, hd, generator=gen)
+    v = torch.randn(1, kv_heads, keys, hd, generator=gen)
+    blocks = (keys + 127) // 128
+    step = 8.0 / (4.0 * scale)          # k component that shifts a block's scores by 8 nats
+    q[..., 0] = 4.0
+    if pattern == "some_rows":
+        q[:, 1::2, :, 0] = 0.0
+    for j in range(blocks):
+        level = j if pattern != "decreasing" else blocks - 1 - j
+        k[:, :, j * 128:(j + 1) * 128, 0] = level * step
+    q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+    out = torch.full((1, q_rows, heads, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kv_sb0 = 0 if shared else keys * hd
+    rc, status = run(q.cuda(), k.cuda(), v.cuda(), out, scale, nb0=heads, nb1=1,
+                     strides=dict(q=(heads * hd, hd, q_rows * heads * hd), k=(hd, kv_sb0, kv_heads * keys * hd),
+                                  v=(hd, kv_sb0, kv_heads * keys * hd), o=(heads * hd, hd, q_rows * heads * hd),
+                                  rows=q_rows, keys=keys, hd=hd))
+    assert rc == 0 and status == 0
+    want = reference(q.float().permute(0, 2, 1, 3), k.float().expand(1, heads, keys, hd),
+                     v.float().expand(1, heads, keys, hd), scale).permute(0, 2, 1, 3)
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    err = (got - want).abs()
+    assert (err <= 0.01 * want.abs() + 0.01).all(), err.max().item()
 
 
 def test_key_split_needs_scratch():

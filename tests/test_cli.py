@@ -34,14 +34,15 @@ def test_flag_validation_messages():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("dtype", ["bf16", "w8a8"])
+@pytest.mark.parametrize("dtype", ["bf16", "fp8", "w8a8"])
 def test_report_has_the_reference_keys(dtype):
+    extra = ["--calibration", "uniform:0.05"] if dtype == "fp8" else []
     r = _run("random", "--dtype", dtype, "--views", "1", "--token-count", "8", "--iterations", "3",
-             "--image-input", "nhwc", "--num-flow-steps", "2")
+             "--image-input", "nhwc", "--num-flow-steps", "2", *extra)
     assert r.returncode == 0, r.stderr[-2000:]
     report = json.loads(r.stdout)
     assert report["profile"] == "pi05_1view_h10_steps2"
-    assert report["precision"] == ("bf16" if dtype == "bf16" else "int8_w8a8")
+    assert report["precision"] == {"bf16": "bf16", "fp8": "fp8", "w8a8": "int8_w8a8"}[dtype]
     assert report["weights"] == "synthetic" and report["token_count"] == 8 and report["iterations"] == 3
     assert set(report["latency_ms"]) == {"min", "p50", "p95", "max", "mean", "standard_deviation"}
     assert set(report["image_input"]) == {"kind", "graph_includes_cuda_preprocess",

@@ -141,3 +141,102 @@ def test_capture_rejects_bad_shapes(cfg):
     with pytest.raises(Pi05Error):
         rt.capture_infer_rgb_u8(cfg.max_token_len + 1, "nhwc", 1)
     rt.close()
+
+
+# ---- the benchmark configurations' wording: N(0, 0.02) weights, static INT8 activations ----
+
+
+def test_normal_weights_bit_exact(cfg):
+    """The seeded N(0, 0.02) generator on the GPU equals the oracle's counter-based stream."""
+    from apxinf_b200.engine import Pi05Runtime
+    rt = Pi05Runtime.random(cfg, dtype="bf16", seed=3, device=0, weights_dist="normal")
+    w = O.SyntheticWeights(cfg, 3, "normal")
+    want = w.packed(["language.1.q", "language.1.k", "language.1.v"]).T
+    got = _bf16(rt.read_weight("language.1.qkv.weight")).reshape(want.shape)
+    assert np.array_equal(got, want)
+    assert np.array_equal(_bf16(rt.read_weight("time_mlp_out.bias")), w.get("time_mlp_out.bias"))
+    assert np.array_equal(_bf16(rt.read_weight("vision.position_embedding")).reshape(-1, cfg.vision_width),
+                          w.get("vision.position_embedding"))
+    values = w.get("vision.0.fc1.weight")
+    assert abs(float(values.std()) - 0.02) < 1e-3 and abs(float(values.mean())) < 1e-3
+    rt.close()
+
+
+@pytest.mark.parametrize("dtype,min_cos,max_abs", [("bf16", 0.999, 2e-2), ("fp8", 0.99, None),
+                                                     ("int8", 0.99, None)])
+def test_forward_with_normal_weights(cfg, dtype, min_cos, max_abs):
+    from apxinf_b200.engine import Pi05Runtime
+    token_count = 6
+    rt = Pi05Runtime.random(cfg, dtype=dtype, seed=5, device=0, fp8_act_scale=0.05,
+                            weights_dist="normal")
+    g = rt.capture_infer_rgb_u8(token_count, "nhwc", 1)
+    images, tokens, noise = O.synthetic_observation(cfg, 21, token_count)
+    got = g.infer_host(images[None], tokens[None], noise[None])[0]
+    want = O.infer(cfg, 5, images, tokens, noise, weights_dist="normal", dtype=dtype,
+                   act_scale=0.05, vision_round_scores=True)
+    m = O.compare(got, want)
+    assert m["cosine"] >= min_cos, m
+    if max_abs is not None:
+        assert m["max_abs"] <= max_abs, m
+    g.close()
+    rt.close()
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+def test_static_int8_activations_match_oracle(cfg, batch):
+    """One fixed scale per GEMM input, the quantiser fused into norms and epilogues. The site
+    table is calibrated by the oracle (dynamic pass, absmax / 127) and set by name."""
+    from apxinf_b200.engine import Pi05Runtime
+    token_count = 6
+    obs = [O.synthetic_observation(cfg, 300 + i, token_count) for i in range(batch)]
+    weights = O.SyntheticWeights(cfg, 3)
+    calib = O.Pi05Oracle(cfg, weights, O.OracleOptions(dtype="int8", calibrate=True,
+                                                       vision_round_scores=True))
+    for o in obs:
+        calib.infer(*o)
+    table = {site: max(a, 1e-6) / 127.0 for site, a in calib.amax.items()}
+    rt = Pi05Runtime.random(cfg, dtype="int8", seed=3, device=0, fp8_act_scale=0.05,
+                            int8_activations="static", activation_scales=table)
+    assert abs(rt.activation_scale("action.input") - table["action.input"]) < 1e-9
+    g = rt.capture_infer_rgb_u8(token_count, "nhwc", batch)
+    # the static path has no per-row quantiser launches
+    assert "quantize_rows_int8" not in g.launch_names()
+    got = g.infer_host(np.stack([o[0] for o in obs]), np.stack([o[1] for o in obs]),
+                       np.stack([o[2] for o in obs]))
+    for i in range(batch):
+        want = O.Pi05Oracle(cfg, weights, O.OracleOptions(
+            dtype="int8", int8_act="static", act_scales=table, vision_round_scores=True)).infer(*obs[i])
+        m = O.compare(got[i], want)
+        assert m["cosine"] >= 0.99, (i, m)
+    g.close()
+    rt.close()
+
+
+def test_activation_scale_sites(cfg):
+    """FP8 with two sites set away from the uniform scale follows the oracle given the same
+    table; unknown sites and bad values are refused."""
+    from apxinf_b200 import Pi05Error
+    from apxinf_b200.engine import Pi05Runtime
+    table = {"vision.layers.0.mlp_activation": 0.02, "action.layers.1.attention_norm": 0.08,
+             "language.layers.0.attention_output": 0.01, "action.input": 0.03}
+    rt = Pi05Runtime.random(cfg, dtype="fp8", seed=3, device=0, fp8_act_scale=0.05,
+                            activation_scales=table)
+    with pytest.raises(Pi05Error):
+        rt.set_activation_scale("vision.layers.99.mlp_norm", 0.1)
+    with pytest.raises(Pi05Error):
+        rt.set_activation_scale("action.input", -1.0)
+    assert rt.activation_scale("time.hidden") == pytest.approx(0.05)
+    token_count = 6
+    g = rt.capture_infer_rgb_u8(token_count, "nhwc", 1)
+    images, tokens, noise = O.synthetic_observation(cfg, 9, token_count)
+    got = g.infer_host(images[None], tokens[None], noise[None])[0]
+    want = O.infer(cfg, 3, images, tokens, noise, dtype="fp8", act_scale=0.05, act_scales=table,
+                   vision_round_scores=True)
+    uniform = O.infer(cfg, 3, images, tokens, noise, dtype="fp8", act_scale=0.05,
+                      vision_round_scores=True)
+    m = O.compare(got, want)
+    assert m["cosine"] >= 0.99, m
+    # the table matters: the engine is closer to the oracle with the table than without
+    assert m["rmse"] <= O.compare(got, uniform)["rmse"] + 1e-6
+    g.close()
+    rt.close()

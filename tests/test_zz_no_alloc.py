@@ -37,10 +37,24 @@ def test_static_scratch_matches_caller_scratch_twice(op):
                 tile_counters=counters, force_split_k=8)
     torch.cuda.synchronize()
     assert st.item() == 0 and want.float().abs().max().item() > 0
+    outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    status = K.new_status()
+    # first call on the device (address look-up) happens here if no earlier test made it
+    K.gemm(ad, bd, outs[0], op=op, bias=bias, alpha=alpha, force_split_k=8, static_scratch=True,
+           status=status)
+    torch.cuda.synchronize()
     for call in range(2):
-        got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
-        st = K.gemm(ad, bd, got, op=op, bias=bias, alpha=alpha, force_split_k=8, static_scratch=True)
+        got = outs[call]
+        got.fill_(float("nan"))
         torch.cuda.synchronize()
+        # the entry point takes no device memory: the driver's free-memory figure is the same
+        # before and after the call (outputs and the status word were allocated above)
+        free_before, _ = torch.cuda.mem_get_info()
+        st = K.gemm(ad, bd, got, op=op, bias=bias, alpha=alpha, force_split_k=8, static_scratch=True,
+                    status=status)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before, (free_before, free_after)
         assert st.item() == 0
         # same kernel, same split order: no tolerance needed (the GEMM tests allow one bf16
         # ulp against the CPU reference; here both sides are the GPU)
@@ -72,3 +86,22 @@ def test_static_scratch_large_rows_and_limits():
     assert info.value.code == -7 and "scratch" in str(info.value)
     with pytest.raises(Pi05Error):  # the entry point is the split-K variant only
         K.gemm(a, b, got, op=L.OP_BF16, out_type=L.OUT_F32, force_split_k=1, static_scratch=True)
+
+
+def test_static_scratch_wants_a_stream_of_the_current_device():
+    """The built-in array's address is the current device's; a stream of another device is
+    refused before anything is launched. Needs a second GPU to see the refusal."""
+    from apxinf_b200 import Pi05Error, _lib as L, kernels as K
+    a = torch.zeros(16, 256, dtype=torch.bfloat16, device="cuda:0")
+    b = torch.zeros(128, 256, dtype=torch.bfloat16, device="cuda:0")
+    out = torch.zeros(16, 128, dtype=torch.bfloat16, device="cuda:0")
+    # a non-default stream of the current device is accepted
+    side = torch.cuda.Stream(device=0)
+    K.gemm(a, b, out, op=L.OP_BF16, force_split_k=2, static_scratch=True, stream=side)
+    side.synchronize()
+    if torch.cuda.device_count() < 2:
+        return
+    other = torch.cuda.Stream(device=1)
+    with pytest.raises(Pi05Error) as info:
+        K.gemm(a, b, out, op=L.OP_BF16, force_split_k=2, static_scratch=True, stream=other)
+    assert info.value.code == -1
