@@ -27,8 +27,24 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import subprocess
 import sys
+
+
+def _host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+if "reference" in sys.argv[1:] or any(a.startswith("--impl=reference") for a in sys.argv[1:]):
+    # the CPU arm uses every host thread it may run on, whatever the launcher exported
+    # (torchrun sets OMP_NUM_THREADS=1); must happen before NumPy loads its BLAS
+    for _name in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_name] = str(_host_threads())
+
+import hashlib
+import subprocess
 import threading
 import time
 from dataclasses import replace
@@ -43,7 +59,45 @@ METRIC = "pi05_fp8_action_chunks_per_s"
 UNIT = "action chunks/s"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one language.gate_up launch at batch 64, from
+# the single-pass ncu capture summarised in
+# profiles/gemm_umma_persistent_e4m3_gate_up_batch64_dram_traffic.md, together with the git blob
+# id of the kernel source that was profiled: the bench line reports the traffic only while the
+# kernel source is still that one (null otherwise: a stale figure says nothing).
 GATE_UP_DRAM_BYTES_BATCH64 = 276.02e6 + 508.51e6
+GATE_UP_PROFILED_KERNEL_BLOB = "a7b660da6592"  # git hash-object apxinf_b200/csrc/gemm_umma.cuh (first 12)
+
+
+def kernel_source_blob() -> str:
+    data = (ROOT / "apxinf_b200" / "csrc" / "gemm_umma.cuh").read_bytes()
+    return hashlib.sha1(b"blob %d\0" % len(data) + data).hexdigest()[:12]
+
+
+def algorithmic_work(cfg, token_count: int, batch: int, weight_bytes: int):
+    """FLOPs of one batched forward and the minimum HBM bytes of one B=1 forward (every weight
+    read once per use, the KV cache once per flow step), from the GEMM table of the model:
+    vision patch/qkv/o/fc1/fc2/projector, language qkv/o/gate_up/down (17 full layers + the
+    last layer's K/V projection), action in/out/qkv/o/gate_up/down per flow step, and the
+    three attention shapes."""
+    V = cfg.num_views * cfg.patches_per_view
+    P, H, S = V + token_count, cfg.action_horizon, cfg.num_flow_steps
+    vw, lg, ac = cfg.vision_width, cfg.language, cfg.action_expert
+    qw = lg.num_heads * lg.head_dim
+    kvw = qw + 2 * lg.head_dim
+    vision_w = (3 * cfg.patch_size ** 2 * vw + cfg.vision_depth * (4 * vw * vw + 2 * vw * cfg.vision_mlp_dim)
+                + vw * lg.width)
+    language_full = lg.width * kvw + qw * lg.width + 3 * lg.width * lg.mlp_dim
+    language_w = (lg.depth - 1) * language_full + lg.width * kvw
+    action_layer = ac.width * kvw + qw * ac.width + 3 * ac.width * ac.mlp_dim
+    action_w = ac.depth * action_layer + 2 * cfg.action_dim * ac.width
+    gemm_flops = 2.0 * (V * vision_w + P * language_w + S * H * action_w)
+    attn_flops = (4.0 * cfg.vision_depth * cfg.num_views * cfg.vision_heads * cfg.patches_per_view ** 2
+                  * cfg.vision_head_dim
+                  + 4.0 * (lg.depth - 1) * lg.num_heads * P * P * lg.head_dim
+                  + 4.0 * S * ac.depth * ac.num_heads * H * (P + H) * ac.head_dim)
+    kv_bytes = 2 * lg.depth * (P + H) * lg.head_dim * 2
+    b1_bytes = weight_bytes * (vision_w + language_w + S * action_w) + (S + 1) * kv_bytes
+    return {"flops_per_step": batch * (gemm_flops + attn_flops), "b1_hbm_bytes": b1_bytes}
 
 
 def measured_peaks():
@@ -148,7 +202,11 @@ class CpuSample:
         self.oracle = O.Pi05Oracle(self.cfg, weights, O.OracleOptions(dtype="fp8", act_scale=0.05))
         self.oracle._prepare_all = True
         self.oracle.infer(*self.inputs)  # generates and caches the weights
-        self.threads = os.cpu_count() or 1
+        self.threads = _host_threads()
+        self.sampled = {"siglip_layers": [depth, full.vision_depth],
+                        "gemma_2b_layers": [depth, full.language.depth - 1],
+                        "expert_layers": [depth + 1, full.action_expert.depth],
+                        "flow_steps": [1, full.num_flow_steps]}
         self.sample = (
             f"NumPy oracle, FP8 arithmetic, B=1: {depth} of {full.vision_depth} SigLIP layers, "
             f"{depth} of {full.language.depth - 1} Gemma-2B layers, 1 of {full.num_flow_steps} "
@@ -187,11 +245,45 @@ def cpu_block_cfg1():
             "sample": f"{tokens} of 522 tokens timed ({seconds:.2f} s), scaled linearly"}
 
 
+def complete_cpu_forward(budget_s: float, estimate_generation_s: float):
+    """One complete oracle forward (every layer, every flow step) next to the scaled sample,
+    when generating the full 2.6 G synthetic weights fits the time budget and host memory."""
+    if estimate_generation_s > budget_s:
+        return {"skipped": f"generating the full weights would take about {estimate_generation_s:.0f} s "
+                           f"(budget {budget_s:.0f} s)"}
+    try:
+        available_gb = os.sysconf("SC_AVPHYS_PAGES") * os.sysconf("SC_PAGE_SIZE") / 2 ** 30
+    except (ValueError, OSError):
+        available_gb = 0.0
+    if available_gb < 48:
+        return {"skipped": f"{available_gb:.0f} GB of host memory free, 48 GB wanted for cached weights"}
+    from oracle import pi05_oracle as O
+    cfg = replace(O.Pi05Config(), num_views=2, action_horizon=50)
+    weights = O.SyntheticWeights(cfg, 0)
+    weights.cache_prefixes = ("",)
+    oracle = O.Pi05Oracle(cfg, weights, O.OracleOptions(dtype="fp8", act_scale=0.05))
+    oracle._prepare_all = True
+    inputs = O.synthetic_observation(cfg, 1234, 10)
+    t0 = time.perf_counter()
+    oracle.infer(*inputs)  # generates, quantises and caches every weight
+    first = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    oracle.infer(*inputs)
+    return {"seconds": time.perf_counter() - t0, "first_pass_with_weight_generation_s": first}
+
+
 def run_reference_arm(args):
     rank, world, _ = dist_env()
     if rank != 0:
         return 0
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=_host_threads())
+    except Exception:
+        pass
+    t0 = time.perf_counter()
     cpu = CpuSample()
+    construct_s = time.perf_counter() - t0
     sample, threads = cpu.sample, cpu.threads
     times = []
     for i in range(args.warmup + args.steps):
@@ -200,6 +292,7 @@ def run_reference_arm(args):
             times.append(seconds)
     per_forward = float(np.mean(times))
     value = 1.0 / per_forward
+    sampled_seconds = float(np.sum(times))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_forward * 1e3,
@@ -210,9 +303,15 @@ def run_reference_arm(args):
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        # the figure is an estimate: a few layers and one flow step are timed and scaled
+        "extrapolated": True, "sampled": cpu.sampled, "timed_seconds_per_step": sampled_seconds / len(times),
         "note": "PI0.5 has no CPU implementation in the reference and its Rust host cannot be "
-                "built in this image; this arm times the CPU oracle port of its arithmetic",
+                "built in this image; this arm times the CPU oracle port of its arithmetic. "
+                "ms_per_step is the scaled estimate of one complete forward, not a run of one",
     }
+    if world == 1 and not args.no_complete_forward:
+        # weight generation of the sample covered ~2/27 + 3/18 + 3/18 of the tensors
+        line["complete_forward"] = complete_cpu_forward(args.complete_forward_budget, construct_s * 6.0)
     print(json.dumps(line), flush=True)
     return 0
 
@@ -260,7 +359,10 @@ def run_ours(args):
     cfg_tp = Pi05Config(num_views=2, action_horizon=50)
     rt = Pi05Runtime.random(cfg_tp, dtype="fp8", seed=0, device=local, fp8_act_scale=0.05)
     graph = rt.capture_infer_rgb_u8(token_count, "nhwc", args.batch)
-    images, tokens, noise = synthetic_batch(cfg_tp, args.batch, token_count, 1000 + rank * args.batch)
+    # this rank's contiguous shard of the global batch (observation i has seed 1000 + i)
+    from apxinf_b200.parallel import shard_bounds
+    shard = shard_bounds(args.batch * world, world)[rank]
+    images, tokens, noise = synthetic_batch(cfg_tp, shard.size, token_count, 1000 + shard.start)
     from apxinf_b200.engine import float_to_bf16_bits
     h_images = pinned_like(images, torch)
     h_tokens = pinned_like(tokens.astype(np.uint32).view(np.int32), torch)
@@ -319,17 +421,38 @@ def run_ours(args):
             "frac": achieved / peak,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the single-pass ncu
             # capture of this workload summarised under profiles/ (batch 64 only)
-            "traffic": GATE_UP_DRAM_BYTES_BATCH64 if args.batch == 64 else None,
+            "traffic": (GATE_UP_DRAM_BYTES_BATCH64
+                        if args.batch == 64 and kernel_source_blob() == GATE_UP_PROFILED_KERNEL_BLOB else None),
+            "traffic_profiled_kernel_blob": GATE_UP_PROFILED_KERNEL_BLOB,
+            "kernel_blob_now": kernel_source_blob(),
             "launch_ms": avg_ms, "launches_timed": count,
             "flops_per_launch": flops,
             "peak_source": (f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); "
                             "no FP8 peak is measured on this pool, FP8 dense = 2 x BF16 nominally"),
         }
+        # ---- whole step against the same tensor peak ----
+        work = algorithmic_work(cfg_tp, token_count, args.batch, 1)
+        step_ms = device_seconds / args.steps * 1e3
+        step_achieved = work["flops_per_step"] / (step_ms * 1e-3) / 1e12
+        roofline_step = {"bound": "tensor", "flops_per_step": work["flops_per_step"],
+                         "achieved": step_achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": step_achieved / peak, "peak_source": roofline["peak_source"]}
         # ---- B=1 latency, the other half of the headline ----
-        latency = measure_latency(rt_dtype="fp8", device=local)
+        latency = measure_latency(rt_dtype="fp8", device=local, per_op=True)
+        b1 = algorithmic_work(Pi05Config(), token_count, 1, 1)
+        latency["hbm_bytes"] = b1["b1_hbm_bytes"]
+        latency["hbm_gbs"] = b1["b1_hbm_bytes"] / (latency["p50_ms"] * 1e-3) / 1e9
+        latency["hbm_frac"] = latency["hbm_gbs"] / peaks["hbm_gbs"]
+        latency["hbm_peak_gbs"] = peaks["hbm_gbs"]
         # the other two precisions of the path, same protocol (p50 only)
+        bf16_latency = measure_latency(rt_dtype="bf16", device=local, per_op=True)
         latency["other_precisions_p50_ms"] = {
-            dtype: measure_latency(rt_dtype=dtype, device=local)["p50_ms"] for dtype in ("bf16", "int8")}
+            "bf16": bf16_latency["p50_ms"], "int8": measure_latency(rt_dtype="int8", device=local)["p50_ms"]}
+        ref_cuda = None
+        if not args.no_ref_cuda and world == 1:
+            ref_cuda = reference_cuda_leg(latency.pop("op_us", {}), bf16_latency.pop("op_us", {}),
+                                          bf16_latency["stage_ms_eager"])
+        latency.pop("op_us", None)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": device_seconds / args.steps * 1e3,
@@ -338,7 +461,8 @@ def run_ours(args):
             "e2e": {"value": chunks / e2e_seconds, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": (graph.num_launches() - 1) * args.steps,
-            "roofline": roofline, "latency_b1": latency, "outputs_finite": finite,
+            "roofline": roofline, "roofline_step": roofline_step, "latency_b1": latency,
+            "ref_cuda": ref_cuda, "outputs_finite": finite,
         }
     graph.close()
     rt.close()
@@ -347,7 +471,8 @@ def run_ours(args):
             cpu = CpuSample()
             seconds = min(cpu.seconds() for _ in range(2))
             line["cpu_baseline"] = {"value": 1.0 / seconds, "unit": UNIT, "cores": cpu.threads,
-                                    "kind": "port", "sample": cpu.sample}
+                                    "kind": "port", "sample": cpu.sample, "extrapolated": True,
+                                    "sampled": cpu.sampled}
             line["cpu_block_cfg1"] = cpu_block_cfg1()
         else:
             line["cpu_baseline"] = None
@@ -358,7 +483,136 @@ def run_ours(args):
     return 0
 
 
-def measure_latency(rt_dtype, device):
+MODEL_GEMMS = {  # (M, N, K) of every GEMM of the replayed B=1 graph (2 views, 10 tokens, H=10)
+    "vision.patch_embed": (512, 1152, 588), "vision.qkv": (512, 3456, 1152), "vision.o": (512, 1152, 1152),
+    "vision.fc1": (512, 4304, 1152), "vision.fc2": (512, 1152, 4304), "vision.projector": (512, 2048, 1152),
+    "language.qkv": (522, 2560, 2048), "language.o": (522, 2048, 2048),
+    "language.gate_up": (522, 32768, 2048), "language.down": (522, 2048, 16384),
+    "action.in": (10, 1024, 32), "action.qkv": (10, 2560, 1024), "action.o": (10, 1024, 2048),
+    "action.gate_up": (10, 8192, 1024), "action.down": (10, 1024, 4096), "action.out": (10, 32, 1024),
+}
+MODEL_ATTENTION = {  # (query tokens, keys, heads, head_dim); SigLIP is per view
+    "language.attn": (522, 522, 8, 256), "action.attn": (10, 532, 8, 256),
+}
+
+
+def reference_cuda_leg(ours_fp8_us, ours_bf16_us, ours_bf16_stage_ms):
+    """The reference's own CUDA build on this GPU, beside ours (outside every timed region of
+    the headline numbers): its B=1 BF16 forward replayed eagerly op by op over its compiled
+    adapters (stage times), and single-op times of its cuBLASLt FP8 / BF16 linear layers and
+    its three-launch cuBLAS MQA at the model's shapes. Ours: the same ops inside the B=1
+    graphs' launch lists, each timed with a CUDA-event pair in one eager pass (ours carry
+    their fused epilogues: bias, GELU, residual, GeGLU, quantisation). Needs oracle/_ref."""
+    try:
+        from oracle import ref_forward as R
+        from oracle import pi05_oracle as O
+        if not R.available():
+            return {"unavailable": "oracle/_ref not built (make -C oracle with the reference tree present)"}
+        cfg = O.Pi05Config()
+        ref = R.RefBf16Forward(cfg, 0)
+        inputs = O.synthetic_observation(cfg, 1234, 10)
+        ref.infer(*inputs)  # warm-up: weight generation, cuBLAS heuristics
+        runs = [ref.infer(*inputs, timed=True)[1] for _ in range(3)]
+        ref.close()
+        del ref
+        import torch
+        torch.cuda.empty_cache()
+        stage = {k: float(np.median([r[k] for r in runs])) for k in ("vision", "prefix", "denoise")}
+        gemms = R.time_gemms(MODEL_GEMMS)
+        mqa = R.time_mqa(MODEL_ATTENTION)
+        ours = ours_standalone_us(R.graph_time_us, R.weight_copies)
+        table = {}
+        for name, shape in MODEL_GEMMS.items():
+            table[name] = {"mnk": list(shape), "ref_cublaslt_fp8_us": gemms[name].get("fp8_us"),
+                           "ref_cublaslt_bf16_us": gemms[name].get("bf16_us"),
+                           "ours_fp8_us": ours[name]["fp8_us"], "ours_bf16_us": ours[name]["bf16_us"],
+                           "ours_fp8_in_graph_us": ours_fp8_us.get(name),
+                           "ours_bf16_in_graph_us": ours_bf16_us.get(name)}
+        for name, shape in MODEL_ATTENTION.items():
+            table[name] = {"q_keys_heads_hd": list(shape), "ref_cublas_mqa_bf16_us": mqa[name]["us"],
+                           "ours_bf16_us": ours[name]["bf16_us"],
+                           "ours_fp8_in_graph_us": ours_fp8_us.get(name),
+                           "ours_bf16_in_graph_us": ours_bf16_us.get(name)}
+        return {"what": "reference CUDA kernels + cuBLAS(Lt) compiled for sm_100a from the reference tree, B=1",
+                "bf16_b1_eager_stage_ms": {**stage, "total": sum(stage.values()), "launches": runs[0]["launches"]},
+                "ours_bf16_b1_eager_stage_ms": ours_bf16_stage_ms,
+                "per_op_us": table,
+                "per_op_method": "ref_* and ours_*_us: 20 launches of the bare op captured into one CUDA graph, "
+                                 "weights rotating through > L2 of copies, best of 5 replays / 20; "
+                                 "ours_*_in_graph_us: the op inside the model's launch list with its fused "
+                                 "epilogue, one CUDA-event pair per launch in an eager pass",
+                "left_out": "CUTLASS sm100 FP8 GEMM / dual GeGLU / FMHA translation units: closed on this pool "
+                            "(their tactics launch TMA multicast clusters)"}
+    except Exception as error:  # the checker is optional equipment of the bench
+        return {"unavailable": f"{type(error).__name__}: {error}"}
+
+
+def ours_standalone_us(graph_time_us, weight_copies):
+    """This library's kernels on the same bare problems and through the same timing harness as
+    the reference's library calls: pi05_gemm (store epilogue, e4m3 -> bf16 and bf16 -> bf16)
+    and pi05_attention (multi-query heads packed, key-split for the 10-token shape)."""
+    import ctypes as C
+    import torch
+    from apxinf_b200 import _lib as L, kernels as K, lib
+    results = {}
+    partials = torch.zeros(32 << 20, dtype=torch.uint8, device="cuda")
+    counters = torch.zeros(4096, dtype=torch.int32, device="cuda")
+    status = K.new_status()
+    for name, (m, n, k) in MODEL_GEMMS.items():
+        entry = {}
+        k_pad = (k + 15) // 16 * 16
+        for label, dtype, op, elem in (("fp8", torch.float8_e4m3fn, L.OP_E4M3, 1), ("bf16", torch.bfloat16, L.OP_BF16, 2)):
+            copies = weight_copies(n * k * elem)
+            a = torch.zeros(m, k_pad, device="cuda").to(dtype)
+            a[:, :k] = torch.randn(m, k, device="cuda").to(dtype)
+            ws = []
+            for _ in range(copies):
+                w = torch.zeros(n, k_pad, device="cuda").to(dtype)
+                w[:, :k] = torch.randn(n, k, device="cuda").to(dtype)
+                ws.append(w)
+            out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+
+            def launch(i, a=a, ws=ws, out=out, op=op):
+                K.gemm(a, ws[i % len(ws)], out, op=op, alpha=0.01, partials=partials, tile_counters=counters,
+                       status=status)
+            entry[label + "_us"] = graph_time_us(launch)
+            del a, ws, out
+        results[name] = entry
+    handle = lib()
+
+    class AttentionArgs(C.Structure):
+        _fields_ = [("q", C.c_void_p), ("q_ld", C.c_int64), ("q_sb0", C.c_int64), ("q_sb1", C.c_int64),
+                    ("k", C.c_void_p), ("k_ld", C.c_int64), ("k_sb0", C.c_int64), ("k_sb1", C.c_int64),
+                    ("v", C.c_void_p), ("v_ld", C.c_int64), ("v_sb0", C.c_int64), ("v_sb1", C.c_int64),
+                    ("out", C.c_void_p), ("out_ld", C.c_int64), ("out_sb0", C.c_int64), ("out_sb1", C.c_int64),
+                    ("q_rows", C.c_int32), ("keys", C.c_int32), ("head_dim", C.c_int32),
+                    ("nb0", C.c_int32), ("nb1", C.c_int32), ("scale", C.c_float),
+                    ("out_e4m3", C.c_int32), ("out_inv_scale", C.c_float), ("status", C.c_void_p),
+                    ("key_split", C.c_int32), ("split_scratch", C.c_void_p), ("split_scratch_bytes", C.c_int64)]
+    handle.pi05_attention.argtypes = [C.POINTER(AttentionArgs), C.c_void_p]
+    handle.pi05_attention.restype = C.c_int
+    for name, (qt, kt, heads, hd) in MODEL_ATTENTION.items():
+        q = torch.randn(qt, heads * hd, device="cuda").to(torch.bfloat16)
+        kk = torch.randn(kt, hd, device="cuda").to(torch.bfloat16)
+        vv = torch.randn(kt, hd, device="cuda").to(torch.bfloat16)
+        out = torch.empty(qt, heads * hd, dtype=torch.bfloat16, device="cuda")
+        args = AttentionArgs(q=q.data_ptr(), q_ld=heads * hd, q_sb0=hd, q_sb1=0, k=kk.data_ptr(), k_ld=hd,
+                             v=vv.data_ptr(), v_ld=hd, out=out.data_ptr(), out_ld=heads * hd, out_sb0=hd,
+                             q_rows=qt, keys=kt, head_dim=hd, nb0=heads, nb1=1, scale=1.0 / 16.0,
+                             out_inv_scale=1.0, status=status.data_ptr(), key_split=int(qt * heads <= 128 * 31),
+                             split_scratch=partials.data_ptr(), split_scratch_bytes=partials.numel())
+        if qt * heads > 1024:
+            args.key_split = 0
+
+        def launch(i):
+            rc = handle.pi05_attention(C.byref(args), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+            if rc != 0:
+                raise RuntimeError(f"pi05_attention status {rc}")
+        results[name] = {"bf16_us": graph_time_us(launch)}
+    return results
+
+
+def measure_latency(rt_dtype, device, per_op=False):
     """B=1 two-view graph-replay latency (pi05_bench protocol: 10 warm-ups, 30 replays)."""
     from apxinf_b200.engine import Pi05Config, Pi05Runtime
     from apxinf_b200.fixtures import synthetic_observation
@@ -375,11 +629,19 @@ def measure_latency(rt_dtype, device):
     out = graph.infer_host(images[None], tokens[None], noise[None])
     update_plus_graph = (time.perf_counter() - t0) * 1e3
     stages = graph.stage_times()
+    op_us = {}
+    if per_op:
+        for name in list(MODEL_GEMMS) + ["vision.attn"] + list(MODEL_ATTENTION):
+            mean_ms, count = graph.time_launches(name)
+            if count > 0:
+                op_us[name] = mean_ms * 1e3
     result = {"workload": f"cfg{dict(bf16=2, fp8=3, int8=3)[rt_dtype]}: {rt_dtype.upper()}, B=1, 2 views, 10 tokens, H=10, 10 flow steps",
               "p50_ms": float(ms[len(ms) // 2]), "p95_ms": float(ms[int(round(0.95 * (len(ms) - 1)))]),
               "min_ms": float(ms[0]), "max_ms": float(ms[-1]),
               "input_update_plus_graph_ms": update_plus_graph, "launches": graph.num_launches(),
               "stage_ms_eager": stages, "finite": bool(np.isfinite(out).all())}
+    if per_op:
+        result["op_us"] = op_us
     graph.close()
     rt.close()
     return result
@@ -393,6 +655,12 @@ def main():
     parser.add_argument("--batch", type=int, default=64, help="observations per GPU per step")
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-ref-cuda", action="store_true",
+                        help="skip the reference-CUDA comparison leg (needs oracle/_ref)")
+    parser.add_argument("--no-complete-forward", action="store_true",
+                        help="reference arm: skip the one complete CPU forward")
+    parser.add_argument("--complete-forward-budget", type=float, default=150.0,
+                        help="reference arm: seconds of weight generation allowed for the complete forward")
     args = parser.parse_args()
     _, world, _ = dist_env()
     if args.impl == "ours" and world != args.gpus:
