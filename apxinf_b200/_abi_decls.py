@@ -36,6 +36,7 @@ PROTOTYPES = [
      [C.POINTER(ModelConfig), C.POINTER(EngineOptions), C.POINTER(_P)]),
     ("pi05_engine_set_activation_scale", C.c_int, [_P, C.c_char_p, C.c_float]),
     ("pi05_engine_activation_scale", C.c_float, [_P, C.c_char_p]),
+    ("pi05_set_tuning", C.c_int, [C.c_char_p, C.c_int32]),
     ("pi05_engine_destroy", None, [_P]),
     ("pi05_engine_weight_bytes", _SZ, [_P]),
     ("pi05_engine_read_weight", C.c_int, [_P, C.c_char_p, _P, _SZ, C.POINTER(_SZ)]),

@@ -14,7 +14,9 @@ LIB_PATH = _PKG / "libpi05_b200.so"
 OP_BF16, OP_E4M3, OP_S8 = 0, 1, 2
 OUT_BF16, OUT_E4M3, OUT_F32, OUT_S32 = 0, 1, 2, 3
 (EPI_STORE, EPI_BIAS_GELU, EPI_BIAS_SILU, EPI_BIAS_RESIDUAL, EPI_BIAS_POS,
- EPI_GATE_RESIDUAL, EPI_GEGLU) = range(7)
+ EPI_GATE_RESIDUAL, EPI_GEGLU, EPI_ROPE, EPI_EULER) = range(9)
+PRO_NONE, PRO_ADA_NORM, PRO_QUANTIZE, PRO_RMS_NORM = range(4)
+OUT_S8 = 4
 
 STATUS_NAMES = {
     0: "PI05_OK",
@@ -54,6 +56,12 @@ class GemmArgs(C.Structure):
         ("partials", C.c_void_p), ("partials_bytes", C.c_uint64),
         ("tile_counters", C.c_void_p), ("max_tiles", C.c_int32), ("force_split_k", C.c_int32),
         ("b_blocked", C.c_int32),
+        ("force_skinny", C.c_int32), ("prologue", C.c_int32), ("style", C.c_void_p),
+        ("eps", C.c_float), ("a_inv_scale", C.c_float), ("a_dynamic_rows", C.c_int32),
+        ("rope_q_out", C.c_void_p), ("rope_k_cache", C.c_void_p), ("rope_v_cache", C.c_void_p),
+        ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
+        ("rope_tokens", C.c_int32), ("rope_q_heads", C.c_int32), ("rope_head_dim", C.c_int32),
+        ("rope_position_offset", C.c_int32), ("rope_cache_rows", C.c_int32), ("dt", C.c_float),
     ]
 
 

@@ -2,6 +2,8 @@
 #include <new>
 
 #include "../../include/pi05_b200.h"
+#include <string>
+
 #include "engine.h"
 
 struct Pi05Engine {
@@ -113,6 +115,21 @@ extern "C" int pi05_engine_create(const Pi05ModelConfig* config, int32_t dtype, 
   options.weight_dist = PI05_WEIGHTS_LCG;
   options.int8_activations = PI05_INT8_ACT_DYNAMIC;
   return pi05_engine_create_ex(config, &options, out);
+}
+
+extern "C" int pi05_set_tuning(const char* name, int32_t value) {
+  if (name == nullptr) return pi05::kPi05ErrInvalidValue;
+  const std::string key(name);
+  if (key == "programmatic_dependent_launch") {
+    pi05::set_pdl_enabled(value != 0);
+  } else if (key == "fuse_small_rows") {
+    pi05::set_fuse_small_rows_enabled(value != 0);
+  } else if (key == "attention_cluster") {
+    pi05::set_fmha_rows_cluster_enabled(value != 0);
+  } else {
+    return pi05::kPi05ErrInvalidValue;
+  }
+  return pi05::kPi05Ok;
 }
 
 extern "C" int pi05_engine_set_activation_scale(Pi05Engine* engine, const char* site, float scale) {

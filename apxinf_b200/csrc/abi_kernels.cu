@@ -60,6 +60,23 @@ extern "C" int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream) {
   q.max_tiles = args->max_tiles;
   q.force_split_k = args->force_split_k;
   q.b_blocked = args->b_blocked != 0;
+  q.force_skinny = args->force_skinny;
+  q.prologue = args->prologue;
+  q.style = args->style;
+  q.eps = args->eps;
+  q.a_inv_scale = args->a_inv_scale;
+  q.a_dynamic_rows = args->a_dynamic_rows != 0;
+  q.rope_q_out = args->rope_q_out;
+  q.rope_k_cache = args->rope_k_cache;
+  q.rope_v_cache = args->rope_v_cache;
+  q.rope_cos = args->rope_cos;
+  q.rope_sin = args->rope_sin;
+  q.rope_tokens = args->rope_tokens;
+  q.rope_q_heads = args->rope_q_heads;
+  q.rope_head_dim = args->rope_head_dim;
+  q.rope_position_offset = args->rope_position_offset;
+  q.rope_cache_rows = args->rope_cache_rows;
+  q.dt = args->dt;
   GemmPlan plan;
   const int rc = gemm_plan_build(q, &plan);
   if (rc != kPi05Ok) return rc;

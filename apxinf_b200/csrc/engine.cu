@@ -783,7 +783,103 @@ int PreparedGraph::build(bool measuring) {
     add_kernel("load_noise", [=](cudaStream_t s) { return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, s); });
   }
   const float dt = -1.0f / static_cast<float>(S_);
+  // At most 16 action rows (B=1, H <= 16): every projection runs on the register-streaming
+  // kernel, and the row kernels between them run inside it: quantiser / adaRMSNorm as its
+  // activation staging, RoPE + cache write and the Euler update as its epilogue. Six launches
+  // per layer and step (qkv, attention x2, o, gate_up, down) instead of nine.
+  const bool fuse_rows = fuse_small_rows_enabled() && Ra <= 16 && ac.width <= 1024 && ac.width % 8 == 0 && c.action_dim % 8 == 0;
+  // GEMM of <= 16 rows whose bf16 input `src` [Ra, k] is normalised / quantised while staged
+  auto fused_problem = [&](const Linear& w, const void* src, int k, int prologue, const void* style,
+                           const std::string& site) {
+    GemmProblem q;
+    const float scale = e_->scale_of(site);
+    q.op = op_of(prec);
+    q.M = Ra;
+    q.N = w.n;
+    q.K = k;
+    q.a = GemmOperand{src, Ra, k, 0, 0};
+    q.b = GemmOperand{w.w, w.n, w.ldk, 0, 0};
+    q.bias = w.bias;
+    q.col_scale = w.col_scale;
+    q.alpha = e_->static_scales() ? scale : 1.0f;
+    q.status = e_->status();
+    q.b_static = true;
+    q.force_skinny = 1;
+    q.prologue = prec == kPrecBf16 && prologue == kProQuantize ? kProNone : prologue;
+    q.style = style;
+    q.eps = c.rms_norm_eps;
+    q.a_inv_scale = 1.0f / scale;
+    q.a_dynamic_rows = prec == kPrecInt8 && !e_->static_int8();
+    return q;
+  };
   for (int step = 0; step < S_; ++step) {
+    if (fuse_rows) {
+      {
+        GemmProblem q = fused_problem(e_->action_in, d_state_, c.action_dim, kProQuantize, nullptr, "action.input");
+        q.out = ha;
+        q.ldc = ac.width;
+        PI05_TRY(add_gemm("action.in", q));
+      }
+      for (int l = 0; l < ac.depth; ++l) {
+        const Engine::ActionLayer& w = e_->action[l];
+        const uint16_t* attn_style = static_cast<const uint16_t*>(style_ptr(2 * l, step));
+        const uint16_t* mlp_style = static_cast<const uint16_t*>(style_ptr(2 * l + 1, step));
+        {
+          GemmProblem q = fused_problem(w.qkv, ha, ac.width, kProAdaNorm, attn_style, asite(l, "attention_norm"));
+          q.out = qkv_a;  // unused by the RoPE epilogue, kept as a valid pointer
+          q.ldc = qw + 2 * hd;
+          q.mode = kEpiRope;
+          q.rope_q_out = qbuf_a;
+          q.rope_k_cache = k_cache[l];
+          q.rope_v_cache = v_cache[l];
+          q.rope_cos = e_->rope_cos;
+          q.rope_sin = e_->rope_sin;
+          q.rope_tokens = H_;
+          q.rope_q_heads = qh;
+          q.rope_head_dim = hd;
+          q.rope_position_offset = P_;
+          q.rope_cache_rows = cache_rows;
+          PI05_TRY(add_gemm("action.qkv", q));
+        }
+        attn_a.scale = e_->scale_of(asite(l, "attention_output"));
+        PI05_TRY(attention("action.attn", qbuf_a, hd, (long long)H_ * qw, 0, k_cache[l], hd, (long long)cache_rows * hd, 0,
+                           v_cache[l], hd, (long long)cache_rows * hd, 0, H_ * qh, cache_rows, hd, B_, 1, scale_g,
+                           logits_a, &attn_a, hd, (long long)H_ * qw, 0));
+        PI05_TRY(linear("action.o", attn_a, Ra, w.o, kEpiGateResidual, ha, ac.width, kOutBf16, ha, attn_style + 2 * ac.width, nullptr, 1, 1.0f));
+        {
+          GemmProblem q = fused_problem(w.gate_up, ha, ac.width, kProAdaNorm, mlp_style, asite(l, "mlp_norm"));
+          act_a.scale = e_->scale_of(asite(l, "mlp_activation"));
+          const bool dynamic_int8 = prec == kPrecInt8 && !e_->static_int8();
+          q.out = dynamic_int8 ? act_a.wide : act_a.data;
+          q.ldc = act_a.ld;
+          q.mode = kEpiGeglu;
+          q.out_type = prec == kPrecBf16 || dynamic_int8 ? kOutBf16 : prec == kPrecFp8 ? kOutE4m3 : kOutS8;
+          q.out_inv_scale = 1.0f / act_a.scale;
+          PI05_TRY(add_gemm("action.gate_up", q));
+          if (dynamic_int8) {
+            const void* wide = act_a.wide;
+            int8_t* data = static_cast<int8_t*>(act_a.data);
+            float* rs = act_a.row_scale;
+            const int cols = static_cast<int>(act_a.ld);
+            add_kernel("quantize_rows_int8", [=](cudaStream_t s) {
+              return launch_quantize_rows_int8(wide, data, rs, Ra, cols, cols, cols, s);
+            });
+          }
+        }
+        PI05_TRY(linear("action.down", act_a, Ra, w.down, kEpiGateResidual, ha, ac.width, kOutBf16, ha, mlp_style + 2 * ac.width, nullptr, 1, 1.0f));
+      }
+      {
+        // final adaRMSNorm -> velocity head -> Euler update of the state, one launch
+        GemmProblem q = fused_problem(e_->action_out, ha, ac.width, kProAdaNorm, style_ptr(2 * ac.depth, step), "action.final_norm");
+        q.out = d_state_;
+        q.ldc = c.action_dim;
+        q.mode = kEpiEuler;
+        q.residual = d_state_;
+        q.dt = dt;
+        PI05_TRY(add_gemm("action.out", q));
+      }
+      continue;
+    }
     quantize_to_act("quantize_state", d_state_, Ra, c.action_dim, &state_act, "action.input");
     PI05_TRY(linear("action.in", state_act, Ra, e_->action_in, kEpiStore, ha, ac.width, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f));
     PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, style_ptr(0, step), c.rms_norm_eps, &na, asite(0, "attention_norm")));

@@ -1,11 +1,90 @@
 #include "fmha.h"
 
 #include <algorithm>
+#include <cstring>
 
+#include "fmha_rows.cuh"
 #include "fmha_split.cuh"
 #include "fmha_online.cuh"
 
 namespace pi05 {
+
+static_assert(sizeof(FmhaRowsParams) <= 160, "FmhaPlan::rows_params is too small");
+
+namespace {
+bool g_rows_cluster = true;
+}
+bool fmha_rows_cluster_enabled() { return g_rows_cluster; }
+void set_fmha_rows_cluster_enabled(bool enabled) { g_rows_cluster = enabled; }
+
+namespace {
+
+// Few query rows over one shared K/V head per sample: fill the cluster kernel's parameters.
+// Two operand forms reach it: heads as nb0 sharing one K/V head (k_sb0 = v_sb0 = 0, samples
+// as nb1), or heads already folded into the rows with one K/V per nb0 entry (nb1 = 1).
+bool rows_cluster_fits(const FmhaProblem& q, FmhaRowsParams* r, int* smem) {
+  if (!fmha_rows_cluster_enabled() || q.head_dim % 16 != 0 || q.head_dim > 256) return false;
+  const bool shared = q.nb0 > 1 && q.k_sb0 == 0 && q.v_sb0 == 0;
+  int heads, samples;
+  long long q_sample, k_sample, v_sample, o_sample;
+  if (shared) {
+    heads = q.nb0;
+    samples = q.nb1;
+    q_sample = q.q_sb1; k_sample = q.k_sb1; v_sample = q.v_sb1; o_sample = q.out_sb1;
+  } else if (q.nb1 == 1) {
+    heads = 1;
+    samples = q.nb0;
+    q_sample = q.q_sb0; k_sample = q.k_sb0; v_sample = q.v_sb0; o_sample = q.out_sb0;
+  } else {
+    return false;
+  }
+  const int rows = q.q_rows * heads;
+  const int tiles = (rows + 15) / 16;
+  if (static_cast<long long>(tiles) * samples > 64) return false;  // beyond that the persistent kernel wins
+  const int slice = ((q.keys + kRowsCluster - 1) / kRowsCluster + 15) / 16 * 16;
+  if (slice > 256) return false;
+  auto aligned16 = [](const void* ptr, long long stride_elems) {
+    return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && (stride_elems * 2) % 16 == 0;
+  };
+  if (!aligned16(q.q, q.q_ld) || !aligned16(q.k, q.k_ld) || !aligned16(q.v, q.v_ld) ||
+      (q.q_sb0 * 2) % 16 != 0 || (q_sample * 2) % 16 != 0 || (k_sample * 2) % 16 != 0 ||
+      (v_sample * 2) % 16 != 0) {
+    return false;
+  }
+  // outputs are written as pairs of elements
+  const int out_elem = q.out_e4m3 ? 1 : 2;
+  if ((reinterpret_cast<uintptr_t>(q.out) % (2 * out_elem)) != 0 || q.out_ld % 2 != 0 || q.out_sb0 % 2 != 0 ||
+      o_sample % 2 != 0) {
+    return false;
+  }
+  r->q = static_cast<const __nv_bfloat16*>(q.q);
+  r->q_ld = q.q_ld;
+  r->q_sb0 = shared ? q.q_sb0 : 0;
+  r->q_sb1 = q_sample;
+  r->k = static_cast<const __nv_bfloat16*>(q.k);
+  r->k_ld = q.k_ld;
+  r->k_sb1 = k_sample;
+  r->v = static_cast<const __nv_bfloat16*>(q.v);
+  r->v_ld = q.v_ld;
+  r->v_sb1 = v_sample;
+  r->out = q.out;
+  r->out_ld = q.out_ld;
+  r->out_sb0 = shared ? q.out_sb0 : 0;
+  r->out_sb1 = o_sample;
+  r->rows = rows;
+  r->heads = heads;
+  r->keys = q.keys;
+  r->head_dim = q.head_dim;
+  r->slice_keys = slice;
+  r->tiles = tiles;
+  r->scale = q.scale;
+  r->out_e4m3 = q.out_e4m3 ? 1 : 0;
+  r->out_inv_scale = q.out_inv_scale;
+  *smem = fmha_rows_smem_bytes(q.head_dim, slice);
+  return *smem <= 227 * 1024;
+}
+
+}  // namespace
 
 bool fmha_supported(int q_rows, int keys, int head_dim) {
   return q_rows > 0 && keys > 0 && keys <= 1024 && head_dim >= 16 && head_dim <= 256 &&
@@ -80,6 +159,17 @@ int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
       return kPi05ErrScratchLimit;
     }
     plan->split_scratch = q.split_scratch;
+    FmhaRowsParams rows{};
+    int rows_smem = 0;
+    plan->rows_cluster = rows_cluster_fits(q, &rows, &rows_smem);
+    if (plan->rows_cluster) {
+      std::memcpy(plan->rows_params, &rows, sizeof(rows));
+      plan->rows_smem = rows_smem;
+      const int samples = rows.heads == q.nb0 && q.nb0 > 1 && q.k_sb0 == 0 && q.v_sb0 == 0 ? q.nb1 : q.nb0;
+      plan->grid = dim3(static_cast<unsigned>(rows.tiles * samples * kRowsCluster), 1, 1);
+      cudaFuncSetAttribute(fmha_rows_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      return kPi05Ok;
+    }
     plan->grid = dim3(static_cast<unsigned>(items * splits), 1, 1);
     plan->combine_grid = dim3(static_cast<unsigned>(items * (128 / kCombineRows)), 1, 1);
     cudaFuncSetAttribute(fmha_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSplitSmemBytes);
@@ -91,6 +181,25 @@ int fmha_plan_build(const FmhaProblem& q, FmhaPlan* plan) {
 }
 
 cudaError_t fmha_plan_launch(const FmhaPlan& plan, cudaStream_t stream) {
+  if (plan.key_split && plan.rows_cluster) {
+    FmhaRowsParams rows;
+    std::memcpy(&rows, plan.rows_params, sizeof(rows));
+    cudaLaunchConfig_t config = {};
+    config.gridDim = plan.grid;
+    config.blockDim = dim3(kRowsThreads);
+    config.dynamicSmemBytes = plan.rows_smem;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = kRowsCluster;
+    attributes[0].val.clusterDim.y = 1;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes;
+    config.numAttrs = pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&config, fmha_rows_cluster_kernel, rows);
+  }
   if (plan.key_split) {
     cudaError_t err = launch_pdl(fmha_split_kernel, plan.grid, dim3(kSplitThreads), kSplitSmemBytes, stream,
                                  plan.tmap_q, plan.tmap_k, plan.tmap_v, plan.params, plan.split_scratch);

@@ -50,6 +50,9 @@ struct FmhaProblem {
   size_t split_scratch_bytes = 0;
 };
 
+// Parameters of the cluster kernel for a handful of query rows (fmha_rows.cuh).
+struct FmhaRowsParams;
+
 struct FmhaPlan {
   CUtensorMap tmap_q, tmap_k, tmap_v;
   FmhaParams params;
@@ -57,7 +60,16 @@ struct FmhaPlan {
   bool key_split = false;
   float* split_scratch = nullptr;
   dim3 combine_grid;
+  // few query rows: one cluster of 8 CTAs per 16-row tile, no scratch (fmha_rows.cuh)
+  bool rows_cluster = false;
+  alignas(8) unsigned char rows_params[160];
+  int rows_smem = 0;
 };
+
+// Process-wide switch (default on): launches with few query rows use the cluster kernel
+// instead of the key-split kernel pair.
+bool fmha_rows_cluster_enabled();
+void set_fmha_rows_cluster_enabled(bool enabled);
 
 bool fmha_supported(int q_rows, int keys, int head_dim);
 // Query tiles (CTAs of the unsplit kernel) and scratch bytes of the key-split path.

@@ -11,9 +11,12 @@ namespace pi05 {
 
 namespace {
 bool g_pdl_enabled = true;
+bool g_fuse_small_rows = true;
 }
 bool pdl_enabled() { return g_pdl_enabled; }
 void set_pdl_enabled(bool enabled) { g_pdl_enabled = enabled; }
+bool fuse_small_rows_enabled() { return g_fuse_small_rows; }
+void set_fuse_small_rows_enabled(bool enabled) { g_fuse_small_rows = enabled; }
 
 namespace {
 
@@ -132,10 +135,140 @@ const void* select_kernel(int block_n, bool swap, bool b_mn, bool multi_wave, in
 
 }  // namespace
 
+namespace {
+
+template <int OP, int NTW>
+const void* skinny_ptr(int /*smem*/) {
+  auto kernel = &gemm_skinny_kernel<OP, NTW>;
+  // plans of different K share the kernel: allow the largest tile any of them may ask for
+  cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  return reinterpret_cast<const void*>(kernel);
+}
+
+bool needs_skinny(const GemmProblem& q) {
+  return q.prologue != kProNone || q.mode == kEpiRope || q.mode == kEpiEuler;
+}
+
+// Can the at-most-16-row kernel take this problem? (Everything it cannot take still has the
+// tcgen05 path, except the fused prologues and the RoPE / Euler epilogues.)
+bool skinny_fits(const GemmProblem& q) {
+  const int es = elem_bytes(q.op);
+  const bool aligned = (reinterpret_cast<uintptr_t>(q.a.ptr) & 15u) == 0 &&
+                       (reinterpret_cast<uintptr_t>(q.b.ptr) & 15u) == 0 &&
+                       (q.b.ld * es) % 16 == 0 && ((long long)q.K * es) % 16 == 0 &&
+                       (q.a.ld * (q.prologue != kProNone ? 2 : es)) % 16 == 0;
+  if (q.M > 16 || q.b_mn_major || q.b_blocked || q.nb0 * q.nb1 != 1 || q.mode == kEpiBiasPos || !aligned) {
+    return false;
+  }
+  if (q.prologue != kProNone && (q.K % 8 != 0 || q.K > 8 * 32 * 4)) return false;
+  if (q.mode == kEpiGeglu && q.N % 128 != 0) return false;
+  if (q.mode == kEpiRope &&
+      (q.rope_head_dim <= 0 || q.rope_head_dim % 16 != 0 || q.N != (q.rope_q_heads + 2) * q.rope_head_dim ||
+       q.rope_q_out == nullptr || q.rope_k_cache == nullptr || q.rope_v_cache == nullptr ||
+       q.rope_cos == nullptr || q.rope_sin == nullptr || q.rope_tokens <= 0 || q.M % q.rope_tokens != 0)) {
+    return false;
+  }
+  if (q.prologue == kProAdaNorm && q.style == nullptr) return false;
+  return true;
+}
+
+int skinny_plan_build(const GemmProblem& q, GemmPlan* plan) {
+  const int es = elem_bytes(q.op);
+  SkinnyParams& p = plan->skinny_params;
+  p = SkinnyParams{};
+  p.a = q.a.ptr;
+  p.lda = q.a.ld;
+  p.w = reinterpret_cast<const uint8_t*>(q.b.ptr);
+  p.ldw_bytes = q.b.ld * es;
+  p.M = q.M;
+  p.N = q.N;
+  p.K = q.K;
+  p.kbytes = q.K * es;
+  p.a_stride = (p.kbytes + 127) / 128 * 128 + 64;
+  p.raw_stride = q.prologue != kProNone ? q.K * 2 + 16 : 0;
+  p.steps = (p.kbytes + 63) / 64;
+  const int ntw = (q.mode == kEpiGeglu || q.mode == kEpiRope) ? 2 : 1;
+  p.tile_offset = q.mode == kEpiGeglu ? 64 : q.mode == kEpiRope ? q.rope_head_dim / 2 : 8;
+  p.prologue = q.prologue;
+  p.style = reinterpret_cast<const __nv_bfloat16*>(q.style);
+  p.eps = q.eps;
+  p.a_inv_scale = q.a_inv_scale;
+  p.dynamic_rows = q.a_dynamic_rows ? 1 : 0;
+  p.out = q.out;
+  p.ldc = q.ldc;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(q.residual);
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(q.bias);
+  p.col_scale = q.col_scale;
+  p.row_scale = q.row_scale;
+  p.gate = reinterpret_cast<const __nv_bfloat16*>(q.gate);
+  p.alpha = q.alpha;
+  p.out_inv_scale = q.out_inv_scale;
+  p.mode = q.mode;
+  p.out_type = q.out_type;
+  p.dt = q.dt;
+  p.q_out = q.rope_q_out;
+  p.k_cache = q.rope_k_cache;
+  p.v_cache = q.rope_v_cache;
+  p.cos_table = q.rope_cos;
+  p.sin_table = q.rope_sin;
+  p.tokens = q.rope_tokens;
+  p.q_heads = q.rope_q_heads;
+  p.head_dim = q.rope_head_dim;
+  p.position_offset = q.rope_position_offset;
+  p.cache_rows = q.rope_cache_rows;
+  // K over `ksplit` warps (up to four 64-byte steps in flight each), and as many column groups
+  // per CTA as keeps the grid near one CTA per SM: the activation staging (and a fused
+  // producer) then runs once per 16-64 columns instead of once per 8-16
+  int ksplit = std::max(1, std::min(kSkinnyMaxWarps, (p.steps + kSkinnyUnroll - 1) / kSkinnyUnroll));
+  const int total_groups = (q.N + 8 * ntw - 1) / (8 * ntw);
+  int groups = std::max(1, std::min(kSkinnyMaxWarps / ksplit, (total_groups + 147) / 148));
+  p.groups = groups;
+  p.ksplit = ksplit;
+  const int warps = groups * ksplit;
+  const int smem = skinny_smem_bytes(p.a_stride, warps, ntw, p.raw_stride,
+                                     q.prologue == kProAdaNorm ? q.K * 4 : 0);
+  if (smem > 227 * 1024) return kPi05ErrUnsupported;
+  const void* kernel = nullptr;
+  if (q.op == kOpBf16) kernel = ntw == 2 ? skinny_ptr<kOpBf16, 2>(smem) : skinny_ptr<kOpBf16, 1>(smem);
+  if (q.op == kOpE4m3) kernel = ntw == 2 ? skinny_ptr<kOpE4m3, 2>(smem) : skinny_ptr<kOpE4m3, 1>(smem);
+  if (q.op == kOpS8) kernel = ntw == 2 ? skinny_ptr<kOpS8, 2>(smem) : skinny_ptr<kOpS8, 1>(smem);
+  plan->skinny = true;
+  plan->kernel = kernel;
+  plan->threads = 32 * warps;
+  plan->smem_bytes = smem;
+  plan->grid = dim3(static_cast<unsigned>((total_groups + groups - 1) / groups), 1, 1);
+  plan->swap = false;
+  plan->block_n = 8 * ntw;
+  plan->split_k = 1;
+  plan->persistent = false;
+  return kPi05Ok;
+}
+
+}  // namespace
+
 int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   if (plan == nullptr || q.a.ptr == nullptr || q.b.ptr == nullptr || q.out == nullptr ||
       q.M <= 0 || q.N <= 0 || q.K <= 0 || q.nb0 <= 0 || q.nb1 <= 0 || q.status == nullptr) {
     return kPi05ErrInvalidValue;
+  }
+  plan->skinny = false;
+  {
+    // at most 16 rows: the register-streaming kernel, unless the caller pins a tcgen05 variant
+    const bool pinned = q.force_swap >= 0 || q.force_block_n != 0 || q.force_split_k != 0 ||
+                        q.force_two_per_sm >= 0;
+    const bool want = q.force_skinny == 1 || needs_skinny(q) || (q.force_skinny < 0 && !pinned);
+    if (want && q.force_skinny != 0 && skinny_fits(q)) {
+      if (q.op != kOpBf16 && q.op != kOpE4m3 && q.op != kOpS8) return kPi05ErrInvalidValue;
+      if (q.out_type < kOutBf16 || q.out_type > kOutS8) return kPi05ErrInvalidValue;
+      if (q.out_type == kOutS32 && q.op != kOpS8) return kPi05ErrInvalidValue;
+      if ((q.mode == kEpiBiasResidual || q.mode == kEpiGateResidual || q.mode == kEpiEuler) &&
+          q.residual == nullptr) {
+        return kPi05ErrInvalidValue;
+      }
+      if (q.mode == kEpiGateResidual && q.gate == nullptr) return kPi05ErrInvalidValue;
+      return skinny_plan_build(q, plan);
+    }
+    if (q.force_skinny == 1 || needs_skinny(q)) return kPi05ErrUnsupported;
   }
   if (q.op != kOpBf16 && q.op != kOpE4m3 && q.op != kOpS8) return kPi05ErrInvalidValue;
   if (q.out_type < kOutBf16 || q.out_type > kOutS8) return kPi05ErrInvalidValue;
@@ -321,6 +454,20 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
 }
 
 cudaError_t gemm_plan_launch(const GemmPlan& plan, cudaStream_t stream) {
+  if (plan.skinny) {
+    void* skinny_args[1] = {const_cast<SkinnyParams*>(&plan.skinny_params)};
+    cudaLaunchConfig_t config = {};
+    config.gridDim = plan.grid;
+    config.blockDim = dim3(plan.threads);
+    config.dynamicSmemBytes = plan.smem_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelExC(&config, plan.kernel, skinny_args);
+  }
   void* args[6] = {const_cast<CUtensorMap*>(&plan.tmap_a), const_cast<CUtensorMap*>(&plan.tmap_b),
                    const_cast<GemmParams*>(&plan.params), const_cast<int*>(&plan.tiles_a),
                    const_cast<int*>(&plan.tiles_b), const_cast<int*>(&plan.total_tiles)};

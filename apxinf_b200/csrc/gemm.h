@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "gemm_skinny.cuh"
 #include "gemm_umma.cuh"
 
 namespace pi05 {
@@ -56,6 +57,23 @@ struct GemmProblem {
   bool b_static = false;
   // b (weights) is stored K-block-major: [ceil(K / kb)][N][kb] with kb = 128 bytes of K
   bool b_blocked = false;
+  // ---- launches with at most 16 rows (gemm_skinny.cuh) ----
+  // producer fused into the activation staging: `a` then points to bf16 rows [M, K]
+  int prologue = kProNone;          // SkinnyPrologue
+  const void* style = nullptr;      // kProAdaNorm: bf16 scale | shift, each K long
+  float eps = 1e-6f;
+  float a_inv_scale = 1.0f;         // static quantisation scale^-1 of the staged activations
+  bool a_dynamic_rows = false;      // int8: per-row scales computed in the prologue
+  // kEpiRope: q|k|v projection -> rotated Q rows, K/V cache rows
+  void* rope_q_out = nullptr;
+  void* rope_k_cache = nullptr;
+  void* rope_v_cache = nullptr;
+  const float* rope_cos = nullptr;
+  const float* rope_sin = nullptr;
+  int rope_tokens = 0, rope_q_heads = 0, rope_head_dim = 0, rope_position_offset = 0,
+      rope_cache_rows = 0;
+  float dt = 0.0f;                  // kEpiEuler
+  int force_skinny = -1;            // -1 auto, 0 never, 1 always (error if the shape does not fit)
   // tuning overrides (0 / -1 = automatic)
   int force_swap = -1;
   int force_block_n = 0;
@@ -73,6 +91,8 @@ struct GemmPlan {
   bool swap = false;
   int block_n = 0;
   int split_k = 1;
+  bool skinny = false;      // gemm_skinny_kernel (M <= 16): the tensor maps are unused
+  SkinnyParams skinny_params;
   bool persistent = false;  // one CTA per SM walking tiles, double-buffered accumulator
   bool multi_wave_candidate = false;
   int tiles_a = 0, tiles_b = 0, total_tiles = 0;

@@ -110,6 +110,7 @@ extern "C" int pi05_gemm_static_scratch(const Pi05GemmArgs* args, void* cuda_str
   q.force_block_n = args->force_block_n;
   q.force_split_k = args->force_split_k;
   q.b_blocked = args->b_blocked != 0;
+  q.force_skinny = 0;  // this entry point is the split-K tcgen05 variant
   q.partials = scratch->partials;
   q.partials_bytes = PI05_STATIC_SCRATCH_BYTES;
   q.tile_counters = scratch->counters;

@@ -19,6 +19,10 @@ namespace pi05 {
 // programmatic edges is refused by the driver.
 bool pdl_enabled();
 void set_pdl_enabled(bool enabled);
+// Process-wide switch (default on): graphs whose action expert has at most 16 rows plan the
+// fused register-streaming launches; off, they plan the same launch list as larger batches.
+bool fuse_small_rows_enabled();
+void set_fuse_small_rows_enabled(bool enabled);
 
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

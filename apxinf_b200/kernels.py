@@ -42,8 +42,11 @@ def gemm(a, b, out, *, op, mode=_lib.EPI_STORE, out_type=_lib.OUT_BF16, bias=Non
          residual=None, col_scale=None, row_scale=None, pos=None, gate=None, alpha=1.0,
          out_inv_scale=1.0, b_mn_major=False, status=None, stream=None, force_swap=-1,
          force_block_n=0, partials=None, tile_counters=None, force_split_k=0,
-         static_scratch=False, b_blocked=None):
-    """out[.., M, N'] = epilogue(a[.., M, K] @ b[.., N, K]^T); see Pi05GemmArgs."""
+         static_scratch=False, b_blocked=None, force_skinny=-1, prologue=0, style=None, eps=1e-6,
+         a_inv_scale=1.0, a_dynamic_rows=False, rope=None, dt=0.0):
+    """out[.., M, N'] = epilogue(a[.., M, K] @ b[.., N, K]^T); see Pi05GemmArgs.
+    `rope`: dict(q_out, k_cache, v_cache, cos, sin, tokens, q_heads, head_dim, position_offset,
+    cache_rows) for mode EPI_ROPE."""
     m, k, lda, nb0, nb1, a_sb0, a_sb1 = _operand(a)
     if b_blocked is not None:
         # b is [ceil(K / kb), N, kb]; the logical (N, K) comes with it
@@ -74,7 +77,14 @@ def gemm(a, b, out, *, op, mode=_lib.EPI_STORE, out_type=_lib.OUT_BF16, bias=Non
         tile_counters=_ptr(tile_counters),
         max_tiles=(tile_counters.numel() if tile_counters is not None else 0),
         force_split_k=force_split_k,
-        b_blocked=int(b_blocked is not None))
+        b_blocked=int(b_blocked is not None), force_skinny=force_skinny, prologue=prologue,
+        style=_ptr(style), eps=eps, a_inv_scale=a_inv_scale, a_dynamic_rows=int(a_dynamic_rows), dt=dt)
+    if rope is not None:
+        args.rope_q_out, args.rope_k_cache, args.rope_v_cache = (_ptr(rope["q_out"]), _ptr(rope["k_cache"]),
+                                                                 _ptr(rope["v_cache"]))
+        args.rope_cos, args.rope_sin = _ptr(rope["cos"]), _ptr(rope["sin"])
+        args.rope_tokens, args.rope_q_heads, args.rope_head_dim = rope["tokens"], rope["q_heads"], rope["head_dim"]
+        args.rope_position_offset, args.rope_cache_rows = rope["position_offset"], rope["cache_rows"]
     if static_scratch:
         check(lib().pi05_gemm_static_scratch(C.byref(args), _stream_ptr(stream)),
               "pi05_gemm_static_scratch")

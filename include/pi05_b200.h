@@ -43,7 +43,18 @@ enum {
   PI05_EPI_BIAS_RESIDUAL = 3,
   PI05_EPI_BIAS_POS = 4,
   PI05_EPI_GATE_RESIDUAL = 5,
-  PI05_EPI_GEGLU = 6
+  PI05_EPI_GEGLU = 6,
+  /* m <= 16 only (see "Launches with at most 16 rows" below) */
+  PI05_EPI_ROPE = 7,  /* packed q|k|v projection -> rotate-half RoPE, Q rows and K/V cache rows */
+  PI05_EPI_EULER = 8  /* out = residual + dt * bf16(bf16(v) + bias): velocity head + Euler step */
+};
+/* Producers that can run inside a GEMM of at most 16 rows instead of as a kernel before it:
+ * `a` is then a bf16 matrix [m, k] and the GEMM stages it in its operand type itself. */
+enum {
+  PI05_PRO_NONE = 0,
+  PI05_PRO_ADA_NORM = 1,  /* adaptive RMSNorm: x rsqrt(mean x^2 + eps) (1 + style[0:k]) + style[k:2k] */
+  PI05_PRO_QUANTIZE = 2,  /* conversion only (e4m3 / int8 quantisation of a bf16 tensor) */
+  PI05_PRO_RMS_NORM = 3   /* RMSNorm with unit weight */
 };
 
 /*
@@ -97,6 +108,29 @@ typedef struct Pi05GemmArgs {
    * or 128 one-byte elements, the tail block zero padded), so each tile load is one
    * contiguous run; ldb and the batch strides of b are ignored. */
   int32_t b_blocked;
+  /* Launches with at most 16 rows (m <= 16, the B=1 action expert) run on a kernel of their
+   * own that streams the weights through registers (crates/apxinf-model/src/pi05/
+   * bf16_executor.rs:89-157 is the call list it serves). force_skinny: -1 automatic (taken
+   * unless a force_* field above pins a tcgen05 variant), 0 never, 1 required
+   * (PI05_ERR_UNSUPPORTED if the problem does not fit). The fields below need that kernel. */
+  int32_t force_skinny;
+  int32_t prologue;        /* PI05_PRO_*; k <= 1024 and a multiple of 8 */
+  const void* style;       /* PI05_PRO_ADA_NORM: bf16 [2 k] */
+  float eps;
+  float a_inv_scale;       /* 1 / static activation scale of the staged operand (e4m3, int8) */
+  int32_t a_dynamic_rows;  /* int8: per-row scales computed by the prologue instead */
+  /* PI05_EPI_ROPE (n = (q_heads + 2) * head_dim, one K/V head; replaces
+   * apxinf_static_qkv_rope_*, crates/apxinf-cuda/kernels/custom/fused.cuh:471-525): row r is
+   * token r % rope_tokens of sample r / rope_tokens at position rope_position_offset + token;
+   * q_out bf16 [m, q_heads, head_dim]; K / V go to row position of the sample's
+   * [rope_cache_rows, head_dim] cache; cos / sin f32 [positions, head_dim / 2]. */
+  void* rope_q_out;
+  void* rope_k_cache;
+  void* rope_v_cache;
+  const float* rope_cos;
+  const float* rope_sin;
+  int32_t rope_tokens, rope_q_heads, rope_head_dim, rope_position_offset, rope_cache_rows;
+  float dt;                /* PI05_EPI_EULER */
 } Pi05GemmArgs;
 
 int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream);
@@ -289,6 +323,16 @@ const char* pi05_graph_launch_name(const Pi05Graph* graph, int32_t index);
 /* Copies a named intermediate ("prefix", "kv.3.k", "state", "vision.hidden", ...) to the host. */
 int pi05_graph_read_tensor(Pi05Graph* graph, const char* name, void* host, size_t capacity,
                            size_t* actual);
+
+/* Process-wide planning switches, for A/B measurements and tests; they apply to graphs captured
+ * afterwards. "programmatic_dependent_launch" (default 1): launches carry the programmatic
+ * stream-serialisation attribute. "fuse_small_rows" (default 1): graphs whose action expert has
+ * at most 16 rows run its projections on the register-streaming kernel with the row kernels
+ * fused in; 0 plans the launch list larger batches use. "attention_cluster" (default 1):
+ * key-split attention requests (few query rows) run as one launch of 8-CTA clusters that merge
+ * their slices through distributed shared memory; 0 keeps the two-launch form with scratch.
+ * Unknown names: PI05_ERR_INVALID_VALUE. */
+int pi05_set_tuning(const char* name, int32_t value);
 
 /* Last CUDA runtime error string seen by this library on the calling thread. */
 const char* pi05_last_cuda_error(void);
