@@ -393,6 +393,44 @@ int PreparedGraph::linear(const char* name, const Act& in, int rows, const Linea
   q.M = rows;
   q.N = w.n;
   q.K = static_cast<int>(std::min<long long>(w.ldk, in.ld));
+  // A few hundred rows against a very long K (the B=1 language.down: 522 x 2048 x 16384) give
+  // too few output tiles for the SMs: the K range goes in two halves as a batch of two GEMMs
+  // writing fp32 partial products, and one row kernel adds them and applies the residual.
+  {
+    const int block_k = 128 / elem_size(prec);
+    const long long tiles256 = (long long)((rows + 127) / 128) * ((w.n + 255) / 256);
+    const bool long_k = q.K / block_k >= 96 && (q.K / 2) % block_k == 0;
+    if (nb0 == 1 && mode == kEpiBiasResidual && out_type == kOutBf16 && gate == nullptr && pos == nullptr &&
+        rows > 64 && tiles256 <= 74 && long_k && w.n % 8 == 0 && d_k_partials_ != nullptr &&
+        (size_t)rows * w.n * 2 * sizeof(float) <= k_partials_bytes_) {
+      GemmProblem h = q;
+      h.K = q.K / 2;
+      h.nb0 = 2;
+      h.a = GemmOperand{in.data, rows, in.ld, h.K, 0};
+      h.b = GemmOperand{w.w, w.n, w.ldk, h.K, 0};
+      h.out = d_k_partials_;
+      h.ldc = w.n;
+      h.out_sb0 = (long long)rows * w.n;
+      h.out_type = kOutF32;
+      h.mode = kEpiStore;
+      h.col_scale = w.col_scale;
+      h.row_scale = prec == kPrecInt8 && !e_->static_int8() ? in.row_scale : nullptr;
+      h.row_scale_sb0 = 0;
+      h.alpha = e_->static_scales() ? in.scale : 1.0f;
+      h.status = e_->status();
+      h.b_static = true;
+      h.force_block_n = 256;
+      PI05_TRY(add_gemm(name, h));
+      const float* partials = static_cast<const float*>(d_k_partials_);
+      const long long count = (long long)rows * w.n;
+      const int cols = w.n;
+      const void* bias = w.bias;
+      add_kernel((std::string(name) + ".sum").c_str(), [=](cudaStream_t s) {
+        return launch_sum_partials(partials, 2, count, cols, residual, bias, out, s);
+      });
+      return kPi05Ok;
+    }
+  }
   q.nb0 = nb0;
   q.a = GemmOperand{in.data, rows, in.ld, a_sb0, 0};
   q.b = GemmOperand{w.w, w.n, w.ldk, 0, 0};
@@ -626,6 +664,9 @@ int PreparedGraph::build(bool measuring) {
   d_styles_ = arena_.alloc((size_t)(2 * ac.depth + 1) * S_ * 3 * ac.width * 2);
   d_time_emb_ = arena_.alloc((size_t)S_ * ac.width * 2);
   d_partials_ = arena_.alloc(kSplitScratchBytes);
+  // fp32 partial products of a K-halved GEMM (B=1 prefill only: a few hundred rows)
+  k_partials_bytes_ = Rp <= 640 ? (size_t)Rp * lg.width * 2 * sizeof(float) : 0;
+  d_k_partials_ = k_partials_bytes_ > 0 ? arena_.alloc(k_partials_bytes_) : nullptr;
   d_tile_counters_ = static_cast<int*>(arena_.alloc((size_t)kSplitMaxTiles * 4));
   note("state", d_state_, (size_t)Ra * c.action_dim * 2);
   note("styles", d_styles_, (size_t)(2 * ac.depth + 1) * S_ * 3 * ac.width * 2);
@@ -784,9 +825,10 @@ int PreparedGraph::build(bool measuring) {
   }
   const float dt = -1.0f / static_cast<float>(S_);
   // At most 16 action rows (B=1, H <= 16): every projection runs on the register-streaming
-  // kernel, and the row kernels between them run inside it: quantiser / adaRMSNorm as its
-  // activation staging, RoPE + cache write and the Euler update as its epilogue. Six launches
-  // per layer and step (qkv, attention x2, o, gate_up, down) instead of nine.
+  // kernel; RoPE + the K/V-cache write are the q|k|v projection's epilogue, the state quantiser
+  // the input projection's staging step, and the final norm and the Euler update the prologue
+  // and epilogue of the velocity head. Seven launches per layer and step (norm, qkv, attention,
+  // o, norm, gate_up, down) instead of nine, and three fewer per step.
   const bool fuse_rows = fuse_small_rows_enabled() && Ra <= 16 && ac.width <= 1024 && ac.width % 8 == 0 && c.action_dim % 8 == 0;
   // GEMM of <= 16 rows whose bf16 input `src` [Ra, k] is normalised / quantised while staged
   auto fused_problem = [&](const Linear& w, const void* src, int k, int prologue, const void* style,
@@ -820,12 +862,31 @@ int PreparedGraph::build(bool measuring) {
         q.ldc = ac.width;
         PI05_TRY(add_gemm("action.in", q));
       }
+      // The two adaRMSNorms of a layer stay launches of their own: as a staging step of the
+      // 80-128 CTAs of the following projection they cost each of those CTAs what the 10-CTA
+      // kernel costs once (measured: 2.5-4 us added to a 3.4 us projection, against about 2 us
+      // for the dependent-launched norm kernel).
+      PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, style_ptr(0, step), c.rms_norm_eps, &na, asite(0, "attention_norm")));
       for (int l = 0; l < ac.depth; ++l) {
         const Engine::ActionLayer& w = e_->action[l];
         const uint16_t* attn_style = static_cast<const uint16_t*>(style_ptr(2 * l, step));
         const uint16_t* mlp_style = static_cast<const uint16_t*>(style_ptr(2 * l + 1, step));
+        const void* next_style = style_ptr(2 * l + 2, step);
         {
-          GemmProblem q = fused_problem(w.qkv, ha, ac.width, kProAdaNorm, attn_style, asite(l, "attention_norm"));
+          // q|k|v projection with RoPE, Q rows and the K/V-cache rows written by its epilogue
+          GemmProblem q;
+          q.op = op_of(prec);
+          q.M = Ra;
+          q.N = w.qkv.n;
+          q.K = static_cast<int>(std::min<long long>(w.qkv.ldk, na.ld));
+          q.a = GemmOperand{na.data, Ra, na.ld, 0, 0};
+          q.b = GemmOperand{w.qkv.w, w.qkv.n, w.qkv.ldk, 0, 0};
+          q.col_scale = w.qkv.col_scale;
+          q.row_scale = prec == kPrecInt8 && !e_->static_int8() ? na.row_scale : nullptr;
+          q.alpha = e_->static_scales() ? na.scale : 1.0f;
+          q.status = e_->status();
+          q.b_static = true;
+          q.force_skinny = 1;
           q.out = qkv_a;  // unused by the RoPE epilogue, kept as a valid pointer
           q.ldc = qw + 2 * hd;
           q.mode = kEpiRope;
@@ -846,27 +907,12 @@ int PreparedGraph::build(bool measuring) {
                            v_cache[l], hd, (long long)cache_rows * hd, 0, H_ * qh, cache_rows, hd, B_, 1, scale_g,
                            logits_a, &attn_a, hd, (long long)H_ * qw, 0));
         PI05_TRY(linear("action.o", attn_a, Ra, w.o, kEpiGateResidual, ha, ac.width, kOutBf16, ha, attn_style + 2 * ac.width, nullptr, 1, 1.0f));
-        {
-          GemmProblem q = fused_problem(w.gate_up, ha, ac.width, kProAdaNorm, mlp_style, asite(l, "mlp_norm"));
-          act_a.scale = e_->scale_of(asite(l, "mlp_activation"));
-          const bool dynamic_int8 = prec == kPrecInt8 && !e_->static_int8();
-          q.out = dynamic_int8 ? act_a.wide : act_a.data;
-          q.ldc = act_a.ld;
-          q.mode = kEpiGeglu;
-          q.out_type = prec == kPrecBf16 || dynamic_int8 ? kOutBf16 : prec == kPrecFp8 ? kOutE4m3 : kOutS8;
-          q.out_inv_scale = 1.0f / act_a.scale;
-          PI05_TRY(add_gemm("action.gate_up", q));
-          if (dynamic_int8) {
-            const void* wide = act_a.wide;
-            int8_t* data = static_cast<int8_t*>(act_a.data);
-            float* rs = act_a.row_scale;
-            const int cols = static_cast<int>(act_a.ld);
-            add_kernel("quantize_rows_int8", [=](cudaStream_t s) {
-              return launch_quantize_rows_int8(wide, data, rs, Ra, cols, cols, cols, s);
-            });
-          }
-        }
+        PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, mlp_style, c.rms_norm_eps, &na, asite(l, "mlp_norm")));
+        PI05_TRY(linear_to_act("action.gate_up", na, Ra, w.gate_up, kEpiGeglu, &act_a, asite(l, "mlp_activation")));
         PI05_TRY(linear("action.down", act_a, Ra, w.down, kEpiGateResidual, ha, ac.width, kOutBf16, ha, mlp_style + 2 * ac.width, nullptr, 1, 1.0f));
+        if (l + 1 < ac.depth) {
+          PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, next_style, c.rms_norm_eps, &na, asite(l + 1, "attention_norm")));
+        }
       }
       {
         // final adaRMSNorm -> velocity head -> Euler update of the state, one launch

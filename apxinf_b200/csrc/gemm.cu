@@ -160,7 +160,12 @@ bool skinny_fits(const GemmProblem& q) {
   if (q.M > 16 || q.b_mn_major || q.b_blocked || q.nb0 * q.nb1 != 1 || q.mode == kEpiBiasPos || !aligned) {
     return false;
   }
-  if (q.prologue != kProNone && (q.K % 8 != 0 || q.K > 8 * 32 * 4)) return false;
+  if (q.prologue != kProNone) {
+    // rows are cut into 8-element chunks reduced in segments of 32 (or one power-of-two segment)
+    const int chunks = q.K / 8;
+    const bool segmentable = chunks % 32 == 0 || (chunks < 32 && (chunks & (chunks - 1)) == 0);
+    if (q.K % 8 != 0 || q.K > 4096 || !segmentable) return false;
+  }
   if (q.mode == kEpiGeglu && q.N % 128 != 0) return false;
   if (q.mode == kEpiRope &&
       (q.rope_head_dim <= 0 || q.rope_head_dim % 16 != 0 || q.N != (q.rope_q_heads + 2) * q.rope_head_dim ||
@@ -219,9 +224,9 @@ int skinny_plan_build(const GemmProblem& q, GemmPlan* plan) {
   // K over `ksplit` warps (up to four 64-byte steps in flight each), and as many column groups
   // per CTA as keeps the grid near one CTA per SM: the activation staging (and a fused
   // producer) then runs once per 16-64 columns instead of once per 8-16
-  int ksplit = std::max(1, std::min(kSkinnyMaxWarps, (p.steps + kSkinnyUnroll - 1) / kSkinnyUnroll));
+  const int ksplit = std::max(1, std::min(kSkinnyMaxWarps, (p.steps + kSkinnyUnroll - 1) / kSkinnyUnroll));
   const int total_groups = (q.N + 8 * ntw - 1) / (8 * ntw);
-  int groups = std::max(1, std::min(kSkinnyMaxWarps / ksplit, (total_groups + 147) / 148));
+  const int groups = std::max(1, std::min(kSkinnyMaxWarps / ksplit, (total_groups + 147) / 148));
   p.groups = groups;
   p.ksplit = ksplit;
   const int warps = groups * ksplit;

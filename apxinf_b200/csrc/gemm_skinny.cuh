@@ -149,7 +149,6 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
   }
 }
 
-constexpr int kMaxNormChunks = 4;  // 4 x 32 lanes x 8 elements: rows of up to 1024 elements
 
 // Stage one bf16 row (already transformed into y[]) into the activation tile in the operand type.
 template <int OP>
@@ -183,6 +182,9 @@ __device__ __forceinline__ void store_staged(uint8_t* row_smem, int chunk, const
 }  // namespace skinny
 
 constexpr int kSkinnyUnroll = 4;      // 64-byte K steps a warp keeps in flight per tile
+// Up to 16 warps per CTA: what bounds these launches is how many weight bytes are in flight
+// before the dependency wait (capping CTAs at 8 warps, so that a successor's CTAs always fit
+// beside them, measured 25 % slower: 13.0 against 10.6 ms for the whole B=1 forward).
 constexpr int kSkinnyMaxWarps = 16;
 
 // `raw_stride`: row pitch of the bf16 copy of the producer's input (fused prologues), else 0;
@@ -343,69 +345,100 @@ gemm_skinny_kernel(const SkinnyParams p) {
       __syncthreads();
       const int chunks = p.K >> 3;
       const bool normed = p.prologue == kProAdaNorm || p.prologue == kProRmsNorm;
-      for (int r = warp; r < p.M; r += warps) {
-        float x[skinny::kMaxNormChunks][8];
-        float sq = 0.0f;
+      // Every thread takes (row, 8-element chunk) items, so the ten rows of a tile are spread
+      // over the whole CTA (a warp per row leaves a 700-instruction serial chain per warp: 2.5 us).
+      // Row statistics are reduced in two fixed-order levels: shuffles inside a segment of
+      // `seg` consecutive chunks, then the row's segment partials from shared memory.
+      const int seg = chunks >= 32 ? 32 : chunks;  // chunks is a multiple of 32 or a power of two below it
+      const int parts = (chunks + 31) >> 5;
+      const int items = p.M * chunks;
+      auto transformed = [&](int r, int c, float inv, float (&y)[8]) {
+        skinny::unpack8(*reinterpret_cast<const uint4*>(raw_tile + r * p.raw_stride + c * 16), y);
+        if (p.prologue == kProAdaNorm) {
+          float sc[8], sh[8];
+          skinny::unpack8(*reinterpret_cast<const uint4*>(style_tile + c * 16), sc);
+          skinny::unpack8(*reinterpret_cast<const uint4*>(style_tile + p.K * 2 + c * 16), sh);
 #pragma unroll
-        for (int i = 0; i < skinny::kMaxNormChunks; ++i) {
-          const int c = lane + 32 * i;
-          if (c < chunks) {
-            skinny::unpack8(*reinterpret_cast<const uint4*>(raw_tile + r * p.raw_stride + c * 16), x[i]);
-          } else {
+          for (int e = 0; e < 8; ++e) y[e] = (y[e] * inv) * (1.0f + sc[e]) + sh[e];
+        } else if (normed) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) x[i][e] = 0.0f;
-          }
-#pragma unroll
-          for (int e = 0; e < 8; ++e) sq += x[i][e] * x[i][e];
+          for (int e = 0; e < 8; ++e) y[e] = y[e] * inv;
         }
-        const float inv = normed ? rsqrtf(skinny::warp_sum(sq) / static_cast<float>(p.K) + p.eps) : 1.0f;
-        float amax = 0.0f;
+        if constexpr (OP == kOpS8) {
+          // the W8A8 path stores 16-bit activations before it quantises them
 #pragma unroll
-        for (int i = 0; i < skinny::kMaxNormChunks; ++i) {
-          const int c = lane + 32 * i;
-          if (c < chunks) {
-            if (p.prologue == kProAdaNorm) {
-              float sc[8], sh[8];
-              skinny::unpack8(*reinterpret_cast<const uint4*>(style_tile + c * 16), sc);
-              skinny::unpack8(*reinterpret_cast<const uint4*>(style_tile + p.K * 2 + c * 16), sh);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) x[i][e] = (x[i][e] * inv) * (1.0f + sc[e]) + sh[e];
-            } else if (normed) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) x[i][e] = x[i][e] * inv;
-            }
-            if constexpr (OP == kOpS8) {
-              // the W8A8 path stores 16-bit activations before it quantises them
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                x[i][e] = round_bf16(x[i][e]);
-                amax = fmaxf(amax, fabsf(x[i][e]));
-              }
-            }
-          }
+          for (int e = 0; e < 8; ++e) y[e] = round_bf16(y[e]);
         }
-        if (OP == kOpS8 && p.dynamic_rows) {
-          const float scale = fmaxf(skinny::warp_max(amax) / 127.0f, 1.0e-12f);
-          if (lane == 0) s_rowscale[r] = scale;
+      };
+      auto segment_reduce = [&](float v, bool maximum) {
+        for (int o = seg >> 1; o > 0; o >>= 1) {
+          const float other = __shfl_xor_sync(0xffffffffu, v, o);
+          v = maximum ? fmaxf(v, other) : v + other;
+        }
+        return v;
+      };
+      // items are laid out so that a warp's 32 lanes cover whole segments: padded to a multiple of 32
+      const int padded_items = (items + 31) & ~31;
+      if (normed) {
+        for (int item = threadIdx.x; item < padded_items; item += blockDim.x) {
+          float sq = 0.0f;
+          const int r = item / chunks, c = item - r * chunks;
+          if (item < items) {
+            float x[8];
+            skinny::unpack8(*reinterpret_cast<const uint4*>(raw_tile + r * p.raw_stride + c * 16), x);
 #pragma unroll
-          for (int i = 0; i < skinny::kMaxNormChunks; ++i) {
-            const int c = lane + 32 * i;
-            if (c < chunks) {
-              uint32_t lo = 0, hi = 0;
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                lo |= static_cast<uint32_t>(to_s8(x[i][e] / scale)) << (8 * e);
-                hi |= static_cast<uint32_t>(to_s8(x[i][4 + e] / scale)) << (8 * e);
-              }
-              *reinterpret_cast<uint2*>(a_tile + r * p.a_stride + c * 8) = make_uint2(lo, hi);
-            }
+            for (int e = 0; e < 8; ++e) sq += x[e] * x[e];
           }
-        } else {
+          sq = segment_reduce(sq, false);
+          if (item < items && (c & (seg - 1)) == 0) s_part[r * 16 + (c >> 5)] = sq;
+        }
+        __syncthreads();
+        if (threadIdx.x < p.M) {
+          float total = 0.0f;
+          for (int part = 0; part < parts; ++part) total += s_part[threadIdx.x * 16 + part];
+          s_stat[threadIdx.x] = rsqrtf(total / static_cast<float>(p.K) + p.eps);
+        }
+        __syncthreads();
+      }
+      if (OP == kOpS8 && p.dynamic_rows) {
+        for (int item = threadIdx.x; item < padded_items; item += blockDim.x) {
+          float amax = 0.0f;
+          const int r = item / chunks, c = item - r * chunks;
+          if (item < items) {
+            float y[8];
+            transformed(r, c, normed ? s_stat[r] : 1.0f, y);
 #pragma unroll
-          for (int i = 0; i < skinny::kMaxNormChunks; ++i) {
-            const int c = lane + 32 * i;
-            if (c < chunks) skinny::store_staged<OP>(a_tile + r * p.a_stride, c, x[i], p.a_inv_scale);
+            for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(y[e]));
           }
+          amax = segment_reduce(amax, true);
+          if (item < items && (c & (seg - 1)) == 0) s_part[r * 16 + (c >> 5)] = amax;
+        }
+        __syncthreads();
+        if (threadIdx.x < p.M) {
+          float amax = 0.0f;
+          for (int part = 0; part < parts; ++part) amax = fmaxf(amax, s_part[threadIdx.x * 16 + part]);
+          s_rowscale[threadIdx.x] = fmaxf(amax / 127.0f, 1.0e-12f);
+        }
+        __syncthreads();
+        for (int item = threadIdx.x; item < items; item += blockDim.x) {
+          const int r = item / chunks, c = item - r * chunks;
+          float y[8];
+          transformed(r, c, normed ? s_stat[r] : 1.0f, y);
+          const float scale = s_rowscale[r];
+          uint32_t lo = 0, hi = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            lo |= static_cast<uint32_t>(to_s8(y[e] / scale)) << (8 * e);
+            hi |= static_cast<uint32_t>(to_s8(y[4 + e] / scale)) << (8 * e);
+          }
+          *reinterpret_cast<uint2*>(a_tile + r * p.a_stride + c * 8) = make_uint2(lo, hi);
+        }
+      } else {
+        for (int item = threadIdx.x; item < items; item += blockDim.x) {
+          const int r = item / chunks, c = item - r * chunks;
+          float y[8];
+          transformed(r, c, normed ? s_stat[r] : 1.0f, y);
+          skinny::store_staged<OP>(a_tile + r * p.a_stride, c, y, p.a_inv_scale);
         }
       }
     }

@@ -469,6 +469,36 @@ __global__ void quantize_s8_kernel(const __nv_bfloat16* input, int8_t* output, l
   }
 }
 
+// One thread per 8 consecutive outputs; the splits' loads are all in flight together.
+__global__ void sum_partials_kernel(const float* __restrict__ partials, int splits, long long count,
+                                    int cols, const __nv_bfloat16* residual,
+                                    const __nv_bfloat16* bias, __nv_bfloat16* out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long vec = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long base = vec * 8;
+  if (base >= count) return;
+  float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+  for (int s = 0; s < splits; ++s) {
+    const float4 a = __ldcg(reinterpret_cast<const float4*>(partials + s * count + base));
+    const float4 b = __ldcg(reinterpret_cast<const float4*>(partials + s * count + base) + 1);
+    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+    acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+  }
+  float r[8], bv[8];
+  unpack8(*reinterpret_cast<const uint4*>(residual + base), r);
+  if (bias != nullptr) {
+    unpack8(*reinterpret_cast<const uint4*>(bias + base % cols), bv);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) bv[i] = 0.0f;
+  }
+  float y[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) y[i] = (rb(acc[i]) + r[i]) + bv[i];
+  *reinterpret_cast<uint4*>(out + base) = pack8(y);
+}
+
 __global__ void euler_kernel(__nv_bfloat16* state, const __nv_bfloat16* velocity, long long count,
                              float dt) {
   pdl_launch_dependents();
@@ -595,6 +625,21 @@ cudaError_t launch_quantize_s8(const void* input, int8_t* output, long long coun
   return launch_pdl(quantize_s8_kernel, dim3(static_cast<unsigned>(blocks > 1184 ? 1184 : blocks)),
                     dim3(threads), 0, stream, reinterpret_cast<const __nv_bfloat16*>(input), output,
                     count, inv_scale);
+}
+
+cudaError_t launch_sum_partials(const float* partials, int splits, long long count, int cols,
+                                const void* residual, const void* bias, void* out,
+                                cudaStream_t stream) {
+  if (partials == nullptr || residual == nullptr || out == nullptr || splits <= 0 || count <= 0 ||
+      cols <= 0 || (cols & 7) != 0 || count % cols != 0) {
+    return cudaErrorInvalidValue;
+  }
+  const int threads = 256;
+  const long long vecs = count / 8;
+  return launch_pdl(sum_partials_kernel, dim3(static_cast<unsigned>((vecs + threads - 1) / threads)),
+                    dim3(threads), 0, stream, partials, splits, count, cols,
+                    reinterpret_cast<const __nv_bfloat16*>(residual),
+                    reinterpret_cast<const __nv_bfloat16*>(bias), reinterpret_cast<__nv_bfloat16*>(out));
 }
 
 cudaError_t launch_euler(void* state, const void* velocity, long long count, float dt,

@@ -88,6 +88,13 @@ cudaError_t launch_quantize_e4m3(const void* input, uint8_t* output, long long c
 cudaError_t launch_quantize_s8(const void* input, int8_t* output, long long count, float inv_scale,
                                cudaStream_t stream);
 
+// out = bf16((bf16(sum_s partials[s]) + residual) + bias): finishes a GEMM whose K range was cut
+// into `splits` batches writing fp32 partial products [splits][count] (count = rows * cols,
+// cols a multiple of 8; bias bf16 [cols] or null).
+cudaError_t launch_sum_partials(const float* partials, int splits, long long count, int cols,
+                                const void* residual, const void* bias, void* out,
+                                cudaStream_t stream);
+
 // state <- bf16(state + dt * velocity)
 cudaError_t launch_euler(void* state, const void* velocity, long long count, float dt,
                          cudaStream_t stream);
