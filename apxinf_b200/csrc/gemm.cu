@@ -99,7 +99,7 @@ const void* persistent_ptr(int* smem, int* threads) {
 template <int OP>
 const void* select_persistent(int block_n, bool b_mn, int* smem, int* threads) {
   if (b_mn) {
-    if constexpr (OP == kOpBf16) {
+    if constexpr (OP == kOpBf16 || OP == kOpE4m3) {
       if (block_n == 128) return persistent_ptr<OP, 128, 6, true>(smem, threads);
       if (block_n == 256) return persistent_ptr<OP, 256, 4, true>(smem, threads);
     }
@@ -115,7 +115,7 @@ template <int OP>
 const void* select_kernel(int block_n, bool swap, bool b_mn, bool multi_wave, int* smem,
                           int* threads) {
   if (b_mn) {
-    if constexpr (OP == kOpBf16) {
+    if constexpr (OP == kOpBf16 || OP == kOpE4m3) {
       if (block_n == 128) return kernel_ptr<OP, 128, 6, false, true>(smem, threads);
       if (block_n == 256) return kernel_ptr<OP, 256, 4, false, true>(smem, threads);
     }
@@ -264,7 +264,7 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
     const bool want = q.force_skinny == 1 || needs_skinny(q) || (q.force_skinny < 0 && !pinned);
     if (want && q.force_skinny != 0 && skinny_fits(q)) {
       if (q.op != kOpBf16 && q.op != kOpE4m3 && q.op != kOpS8) return kPi05ErrInvalidValue;
-      if (q.out_type < kOutBf16 || q.out_type > kOutS8) return kPi05ErrInvalidValue;
+      if (q.out_type < kOutBf16 || q.out_type > kOutF16) return kPi05ErrInvalidValue;
       if (q.out_type == kOutS32 && q.op != kOpS8) return kPi05ErrInvalidValue;
       if ((q.mode == kEpiBiasResidual || q.mode == kEpiGateResidual || q.mode == kEpiEuler) &&
           q.residual == nullptr) {
@@ -276,14 +276,14 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
     if (q.force_skinny == 1 || needs_skinny(q)) return kPi05ErrUnsupported;
   }
   if (q.op != kOpBf16 && q.op != kOpE4m3 && q.op != kOpS8) return kPi05ErrInvalidValue;
-  if (q.out_type < kOutBf16 || q.out_type > kOutS8) return kPi05ErrInvalidValue;
+  if (q.out_type < kOutBf16 || q.out_type > kOutF16) return kPi05ErrInvalidValue;
   if (q.out_type == kOutS32 && q.op != kOpS8) return kPi05ErrInvalidValue;
   if (q.mode == kEpiGeglu && (q.N % 128 != 0 || q.b_mn_major)) return kPi05ErrInvalidValue;
   if ((q.mode == kEpiBiasResidual || q.mode == kEpiGateResidual) && q.residual == nullptr)
     return kPi05ErrInvalidValue;
   if (q.mode == kEpiGateResidual && q.gate == nullptr) return kPi05ErrInvalidValue;
   if (q.mode == kEpiBiasPos && (q.pos == nullptr || q.pos_rows <= 0)) return kPi05ErrInvalidValue;
-  if (q.b_mn_major && q.op != kOpBf16) return kPi05ErrUnsupported;
+  if (q.b_mn_major && q.op == kOpS8) return kPi05ErrUnsupported;
   if (q.b_blocked && (q.b_mn_major || q.nb0 * q.nb1 != 1)) return kPi05ErrUnsupported;
 
   const int es = elem_bytes(q.op);
@@ -342,8 +342,9 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
                     block_k, 128);
     if (rc != kPi05Ok) return rc;
     if (q.b_mn_major) {
+      // [K, N] row-major: boxes of one 128-byte run along N by one K block of rows
       rc = encode_operand_map(&plan->tmap_b, q.op, q.b.ptr, q.N, q.K, q.nb0, q.nb1, q.b.ld, q.b.sb0,
-                      q.b.sb1, 64, 64);
+                      q.b.sb1, block_k, block_k);
     } else if (q.b_blocked) {
       rc = encode_operand_map(&plan->tmap_b, q.op, q.b.ptr, block_k, q.N, (q.K + block_k - 1) / block_k, 1,
                       block_k, (long long)q.N * block_k, 0, block_k, block_n);

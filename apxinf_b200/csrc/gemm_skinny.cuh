@@ -533,6 +533,8 @@ gemm_skinny_kernel(const SkinnyParams p) {
     auto store = [&](void* base, long long index, float o) {
       if (p.out_type == kOutBf16) {
         reinterpret_cast<__nv_bfloat16*>(base)[index] = __float2bfloat16(o);
+      } else if (p.out_type == kOutF16) {
+        reinterpret_cast<__half*>(base)[index] = __float2half_rn(o);
       } else if (p.out_type == kOutE4m3) {
         reinterpret_cast<uint8_t*>(base)[index] = to_e4m3(o * p.out_inv_scale);
       } else if (p.out_type == kOutS8) {
@@ -589,7 +591,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
       if (n >= p.N) continue;
       const long long index = static_cast<long long>(row) * p.ldc + n;
       float o;
-      if (p.out_type == kOutF32) {
+      if (out_is_raw(p.out_type)) {
         o = v[j];
       } else {
         const float extra =

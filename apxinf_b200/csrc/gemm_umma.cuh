@@ -23,6 +23,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
 #include "launch.cuh"
@@ -50,6 +51,7 @@ enum OutType : int {
   kOutF32 = 2,   // raw scaled accumulator (no epilogue rounding), for tests / partial sums
   kOutS32 = 3,   // raw int32 accumulator (kOpS8 only), for bit-exact checks
   kOutS8 = 4,    // static per-tensor int8: clamp(round_half_away(bf16(o) * out_inv_scale), -128, 127)
+  kOutF16 = 5,   // raw scaled accumulator rounded once to f16 (the reference's FP8 GEMM contract)
 };
 
 enum GemmStatus : int {
@@ -222,8 +224,13 @@ __device__ __forceinline__ uint8_t out_byte(const GemmParams& p, float o) {
                               : to_e4m3(o * p.out_inv_scale);
 }
 
+// outputs that skip the fused epilogue: the scaled accumulator itself
+__device__ __forceinline__ bool out_is_raw(int out_type) { return out_type == kOutF32 || out_type == kOutF16; }
+
 __device__ __forceinline__ void store_one(const GemmParams& p, long long index, float o) {
-  if (p.out_type == kOutBf16) {
+  if (p.out_type == kOutF16) {
+    reinterpret_cast<__half*>(p.out)[index] = __float2half_rn(o);
+  } else if (p.out_type == kOutBf16) {
     reinterpret_cast<__nv_bfloat16*>(p.out)[index] = __float2bfloat16(o);
   } else if (out_is_byte(p)) {
     reinterpret_cast<uint8_t*>(p.out)[index] = out_byte(p, o);
@@ -317,6 +324,22 @@ __device__ __forceinline__ void store_chunk8(const GemmParams& p, long long inde
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
         if (t < valid) dst[t] = out_byte(p, o[t]);
+      }
+    }
+  } else if (p.out_type == kOutF16) {
+    __half* dst = reinterpret_cast<__half*>(p.out) + index;
+    if (valid >= 8 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+      uint32_t w[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const __half2 pair = __floats2half2_rn(o[2 * t], o[2 * t + 1]);
+        w[t] = *reinterpret_cast<const uint32_t*>(&pair);
+      }
+      *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        if (t < valid) dst[t] = __float2half_rn(o[t]);
       }
     }
   } else if (p.out_type == kOutF32) {
@@ -527,7 +550,7 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
             o[0] *= s0.x; o[1] *= s0.y; o[2] *= s0.z; o[3] *= s0.w;
             o[4] *= s1.x; o[5] *= s1.y; o[6] *= s1.z; o[7] *= s1.w;
           }
-          if (p.out_type != kOutF32) {
+          if (!out_is_raw(p.out_type)) {
             const float4 b0 = reinterpret_cast<const float4*>(s_bias + j)[0];
             const float4 b1 = reinterpret_cast<const float4*>(s_bias + j)[1];
             const float bias[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
@@ -650,7 +673,7 @@ __device__ __forceinline__ void epilogue_swapped(const GemmParams& p,
           reinterpret_cast<int*>(p.out)[index] = static_cast<int>(raw[t]);
         } else {
           const float v = acc_to_float<OP>(raw[t]) * rs[t] * sc;
-          const float o = p.out_type == kOutF32 ? v : epi_apply<MODE>(v, bias, extra[t], gate);
+          const float o = out_is_raw(p.out_type) ? v : epi_apply<MODE>(v, bias, extra[t], gate);
           store_one(p, index, o);
         }
       }
@@ -664,7 +687,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   using T = OpTraits<OP>;
   static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 256, "bad BLOCK_N");
-  static_assert(!B_MN || (OP == kOpBf16 && BLOCK_N % 64 == 0 && !SWAP), "MN-major B: bf16 only");
+  static_assert(!B_MN || ((OP == kOpBf16 || OP == kOpE4m3) && BLOCK_N % 128 == 0 && !SWAP),
+                "MN-major B: bf16 or e4m3, activations on the 128-row side");
   static_assert(EPI_WARPS == 4 || EPI_WARPS == 8, "4 or 8 epilogue warps");
   constexpr int kHalves = EPI_WARPS / 4;
   constexpr int kEpilogueThreads = 32 * EPI_WARPS;
@@ -740,10 +764,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint8_t* sb = smem + s * kStageBytes + kStageABytes;
         const int kb = kb_begin + it;
         if constexpr (B_MN) {
+          // MN-major B: 128-byte runs along N (kBlockK elements wide), kBlockK K-rows per chunk
 #pragma unroll
-          for (int chunk = 0; chunk < BLOCK_N / 64; ++chunk) {
-            ptx::tma_load_4d(sb + chunk * 8192, &tmap_b, &full_bar[s],
-                             tile_b * BLOCK_N + chunk * 64, kb * kBlockK, b0, b1);
+          for (int chunk = 0; chunk < BLOCK_N / kBlockK; ++chunk) {
+            ptx::tma_load_4d(sb + chunk * (kBlockK * 128), &tmap_b, &full_bar[s],
+                             tile_b * BLOCK_N + chunk * kBlockK, kb * kBlockK, b0, b1);
           }
         } else if (p.blocked_b) {
           ptx::tma_load_4d(sb, &tmap_b, &full_bar[s], 0, tile_b * BLOCK_N, kb, 0);
@@ -799,7 +824,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const uint64_t adesc = ptx::make_smem_desc(a_addr + k * 32, 16, 1024);
-          const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b_addr + k * 2048, 8192, 1024)
+          const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b_addr + k * (kBlockK / 4) * 128, kBlockK * 128, 1024)
                                       : ptx::make_smem_desc(b_addr + k * 32, 16, 1024);
           ptx::umma<T::kKind>(tmem_base, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
         }
@@ -1098,9 +1123,9 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ptx::tma_load_4d(sa, &tmap_a, &full_bar[s], kb * kBlockK, ta * kTileRowsA, b0, b1);
           if constexpr (B_MN) {
 #pragma unroll
-            for (int chunk = 0; chunk < BLOCK_N / 64; ++chunk) {
-              ptx::tma_load_4d(sb + chunk * 8192, &tmap_b, &full_bar[s], tb * BLOCK_N + chunk * 64,
-                               kb * kBlockK, b0, b1);
+            for (int chunk = 0; chunk < BLOCK_N / kBlockK; ++chunk) {
+              ptx::tma_load_4d(sb + chunk * (kBlockK * 128), &tmap_b, &full_bar[s],
+                               tb * BLOCK_N + chunk * kBlockK, kb * kBlockK, b0, b1);
             }
           } else if (p.blocked_b) {
             ptx::tma_load_4d(sb, &tmap_b, &full_bar[s], 0, tb * BLOCK_N, kb, 0);
@@ -1131,7 +1156,7 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint64_t adesc = ptx::make_smem_desc(a_addr + k * 32, 16, 1024);
-            const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b_addr + k * 2048, 8192, 1024)
+            const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b_addr + k * (kBlockK / 4) * 128, kBlockK * 128, 1024)
                                         : ptx::make_smem_desc(b_addr + k * 32, 16, 1024);
             ptx::umma<T::kKind>(tmem_base + buf * BLOCK_N, adesc, bdesc, kIdesc,
                                 (kb | k) != 0 ? 1u : 0u);

@@ -35,7 +35,9 @@ typedef enum Pi05Status {
 /* Operand / output element types and fused epilogues of pi05_gemm. */
 enum { PI05_OP_BF16 = 0, PI05_OP_E4M3 = 1, PI05_OP_S8 = 2 };
 /* PI05_OUT_S8: static per-tensor int8, clamp(round_half_away(bf16(o) * out_inv_scale), -128, 127) */
-enum { PI05_OUT_BF16 = 0, PI05_OUT_E4M3 = 1, PI05_OUT_F32 = 2, PI05_OUT_S32 = 3, PI05_OUT_S8 = 4 };
+/* PI05_OUT_F16: the scaled accumulator rounded once to f16, no fused epilogue (as PI05_OUT_F32) */
+enum { PI05_OUT_BF16 = 0, PI05_OUT_E4M3 = 1, PI05_OUT_F32 = 2, PI05_OUT_S32 = 3, PI05_OUT_S8 = 4,
+       PI05_OUT_F16 = 5 };
 enum {
   PI05_EPI_STORE = 0,
   PI05_EPI_BIAS_GELU = 1,
