@@ -25,6 +25,23 @@ class EngineOptions(C.Structure):
                 ("int8_activations", C.c_int32)]
 
 
+class HostTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("data", C.c_void_p), ("elements", C.c_uint64),
+                ("dtype", C.c_int32)]
+
+
+class Observation(C.Structure):
+    _fields_ = [("token_count", C.c_int32), ("image_layout", C.c_int32), ("images", C.c_void_p),
+                ("patches", C.c_void_p), ("token_ids", C.c_void_p), ("noise", C.c_void_p),
+                ("noise_dtype", C.c_int32)]
+
+
+class Signature(C.Structure):
+    _fields_ = [("elements", C.c_uint64), ("sum", C.c_double), ("abs_checksum", C.c_double),
+                ("l2", C.c_double), ("max_abs", C.c_double), ("sample_count", C.c_int32),
+                ("sample", C.c_float * 256)]
+
+
 _P = C.c_void_p
 _SZ = C.c_size_t
 
@@ -37,6 +54,15 @@ PROTOTYPES = [
     ("pi05_engine_set_activation_scale", C.c_int, [_P, C.c_char_p, C.c_float]),
     ("pi05_engine_activation_scale", C.c_float, [_P, C.c_char_p]),
     ("pi05_set_tuning", C.c_int, [C.c_char_p, C.c_int32]),
+    ("pi05_engine_create_from_tensors", C.c_int,
+     [C.POINTER(ModelConfig), C.POINTER(EngineOptions), C.POINTER(HostTensor), C.c_int32, C.POINTER(_P)]),
+    ("pi05_device_sm", C.c_int, [C.c_int32]),
+    ("pi05_runtime_create", C.c_int, [_P, C.POINTER(_P)]),
+    ("pi05_runtime_destroy", None, [_P]),
+    ("pi05_runtime_infer", C.c_int, [_P, C.POINTER(Observation), _P]),
+    ("pi05_runtime_plan_info", C.c_int,
+     [_P, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    ("pi05_graph_signature", C.c_int, [_P, C.c_char_p, C.POINTER(Signature)]),
     ("pi05_engine_destroy", None, [_P]),
     ("pi05_engine_weight_bytes", _SZ, [_P]),
     ("pi05_engine_read_weight", C.c_int, [_P, C.c_char_p, _P, _SZ, C.POINTER(_SZ)]),

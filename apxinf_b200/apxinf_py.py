@@ -3,15 +3,23 @@ extension (crates/apxinf-py/src/lib.rs:196-500, stub crates/apxinf-py/apxinf_py.
 method names, argument order, shapes, dtypes and error texts, so code written against
 `apxinf_py` runs on this library with `from apxinf_b200 import apxinf_py`.
 
-`Model.load` (checkpoint files) is not available: only synthetic weights exist here.
+Both constructors end in the same library calls: `Model.random` (seeded weights generated on the
+device) and `Model.load` (a LeRobot / OpenPI SafeTensors checkpoint read by
+apxinf_b200.checkpoint). Inference goes through the library's owning frontend
+(`pi05_runtime_infer`): one cached prepared plan per (token count, input kind), like
+Pi05VlaRuntime (crates/apxinf-model/src/pi05/vla_runtime.rs:393-495).
 """
 from __future__ import annotations
 
-from typing import Dict, Optional, Tuple
+import os
+from dataclasses import replace
+from typing import Optional
 
 import numpy as np
 
-from .engine import CapturedGraph, Pi05Config, Pi05Runtime
+from . import checkpoint as _checkpoint
+from ._lib import lib as _lib
+from .engine import Pi05Config, Pi05Runtime, PolicyRuntime
 
 __version__ = "0.1.0"
 
@@ -34,15 +42,60 @@ class Model:
         self._rt = runtime
         self._config = config
         self._device = device
-        self._graphs: Dict[Tuple[str, int], CapturedGraph] = {}
+        self._frontend = PolicyRuntime(runtime)
 
     # ---- construction -------------------------------------------------------------------
     @staticmethod
     def load(model: str, path: str, device: str = "cuda:0", precision: str = "auto",
              calibration: Optional[str] = None, tactics: Optional[str] = None,
              action_horizon: Optional[int] = None) -> "Model":
-        raise NotImplementedError(
-            "apxinf_py.load: checkpoint loading is not part of this library; use Model.random")
+        """A checkpoint directory, `.safetensors` file or index (crates/apxinf-py/src/lib.rs:208-247,
+        load_pi05 in crates/apxinf-model/src/pi05/vla_runtime.rs:497-625). `precision` "auto"
+        picks fp8 when both a calibration and a tactics file are present (given, or
+        `calibration.json` / `tactics.json` beside the checkpoint), else bf16 on this hardware.
+        FP8 needs the calibration (one scale per named activation site) and, like the
+        reference, refuses to run without a tactics file — whose content is not used here:
+        this library plans its own kernels. `action_horizon` overrides `config.json`."""
+        if model not in ("pi05", "pi0.5"):
+            raise ValueError(f"apxinf_py.load: unknown model `{model}`")
+        if precision not in ("auto",) + tuple(_PRECISIONS):
+            raise ValueError(f"apxinf_py: unsupported precision `{precision}` "
+                             "(expected `auto`, `bf16`, `fp8` or `int8`)")
+        index = _parse_device(device)
+        path = os.fspath(path)
+        try:
+            config = _checkpoint.load_config(path)
+            if action_horizon is not None:
+                config = replace(config, action_horizon=int(action_horizon))
+                _checkpoint.validate_config(config)
+            root = _checkpoint.artifact_root(path)
+
+            def artifact(given, name):
+                if given is not None:
+                    return os.fspath(given)
+                candidate = os.path.join(root, name)
+                return candidate if os.path.isfile(candidate) else None
+
+            calibration_path = artifact(calibration, "calibration.json")
+            tactics_path = artifact(tactics, "tactics.json")
+            resolved = _checkpoint.resolve_precision(
+                precision if precision == "auto" else _PRECISIONS[precision],
+                _lib().pi05_device_sm(index), calibration_path is not None and tactics_path is not None)
+            scales = None
+            if resolved == "fp8":
+                if calibration_path is None:
+                    raise RuntimeError("FP8 PI0.5 requires LoadOptions.calibration_path or calibration.json")
+                with open(calibration_path, "r", encoding="utf-8") as handle:
+                    table = _checkpoint.calibration_from_json(handle.read())
+                scales = _checkpoint.calibration_scales(config, table)
+                if tactics_path is None:
+                    raise RuntimeError("FP8 PI0.5 requires LoadOptions.tuning_path or tactics.json")
+            tensors = _checkpoint.tensor_table(config, _checkpoint.load_path(path))
+        except _checkpoint.CheckpointError as error:
+            raise RuntimeError(str(error))
+        runtime = Pi05Runtime.from_tensors(config, tensors, dtype=resolved, device=index,
+                                           activation_scales=scales)
+        return Model(runtime, config, index)
 
     @staticmethod
     def random(model: str, device: str = "cuda:0", precision: str = "bf16", num_views: int = 2,
@@ -97,14 +150,6 @@ class Model:
             raise ValueError("apxinf_py.infer: noise must be C-contiguous float32")
         return noise
 
-    def _graph(self, layout: str, token_count: int) -> CapturedGraph:
-        # one prepared graph per (input kind, token count), like the reference's plan cache
-        key = (layout, token_count)
-        if key not in self._graphs:
-            self._graphs[key] = (self._rt.capture_infer_patches(token_count) if layout == "patches"
-                                 else self._rt.capture_infer_rgb_u8(token_count, layout))
-        return self._graphs[key]
-
     def _infer_patches(self, patches, token_ids, noise) -> np.ndarray:
         """L0: float32 patches [num_views * patches_per_view, 3 * patch_size^2]; returns the
         normalized-domain action float32 [action_horizon, action_dim]."""
@@ -118,8 +163,7 @@ class Model:
             raise ValueError("apxinf_py._infer_patches: patches must be C-contiguous float32")
         tokens = self._validate_tokens(token_ids)
         noise = self._validate_noise(noise)
-        graph = self._graph("patches", tokens.size)
-        return graph.infer_host(patches[None], tokens[None], noise[None])[0]
+        return self._frontend.infer("patches", patches, tokens, noise)
 
     def infer_rgb(self, rgb_u8, layout: str, token_ids, noise) -> np.ndarray:
         """L1: resized RGB uint8, `layout` "nhwc" or "nchw"; returns the normalized-domain
@@ -136,8 +180,7 @@ class Model:
                              f"({c.num_views} views x {c.image_size}x{c.image_size}x3), got {rgb_u8.size}")
         tokens = self._validate_tokens(token_ids)
         noise = self._validate_noise(noise)
-        graph = self._graph(layout, tokens.size)
-        return graph.infer_host(rgb_u8.reshape(1, -1), tokens[None], noise[None])[0]
+        return self._frontend.infer(layout, rgb_u8, tokens, noise)
 
     # ---- shape properties ---------------------------------------------------------------
     @property
@@ -178,7 +221,5 @@ class Model:
                 f"views={c.num_views}, image={c.image_size}, patch={c.patch_size})")
 
     def close(self) -> None:
-        for graph in self._graphs.values():
-            graph.close()
-        self._graphs.clear()
+        self._frontend.close()
         self._rt.close()

@@ -2,7 +2,11 @@
 #include <new>
 
 #include "../../include/pi05_b200.h"
+#include <cmath>
+#include <cstring>
 #include <string>
+#include <unordered_map>
+#include <vector>
 
 #include "engine.h"
 
@@ -73,8 +77,16 @@ extern "C" void pi05_default_config(Pi05ModelConfig* c) {
   c->action_expert = gemma(m.action);
 }
 
-extern "C" int pi05_engine_create_ex(const Pi05ModelConfig* config, const Pi05EngineOptions* options,
-                                     Pi05Engine** out) {
+namespace pi05 {
+extern thread_local std::string g_last_cuda_error;
+}
+
+namespace {
+
+bool g_force_capture_failure = false;  // test hook of the runtime frontend's eager fallback
+
+int create_engine(const Pi05ModelConfig* config, const Pi05EngineOptions* options,
+                  std::unordered_map<std::string, pi05::HostTensor>* tensors, Pi05Engine** out) {
   if (config == nullptr || options == nullptr || out == nullptr || options->device < 0) {
     return pi05::kPi05ErrInvalidValue;
   }
@@ -96,13 +108,42 @@ extern "C" int pi05_engine_create_ex(const Pi05ModelConfig* config, const Pi05En
   o.act_scale = uses_scale ? options->act_scale : 1.0f;
   auto* impl = new (std::nothrow) pi05::Engine(to_internal(*config), o);
   if (impl == nullptr) return pi05::kPi05ErrInvalidValue;
+  if (tensors != nullptr) impl->set_host_tensors(std::move(*tensors));
   const int rc = impl->init();
   if (rc != pi05::kPi05Ok) {
+    if (!impl->missing_tensor().empty()) {
+      pi05::g_last_cuda_error = "missing or mis-sized weight tensor `" + impl->missing_tensor() + "`";
+    }
     delete impl;
     return rc;
   }
   *out = new Pi05Engine{impl};
   return pi05::kPi05Ok;
+}
+
+}  // namespace
+
+extern "C" int pi05_engine_create_ex(const Pi05ModelConfig* config, const Pi05EngineOptions* options,
+                                     Pi05Engine** out) {
+  return create_engine(config, options, nullptr, out);
+}
+
+extern "C" int pi05_engine_create_from_tensors(const Pi05ModelConfig* config,
+                                               const Pi05EngineOptions* options,
+                                               const Pi05HostTensor* tensors, int32_t count,
+                                               Pi05Engine** out) {
+  pi05::g_last_cuda_error.clear();  // a message left by this call names the offending tensor
+  if (tensors == nullptr || count <= 0) return pi05::kPi05ErrInvalidValue;
+  std::unordered_map<std::string, pi05::HostTensor> table;
+  for (int32_t i = 0; i < count; ++i) {
+    if (tensors[i].name == nullptr || tensors[i].data == nullptr ||
+        (tensors[i].dtype != PI05_TENSOR_BF16 && tensors[i].dtype != PI05_TENSOR_F32)) {
+      return pi05::kPi05ErrInvalidValue;
+    }
+    table[tensors[i].name] = pi05::HostTensor{tensors[i].data, static_cast<size_t>(tensors[i].elements),
+                                              tensors[i].dtype == PI05_TENSOR_F32};
+  }
+  return create_engine(config, options, &table, out);
 }
 
 extern "C" int pi05_engine_create(const Pi05ModelConfig* config, int32_t dtype, int32_t device,
@@ -126,6 +167,12 @@ extern "C" int pi05_set_tuning(const char* name, int32_t value) {
     pi05::set_fuse_small_rows_enabled(value != 0);
   } else if (key == "attention_cluster") {
     pi05::set_fmha_rows_cluster_enabled(value != 0);
+  } else if (key == "wait_limit_polls") {
+    pi05::set_wait_polls(value);
+  } else if (key == "drop_one_load") {
+    pi05::set_drop_load_kb(value);
+  } else if (key == "force_capture_failure") {
+    g_force_capture_failure = value != 0;
   } else {
     return pi05::kPi05ErrInvalidValue;
   }
@@ -232,4 +279,158 @@ extern "C" int pi05_graph_read_tensor(Pi05Graph* graph, const char* name, void* 
                                       size_t capacity, size_t* actual) {
   if (name == nullptr) return pi05::kPi05ErrInvalidValue;
   return PI05_GRAPH_CALL(read_tensor(name, host, capacity, actual));
+}
+
+
+// ---------------------------------------------------------------------------
+// Owning frontend: one cached prepared plan per (token_count, image_layout)
+// (crates/apxinf-model/src/pi05/vla_runtime.rs:393-495)
+// ---------------------------------------------------------------------------
+
+struct Pi05Runtime {
+  pi05::Engine* engine = nullptr;       // borrowed
+  pi05::PreparedGraph* plan = nullptr;  // the most recently used shape
+  int token_count = 0, image_layout = 0;
+  bool graph = false;                   // false: capture was unavailable, the plan runs eagerly
+  int builds = 0;
+  std::vector<uint16_t> noise_bits;     // host-side dtype normalisation of the noise
+};
+
+namespace {
+
+uint16_t to_bf16_bits(float value) {
+  uint32_t bits;
+  std::memcpy(&bits, &value, 4);
+  if ((bits & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>((bits >> 16) | 0x40u);
+  return static_cast<uint16_t>((bits + ((bits >> 16) & 1u) + 0x7fffu) >> 16);
+}
+
+// build_prepared (vla_runtime.rs:423-473): allocate, try to capture, fall back to eager
+int build_plan(Pi05Runtime* rt, int token_count, int image_layout) {
+  // the previous plan goes first: its workspace and the new one need not coexist
+  delete rt->plan;
+  rt->plan = nullptr;
+  auto* plan = new (std::nothrow) pi05::PreparedGraph(rt->engine, token_count, image_layout, 1);
+  if (plan == nullptr) return pi05::kPi05ErrInvalidValue;
+  int rc = plan->prepare();
+  if (rc == pi05::kPi05Ok) rc = plan->run_eager();
+  if (rc == pi05::kPi05Ok) rc = plan->sync();
+  if (rc != pi05::kPi05Ok) {
+    delete plan;
+    return rc;
+  }
+  const int capture_rc = g_force_capture_failure ? pi05::kPi05ErrCuda : plan->capture();
+  rt->graph = capture_rc == pi05::kPi05Ok;
+  rt->plan = plan;
+  rt->token_count = token_count;
+  rt->image_layout = image_layout;
+  ++rt->builds;
+  return pi05::kPi05Ok;
+}
+
+}  // namespace
+
+extern "C" int pi05_device_sm(int32_t device) {
+  int major = 0, minor = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return major * 10 + minor;
+}
+
+extern "C" int pi05_runtime_create(Pi05Engine* engine, Pi05Runtime** out) {
+  if (engine == nullptr || out == nullptr) return pi05::kPi05ErrInvalidValue;
+  *out = new Pi05Runtime();
+  (*out)->engine = engine->impl;
+  return pi05::kPi05Ok;
+}
+
+extern "C" void pi05_runtime_destroy(Pi05Runtime* runtime) {
+  if (runtime == nullptr) return;
+  delete runtime->plan;
+  delete runtime;
+}
+
+extern "C" int pi05_runtime_infer(Pi05Runtime* rt, const Pi05Observation* obs, float* actions_out) {
+  if (rt == nullptr || obs == nullptr || actions_out == nullptr || obs->token_ids == nullptr ||
+      obs->noise == nullptr) {
+    return pi05::kPi05ErrInvalidValue;
+  }
+  const pi05::ModelConfig& c = rt->engine->cfg();
+  if (obs->token_count <= 0 || obs->token_count > c.max_token_len) return pi05::kPi05ErrInvalidValue;
+  const bool patches = obs->image_layout == PI05_IMAGE_PATCHES;
+  if (obs->image_layout != PI05_IMAGE_NHWC && obs->image_layout != PI05_IMAGE_NCHW && !patches) {
+    return pi05::kPi05ErrInvalidValue;
+  }
+  if ((patches && obs->patches == nullptr) || (!patches && obs->images == nullptr)) {
+    return pi05::kPi05ErrInvalidValue;
+  }
+  if (obs->noise_dtype != PI05_NOISE_F32 && obs->noise_dtype != PI05_NOISE_BF16) {
+    return pi05::kPi05ErrInvalidValue;
+  }
+  if (rt->plan == nullptr || rt->token_count != obs->token_count || rt->image_layout != obs->image_layout) {
+    const int rc = build_plan(rt, obs->token_count, obs->image_layout);
+    if (rc != pi05::kPi05Ok) return rc;
+  }
+  const size_t count = static_cast<size_t>(c.action_horizon) * c.action_dim;
+  const uint16_t* noise = static_cast<const uint16_t*>(obs->noise);
+  if (obs->noise_dtype == PI05_NOISE_F32) {
+    rt->noise_bits.resize(count);
+    const float* src = static_cast<const float*>(obs->noise);
+    for (size_t i = 0; i < count; ++i) rt->noise_bits[i] = to_bf16_bits(src[i]);
+    noise = rt->noise_bits.data();
+  }
+  int rc = patches ? rt->plan->update_patch_inputs(obs->patches, obs->token_ids, noise)
+                   : rt->plan->update_inputs(obs->images, obs->token_ids, noise);
+  if (rc != pi05::kPi05Ok) return rc;
+  rc = rt->graph ? rt->plan->replay() : rt->plan->run_eager();
+  if (rc != pi05::kPi05Ok) return rc;
+  return rt->plan->output(actions_out);
+}
+
+extern "C" int pi05_runtime_plan_info(const Pi05Runtime* rt, int32_t* token_count, int32_t* image_layout,
+                                      int32_t* uses_graph, int32_t* builds) {
+  if (rt == nullptr) return pi05::kPi05ErrInvalidValue;
+  if (token_count != nullptr) *token_count = rt->plan != nullptr ? rt->token_count : 0;
+  if (image_layout != nullptr) *image_layout = rt->image_layout;
+  if (uses_graph != nullptr) *uses_graph = rt->plan != nullptr && rt->graph ? 1 : 0;
+  if (builds != nullptr) *builds = rt->builds;
+  return pi05::kPi05Ok;
+}
+
+// Stage signature of a named bf16 intermediate
+// (crates/apxinf-model/examples/pi05_integrity_probe.rs:19-51).
+extern "C" int pi05_graph_signature(Pi05Graph* graph, const char* name, Pi05Signature* out) {
+  if (graph == nullptr || name == nullptr || out == nullptr) return pi05::kPi05ErrInvalidValue;
+  size_t bytes = 0;
+  int rc = graph->impl->read_tensor(name, nullptr, 0, &bytes);
+  if (rc != pi05::kPi05Ok) return rc;
+  std::vector<uint16_t> raw(bytes / 2);
+  rc = graph->impl->read_tensor(name, raw.data(), bytes, &bytes);
+  if (rc != pi05::kPi05Ok) return rc;
+  auto value_at = [&](size_t i) {
+    const uint32_t wide = static_cast<uint32_t>(raw[i]) << 16;
+    float v;
+    std::memcpy(&v, &wide, 4);
+    return static_cast<double>(v);
+  };
+  *out = Pi05Signature{};
+  out->elements = raw.size();
+  double squares = 0.0;
+  for (size_t i = 0; i < raw.size(); ++i) {
+    const double v = value_at(i);
+    out->sum += v;
+    out->abs_checksum += v < 0 ? -v : v;
+    squares += v * v;
+    if ((v < 0 ? -v : v) > out->max_abs) out->max_abs = v < 0 ? -v : v;
+  }
+  out->l2 = std::sqrt(squares);
+  out->sample_count = static_cast<int32_t>(raw.size() < 256 ? raw.size() : 256);
+  for (int32_t i = 0; i < out->sample_count; ++i) {
+    const size_t source = out->sample_count == 1 ? 0 : static_cast<size_t>(i) * (raw.size() - 1) / (out->sample_count - 1);
+    out->sample[i] = static_cast<float>(value_at(source));
+  }
+  return pi05::kPi05Ok;
 }

@@ -77,17 +77,76 @@ int ModelConfig::validate() const {
 // Engine: weights
 // ---------------------------------------------------------------------------
 
+namespace {
+// Timing events of one call: created on demand, destroyed on every way out.
+struct EventSet {
+  std::vector<cudaEvent_t> all;
+  ~EventSet() {
+    for (cudaEvent_t e : all) cudaEventDestroy(e);
+  }
+  int add(cudaEvent_t* out) {
+    const cudaError_t err = cudaEventCreate(out);
+    if (err != cudaSuccess) return record_cuda(err);
+    all.push_back(*out);
+    return kPi05Ok;
+  }
+};
+}  // namespace
+
 Engine::Engine(const ModelConfig& cfg, const EngineOptions& options)
     : cfg_(cfg), prec_(options.precision), device_(options.device), seed_(options.seed),
       act_scale_(options.act_scale), weight_dist_(options.weight_dist),
       int8_static_(options.int8_activations == kInt8Static) {}
 
-cudaError_t Engine::fill(void* dst_bf16, long long count) {
+namespace {
+constexpr long long kConvertChunk = 32ll << 20;  // elements per staged chunk of a converted host tensor
+}
+
+// The next tensor, as bf16 (or as f32 when as_f32): from the host table when one was given, else
+// the next `count` values of the synthetic stream (bf16 only).
+int Engine::fetch(const std::string& name, void* dst, long long count, bool as_f32) {
+  if (from_host_) {
+    auto it = host_tensors_.find(name);
+    if (it == host_tensors_.end() || it->second.data == nullptr ||
+        it->second.elements != static_cast<size_t>(count)) {
+      missing_tensor_ = name;
+      return kPi05ErrInvalidValue;
+    }
+    const HostTensor& t = it->second;
+    const size_t src_size = t.f32 ? 4 : 2, dst_size = as_f32 ? 4 : 2;
+    if (t.f32 == as_f32) {
+      PI05_CUDA(cudaMemcpyAsync(dst, t.data, static_cast<size_t>(count) * src_size,
+                                cudaMemcpyHostToDevice, stream_));
+    } else {
+      for (long long done = 0; done < count; done += kConvertChunk) {
+        const long long n = std::min(kConvertChunk, count - done);
+        PI05_CUDA(cudaMemcpyAsync(tmp_convert_, static_cast<const char*>(t.data) + done * src_size,
+                                  static_cast<size_t>(n) * src_size, cudaMemcpyHostToDevice, stream_));
+        PI05_CUDA(launch_convert(tmp_convert_, static_cast<char*>(dst) + done * dst_size, n,
+                                 as_f32 ? 1 : 0, stream_));
+        PI05_CUDA(cudaStreamSynchronize(stream_));
+      }
+    }
+    // the destination may be reused by the next tensor; pageable host memory is consumed at once
+    PI05_CUDA(cudaStreamSynchronize(stream_));
+    return kPi05Ok;
+  }
+  if (as_f32) return kPi05ErrInvalidValue;
   const cudaError_t err = weight_dist_ == kWeightsNormal
-                              ? launch_normal_fill(dst_bf16, seed_, cursor_, count, stream_)
-                              : launch_lcg_fill(dst_bf16, seed_, cursor_, count, stream_);
+                              ? launch_normal_fill(dst, seed_, cursor_, count, stream_)
+                              : launch_lcg_fill(dst, seed_, cursor_, count, stream_);
   cursor_ += static_cast<uint64_t>(count);
-  return err;
+  return record_cuda(err);
+}
+
+int Engine::fetch_layer_norm(const std::string& prefix, int width, LayerNormParams* out) {
+  if (!from_host_ || host_tensors_.find(prefix + ".weight") == host_tensors_.end()) return kPi05Ok;
+  out->weight = dmalloc(static_cast<size_t>(width) * 2);
+  out->bias = dmalloc(static_cast<size_t>(width) * 2);
+  if (out->weight == nullptr || out->bias == nullptr) return record_cuda(cudaErrorMemoryAllocation);
+  PI05_TRY(fetch(prefix + ".weight", out->weight, width));
+  PI05_TRY(fetch(prefix + ".bias", out->bias, width));
+  return kPi05Ok;
 }
 
 float Engine::scale_of(const std::string& site) const {
@@ -139,19 +198,23 @@ int Engine::make_linear(const std::string& prefix, const std::vector<std::string
     out->bias = dmalloc(static_cast<size_t>(n_total) * 2);
     if (out->bias == nullptr) return record_cuda(cudaErrorMemoryAllocation);
   }
+  const bool wide = wide_staging();
+  const size_t stage_elem = wide ? 4 : 2;
   void* stage = prec_ == kPrecBf16 ? out->w : tmp_stage_;
-  const size_t stage_bytes = static_cast<size_t>(n_total) * ldk * 2;
+  const size_t stage_bytes = static_cast<size_t>(n_total) * ldk * stage_elem;
   if (prec_ != kPrecBf16 && stage_bytes > tmp_stage_bytes_) return kPi05ErrInvalidValue;
   PI05_CUDA(cudaMemsetAsync(stage, 0, stage_bytes, stream_));
   int row_offset = 0;
   for (size_t i = 0; i < parts.size(); ++i) {
     const long long count = static_cast<long long>(k) * ns[i];
-    if (static_cast<size_t>(count) * 2 > tmp_src_bytes_) return kPi05ErrInvalidValue;
-    PI05_CUDA(fill(tmp_src_, count));
+    if (static_cast<size_t>(count) * stage_elem > tmp_src_bytes_) return kPi05ErrInvalidValue;
+    // part "w": the projection is its own tensor (prefix); else a sibling of the packed name
+    const std::string base = parts[i] == "w" ? prefix : prefix.substr(0, prefix.rfind('.') + 1) + parts[i];
+    PI05_TRY(fetch(base + ".weight", tmp_src_, count, wide));
     PI05_CUDA(launch_transpose_pack(tmp_src_, stage, k, ns[i], ldk, row_offset,
-                                    interleave ? 1 : 0, static_cast<int>(i), stream_));
+                                    interleave ? 1 : 0, static_cast<int>(i), stream_, wide ? 1 : 0));
     if (bias) {
-      PI05_CUDA(fill(static_cast<uint16_t*>(out->bias) + row_offset, ns[i]));
+      PI05_TRY(fetch(base + ".bias", static_cast<uint16_t*>(out->bias) + row_offset, ns[i]));
     }
     row_offset += ns[i];
   }
@@ -159,7 +222,7 @@ int Engine::make_linear(const std::string& prefix, const std::vector<std::string
     out->col_scale = static_cast<float*>(dmalloc(static_cast<size_t>(n_total) * 4));
     if (out->col_scale == nullptr) return record_cuda(cudaErrorMemoryAllocation);
     PI05_CUDA(launch_quantize_weight_rows(stage, out->w, out->col_scale, n_total, k, ldk,
-                                          prec_ == kPrecInt8 ? 1 : 0, stream_));
+                                          prec_ == kPrecInt8 ? 1 : 0, stream_, wide ? 1 : 0));
   }
   named_[prefix + ".weight"] = {out->w, static_cast<size_t>(n_total) * ldk * es};
   if (out->col_scale != nullptr) named_[prefix + ".scale"] = {out->col_scale, (size_t)n_total * 4};
@@ -241,6 +304,16 @@ int Engine::init() {
   consider(ac.width, cfg_.action_dim, cfg_.action_dim);
   // generation scratch is tracked like every other allocation, so a failed init frees it
   // with the engine; the success path releases it early (see the end of this function)
+  if (wide_staging()) {  // host tensors are staged and quantised as f32
+    max_src *= 2;
+    max_stage *= 2;
+  }
+  size_t convert_bytes = 0;
+  if (from_host_) {
+    convert_bytes = static_cast<size_t>(kConvertChunk) * 4;
+    tmp_convert_ = dmalloc(convert_bytes);
+    if (tmp_convert_ == nullptr) return record_cuda(cudaErrorMemoryAllocation);
+  }
   tmp_src_ = dmalloc(max_src);
   if (tmp_src_ == nullptr) return record_cuda(cudaErrorMemoryAllocation);
   tmp_src_bytes_ = max_src;
@@ -249,7 +322,7 @@ int Engine::init() {
     if (tmp_stage_ == nullptr) return record_cuda(cudaErrorMemoryAllocation);
     tmp_stage_bytes_ = max_stage;
   }
-  weight_bytes_ -= max_src + (prec_ != kPrecBf16 ? max_stage : 0);
+  weight_bytes_ -= max_src + (prec_ != kPrecBf16 ? max_stage : 0) + convert_bytes;
 
   // Generation order = Pi05Weights::synthetic (crates/apxinf-model/src/pi05/weights.rs:255-330).
   cursor_ = 0;
@@ -260,13 +333,16 @@ int Engine::init() {
     PI05_TRY(make_linear(p + ".o", {"o"}, vw, {vw}, true, false, &vision[i].o));
     PI05_TRY(make_linear(p + ".fc1", {"fc1"}, vw, {cfg_.vision_mlp_dim}, true, false, &vision[i].fc1));
     PI05_TRY(make_linear(p + ".fc2", {"fc2"}, cfg_.vision_mlp_dim, {vw}, true, false, &vision[i].fc2));
+    PI05_TRY(fetch_layer_norm(p + ".norm1", vw, &vision[i].norm1));
+    PI05_TRY(fetch_layer_norm(p + ".norm2", vw, &vision[i].norm2));
   }
+  PI05_TRY(fetch_layer_norm("vision.post_norm", vw, &vision_post_norm));
   PI05_TRY(make_linear("vision.patch_embedding", {"w"}, cfg_.patch_width(), {vw}, true, false, &patch));
   {
     const long long count = static_cast<long long>(cfg_.patches_per_view()) * vw;
     position_embedding = dmalloc(count * 2);
     if (position_embedding == nullptr) return record_cuda(cudaErrorMemoryAllocation);
-    PI05_CUDA(fill(position_embedding, count));
+    PI05_TRY(fetch("vision.position_embedding", position_embedding, count));
     named_["vision.position_embedding"] = {position_embedding, (size_t)count * 2};
   }
   PI05_TRY(make_linear("vision.projector", {"w"}, vw, {lg.width}, true, false, &projector));
@@ -274,7 +350,7 @@ int Engine::init() {
     const long long count = static_cast<long long>(cfg_.vocab_size) * lg.width;
     token_embedding = dmalloc(count * 2);
     if (token_embedding == nullptr) return record_cuda(cudaErrorMemoryAllocation);
-    PI05_CUDA(fill(token_embedding, count));
+    PI05_TRY(fetch("token_embedding", token_embedding, count));
     named_["token_embedding"] = {token_embedding, (size_t)count * 2};
   }
   language.resize(lg.depth);
@@ -307,6 +383,9 @@ int Engine::init() {
   tmp_src_ = nullptr;
   release(tmp_stage_);
   tmp_stage_ = nullptr;
+  release(tmp_convert_);
+  tmp_convert_ = nullptr;
+  host_tensors_.clear();  // the caller's buffers are not referenced after init
   return kPi05Ok;
 }
 
@@ -505,9 +584,12 @@ void PreparedGraph::quantize_to_act(const char* name, const void* src, int rows,
 }
 
 int PreparedGraph::norm_to_act(const char* name, const void* x, int rows, int cols, int kind,
-                               const void* style, float eps, Act* out, const std::string& site) {
+                               const void* style, float eps, Act* out, const std::string& site,
+                               const void* weight, const void* bias) {
   out->scale = e_->scale_of(site);
   NormArgs a{};
+  a.weight = weight;
+  a.bias = bias;
   a.input = x;
   a.output = out->data;
   a.row_scale = out->row_scale;
@@ -739,8 +821,12 @@ int PreparedGraph::build(bool measuring) {
   auto vsite = [](int i, const char* part) { return "vision.layers." + std::to_string(i) + "." + part; };
   auto lsite = [](int i, const char* part) { return "language.layers." + std::to_string(i) + "." + part; };
   auto asite = [](int i, const char* part) { return "action.layers." + std::to_string(i) + "." + part; };
-  PI05_TRY(norm_to_act("vision.ln1", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv,
-                       c.vision_depth > 0 ? vsite(0, "attention_norm") : std::string("vision.post_norm")));
+  {
+    const Engine::LayerNormParams& first = c.vision_depth > 0 ? e_->vision[0].norm1 : e_->vision_post_norm;
+    PI05_TRY(norm_to_act("vision.ln1", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv,
+                         c.vision_depth > 0 ? vsite(0, "attention_norm") : std::string("vision.post_norm"),
+                         first.weight, first.bias));
+  }
   const float scale_v = static_cast<float>(1.0 / std::sqrt(static_cast<double>(hd_v)));
   for (int i = 0; i < c.vision_depth; ++i) {
     const Engine::VisionBlock& w = e_->vision[i];
@@ -751,11 +837,16 @@ int PreparedGraph::build(bool measuring) {
                        (long long)pp * 3 * vw, base + 2 * vw, 3 * vw, hd_v, (long long)pp * 3 * vw, pp, pp,
                        hd_v, heads_v, n_images, scale_v, logits_v, &attn_v, vw, hd_v, (long long)pp * vw));
     PI05_TRY(linear("vision.o", attn_v, Rv, w.o, kEpiBiasResidual, xv, vw, kOutBf16, xv, nullptr, nullptr, 1, 1.0f));
-    PI05_TRY(norm_to_act("vision.ln2", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv, vsite(i, "mlp_norm")));
+    PI05_TRY(norm_to_act("vision.ln2", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv, vsite(i, "mlp_norm"),
+                         w.norm2.weight, w.norm2.bias));
     PI05_TRY(linear_to_act("vision.fc1", nv, Rv, w.fc1, kEpiBiasGelu, &act_v, vsite(i, "mlp_activation")));
     PI05_TRY(linear("vision.fc2", act_v, Rv, w.fc2, kEpiBiasResidual, xv, vw, kOutBf16, xv, nullptr, nullptr, 1, 1.0f));
-    PI05_TRY(norm_to_act(i + 1 < c.vision_depth ? "vision.ln1" : "vision.post_ln", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv,
-                         i + 1 < c.vision_depth ? vsite(i + 1, "attention_norm") : std::string("vision.post_norm")));
+    {
+      const Engine::LayerNormParams& next = i + 1 < c.vision_depth ? e_->vision[i + 1].norm1 : e_->vision_post_norm;
+      PI05_TRY(norm_to_act(i + 1 < c.vision_depth ? "vision.ln1" : "vision.post_ln", xv, Rv, vw, kNormLayer, nullptr, c.layer_norm_eps, &nv,
+                           i + 1 < c.vision_depth ? vsite(i + 1, "attention_norm") : std::string("vision.post_norm"),
+                           next.weight, next.bias));
+    }
   }
   // projector writes the image tokens straight into rows [0, V) of each sample's prefix
   PI05_TRY(linear("vision.projector", nv, V_, e_->projector, kEpiStore, xp, lg.width, kOutBf16, nullptr, nullptr, nullptr, 1, 1.0f, B_, (long long)V_ * vw, (long long)P_ * lg.width));
@@ -1103,83 +1194,82 @@ int PreparedGraph::output(float* host_f32) {
 
 int PreparedGraph::time_replays(int iterations, float* ms_each) {
   if (iterations <= 0 || ms_each == nullptr || exec_ == nullptr) return kPi05ErrInvalidValue;
-  cudaEvent_t begin, end;
-  PI05_CUDA(cudaEventCreate(&begin));
-  PI05_CUDA(cudaEventCreate(&end));
+  EventSet events;
+  cudaEvent_t begin = nullptr, end = nullptr;
+  PI05_TRY(events.add(&begin));
+  PI05_TRY(events.add(&end));
   int rc = kPi05Ok;
   for (int i = 0; i < iterations && rc == kPi05Ok; ++i) {
-    cudaEventRecord(begin, e_->stream());
-    rc = replay();
-    cudaEventRecord(end, e_->stream());
+    rc = record_cuda(cudaEventRecord(begin, e_->stream()));
+    if (rc == kPi05Ok) rc = replay();
+    if (rc == kPi05Ok) rc = record_cuda(cudaEventRecord(end, e_->stream()));
     if (rc == kPi05Ok) rc = record_cuda(cudaEventSynchronize(end));
-    if (rc == kPi05Ok) cudaEventElapsedTime(&ms_each[i], begin, end);
+    if (rc == kPi05Ok) rc = record_cuda(cudaEventElapsedTime(&ms_each[i], begin, end));
   }
-  cudaEventDestroy(begin);
-  cudaEventDestroy(end);
-  if (rc == kPi05Ok) rc = sync();
-  return rc;
+  const int status = sync();  // also clears a device-timeout status for the next caller
+  return rc != kPi05Ok ? rc : status;
 }
 
 int PreparedGraph::stage_times(float* ms3) {
   if (ms3 == nullptr) return kPi05ErrInvalidValue;
-  cudaEvent_t ev[4];
-  for (auto& e : ev) PI05_CUDA(cudaEventCreate(&e));
+  PI05_CUDA(cudaSetDevice(e_->device()));
+  EventSet events;
+  cudaEvent_t ev[4] = {};
+  for (auto& e : ev) PI05_TRY(events.add(&e));
   int stage = 0;
-  cudaEventRecord(ev[0], e_->stream());
-  int rc = kPi05Ok;
+  int rc = record_cuda(cudaEventRecord(ev[0], e_->stream()));
   for (const Op& op : ops_) {
-    while (op.stage > stage && stage < 2) cudaEventRecord(ev[++stage], e_->stream());
-    const cudaError_t err = launch_op(op, e_->stream());
-    if (err != cudaSuccess) {
-      rc = record_cuda(err);
-      break;
+    if (rc != kPi05Ok) break;
+    while (op.stage > stage && stage < 2 && rc == kPi05Ok) {
+      rc = record_cuda(cudaEventRecord(ev[++stage], e_->stream()));
     }
+    if (rc == kPi05Ok) rc = record_cuda(launch_op(op, e_->stream()));
   }
-  while (stage < 2) cudaEventRecord(ev[++stage], e_->stream());
-  cudaEventRecord(ev[3], e_->stream());
-  if (rc == kPi05Ok) rc = sync();
-  if (rc == kPi05Ok) {
-    for (int i = 0; i < 3; ++i) cudaEventElapsedTime(&ms3[i], ev[i], ev[i + 1]);
+  while (stage < 2 && rc == kPi05Ok) rc = record_cuda(cudaEventRecord(ev[++stage], e_->stream()));
+  if (rc == kPi05Ok) rc = record_cuda(cudaEventRecord(ev[3], e_->stream()));
+  const int status = sync();
+  if (rc == kPi05Ok) rc = status;
+  for (int i = 0; i < 3 && rc == kPi05Ok; ++i) {
+    rc = record_cuda(cudaEventElapsedTime(&ms3[i], ev[i], ev[i + 1]));
   }
-  for (auto& e : ev) cudaEventDestroy(e);
   return rc;
 }
 
 int PreparedGraph::time_launches(const char* name, float* mean_ms, int* count) {
   if (name == nullptr || mean_ms == nullptr || count == nullptr) return kPi05ErrInvalidValue;
+  *count = 0;
+  *mean_ms = 0.0f;
   PI05_CUDA(cudaSetDevice(e_->device()));
-  std::vector<cudaEvent_t> events;
+  EventSet events;
+  std::vector<cudaEvent_t> pairs;
   int rc = kPi05Ok;
   for (const Op& op : ops_) {
+    if (rc != kPi05Ok) break;
     const bool timed = op.name == name;
+    cudaEvent_t a = nullptr, b = nullptr;
     if (timed) {
-      cudaEvent_t a, b;
-      if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) {
-        rc = kPi05ErrCuda;
-        break;
-      }
-      events.push_back(a);
-      events.push_back(b);
-      cudaEventRecord(a, e_->stream());
+      rc = events.add(&a);
+      if (rc == kPi05Ok) rc = events.add(&b);
+      if (rc == kPi05Ok) rc = record_cuda(cudaEventRecord(a, e_->stream()));
+      if (rc != kPi05Ok) break;
     }
-    const cudaError_t err = launch_op(op, e_->stream());
-    if (timed) cudaEventRecord(events.back(), e_->stream());
-    if (err != cudaSuccess) {
-      rc = record_cuda(err);
-      break;
+    rc = record_cuda(launch_op(op, e_->stream()));
+    if (timed && rc == kPi05Ok) {
+      rc = record_cuda(cudaEventRecord(b, e_->stream()));
+      pairs.push_back(a);
+      pairs.push_back(b);
     }
   }
-  if (rc == kPi05Ok) rc = sync();
+  const int status = sync();
+  if (rc == kPi05Ok) rc = status;
   double total = 0.0;
-  if (rc == kPi05Ok) {
-    for (size_t i = 0; i + 1 < events.size(); i += 2) {
-      float ms = 0.0f;
-      cudaEventElapsedTime(&ms, events[i], events[i + 1]);
-      total += ms;
-    }
+  for (size_t i = 0; i + 1 < pairs.size() && rc == kPi05Ok; i += 2) {
+    float ms = 0.0f;
+    rc = record_cuda(cudaEventElapsedTime(&ms, pairs[i], pairs[i + 1]));
+    total += ms;
   }
-  for (cudaEvent_t e : events) cudaEventDestroy(e);
-  *count = static_cast<int>(events.size() / 2);
+  if (rc != kPi05Ok) return rc;
+  *count = static_cast<int>(pairs.size() / 2);
   *mean_ms = *count > 0 ? static_cast<float>(total / *count) : 0.0f;
   return rc;
 }

@@ -137,7 +137,8 @@ class PreparedGraph {
   int linear_to_act(const char* name, const Act& in, int rows, const Linear& w, int mode,
                     Act* out, const std::string& site);
   int norm_to_act(const char* name, const void* x, int rows, int cols, int kind,
-                  const void* style, float eps, Act* out, const std::string& site);
+                  const void* style, float eps, Act* out, const std::string& site,
+                  const void* weight = nullptr, const void* bias = nullptr);
   // quantises a bf16 tensor (or passes it through) into the precision's operand form
   void quantize_to_act(const char* name, const void* bf16_src, int rows, int cols, Act* out,
                        const std::string& site);
@@ -180,6 +181,20 @@ class PreparedGraph {
 enum WeightDist : int { kWeightsLcg = 0, kWeightsNormal = 1 };
 enum Int8Activations : int { kInt8Dynamic = 0, kInt8Static = 1 };
 
+// A host tensor handed to the engine instead of the synthetic stream: bf16 bits or f32, linear weights
+// in the reference's final [in, out] orientation, named as the synthetic layout names them
+// ("vision.3.q.weight", "language.0.gate.weight", "action.2.input_style.bias", "token_embedding",
+// ...), plus the LayerNorm parameters "vision.<i>.norm1.weight" / ".bias", "vision.<i>.norm2.*",
+// "vision.post_norm.*" (absent = identity).
+// f32 tensors (the reference's folded Gemma projections are f32,
+// crates/apxinf-model/src/pi05/weights.rs:584-601) are quantised from f32 by the FP8 / INT8
+// precisions, as the reference does, and rounded to bf16 (nearest even) where bf16 is stored.
+struct HostTensor {
+  const void* data = nullptr;
+  size_t elements = 0;
+  bool f32 = false;
+};
+
 struct EngineOptions {
   int precision = kPrecBf16;
   int device = 0;
@@ -192,6 +207,11 @@ struct EngineOptions {
 class Engine {
  public:
   Engine(const ModelConfig& cfg, const EngineOptions& options);
+  // weights from host tensors instead of the synthetic generator (call before init)
+  void set_host_tensors(std::unordered_map<std::string, HostTensor> tensors) {
+    host_tensors_ = std::move(tensors);
+    from_host_ = true;
+  }
   ~Engine();
   int init();  // stream, status word, rope tables, synthetic weights
   const ModelConfig& cfg() const { return cfg_; }
@@ -213,7 +233,10 @@ class Engine {
   size_t weight_bytes() const { return weight_bytes_; }
   int read_weight(const char* name, void* host, size_t capacity, size_t* actual);
 
-  struct VisionBlock { Linear qkv, o, fc1, fc2; };
+  // LayerNorm gamma / beta (bf16 device vectors; null = 1 / 0, the synthetic weights)
+  struct LayerNormParams { void* weight = nullptr; void* bias = nullptr; };
+  struct VisionBlock { Linear qkv, o, fc1, fc2; LayerNormParams norm1, norm2; };
+  LayerNormParams vision_post_norm;
   struct LanguageLayer { Linear qkv, o, gate_up, down; };
   struct ActionLayer { Linear input_style, qkv, o, post_style, gate_up, down; };
   std::vector<VisionBlock> vision;
@@ -233,7 +256,17 @@ class Engine {
                   const std::vector<int>& ns, bool bias, bool interleave, Linear* out);
   void* dmalloc(size_t bytes);
   void release(void* p);  // frees one tracked allocation early
-  cudaError_t fill(void* dst_bf16, long long count);  // next `count` stream elements
+  // the tensor `name` into dst (bf16): the next `count` stream elements, or the host tensor
+  int fetch(const std::string& name, void* dst, long long count, bool as_f32 = false);
+  int fetch_layer_norm(const std::string& prefix, int width, LayerNormParams* out);
+  std::unordered_map<std::string, HostTensor> host_tensors_;
+  bool from_host_ = false;
+  std::string missing_tensor_;  // name of the host tensor a failed init wanted
+
+ public:
+  const std::string& missing_tensor() const { return missing_tensor_; }
+
+ private:
   ModelConfig cfg_;
   int prec_, device_;
   uint64_t seed_;
@@ -246,6 +279,8 @@ class Engine {
   uint64_t cursor_ = 0;  // element offset in the synthetic stream
   void* tmp_src_ = nullptr;
   void* tmp_stage_ = nullptr;
+  void* tmp_convert_ = nullptr;  // host tensors whose type differs from the staging type, by chunk
+  bool wide_staging() const { return from_host_ && prec_ != kPrecBf16; }
   size_t tmp_src_bytes_ = 0, tmp_stage_bytes_ = 0;
   size_t weight_bytes_ = 0;
   std::vector<void*> allocations_;

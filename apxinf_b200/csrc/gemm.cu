@@ -12,7 +12,11 @@ namespace pi05 {
 namespace {
 bool g_pdl_enabled = true;
 bool g_fuse_small_rows = true;
+uint32_t g_wait_polls = ptx::kSpinLimit;
+int g_drop_load_kb = -1;
 }
+void set_wait_polls(int polls) { g_wait_polls = polls > 0 ? static_cast<uint32_t>(polls) : ptx::kSpinLimit; }
+void set_drop_load_kb(int kb) { g_drop_load_kb = kb; }
 bool pdl_enabled() { return g_pdl_enabled; }
 void set_pdl_enabled(bool enabled) { g_pdl_enabled = enabled; }
 bool fuse_small_rows_enabled() { return g_fuse_small_rows; }
@@ -391,6 +395,8 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   p.out_type = q.out_type;
   p.group_a = 1;
   p.status = q.status;
+  p.wait_polls = g_wait_polls;
+  p.drop_load_kb = g_drop_load_kb;
 
   const int tiles_x = (p.rows_a + 127) / 128, tiles_y = (p.rows_b + block_n - 1) / block_n;
   const long long tiles = (long long)tiles_x * tiles_y * q.nb0 * q.nb1;

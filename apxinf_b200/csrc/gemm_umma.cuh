@@ -83,6 +83,11 @@ struct GemmParams {
   int mode;
   int out_type;
   int* status;                    // device status word, 0 = ok
+  // Diagnostics of the timeout path (one-CTA-per-tile kernel): the poll budget of every
+  // barrier wait, and a K block whose A load the first CTA announces (expect_tx) but never
+  // issues, so that its stage never fills and the bounded waits run out. -1: none.
+  uint32_t wait_polls;
+  int drop_load_kb;
   // split-K: blockIdx.z = split + split_k * batch; each split owns kb_per_split K blocks,
   // dumps its raw accumulator tile to `partials`, and the last split to arrive on a tile
   // (per-tile arrival counter, left at zero again) sums them in split order and runs the epilogue.
@@ -749,7 +754,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::prefetch_tensormap(&tmap_b);
       bool ok = true;
       int issued = 0;
+      const bool first_cta = (blockIdx.x | blockIdx.y | blockIdx.z) == 0;
       auto load_a = [&](int it) {
+        if (first_cta && it == p.drop_load_kb) return;
         const int s = it % STAGES;
         if (p.blocked_a) {
           ptx::tma_load_4d(smem + s * kStageBytes, &tmap_a, &full_bar[s], 0, tile_a * kTileRowsA,
@@ -793,7 +800,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int it = first_fill; it < my_kb && ok; ++it) {
         const int s = it % STAGES;
         const uint32_t round = it / STAGES;
-        ok = ptx::mbar_wait(&empty_bar[s], (round - 1) & 1);
+        ok = ptx::mbar_wait(&empty_bar[s], (round - 1) & 1, p.wait_polls);
         if (!ok) break;
         ptx::mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
         load_a(it);
@@ -805,7 +812,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // let copies already in flight land before the CTA retires
         const int first = issued > STAGES ? issued - STAGES : 0;
         for (int it = first; it < issued; ++it) {
-          ptx::mbar_wait(&full_bar[it % STAGES], (it / STAGES) & 1);
+          ptx::mbar_wait(&full_bar[it % STAGES], (it / STAGES) & 1, p.wait_polls);
         }
       }
     }
@@ -816,7 +823,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int kb = 0; kb < my_kb; ++kb) {
         const int s = kb % STAGES;
-        ok = ptx::mbar_wait(&full_bar[s], (kb / STAGES) & 1);
+        ok = ptx::mbar_wait(&full_bar[s], (kb / STAGES) & 1, p.wait_polls);
         if (!ok) break;
         ptx::tc_fence_after();
         const uint32_t a_addr = ptx::smem_u32(smem + s * kStageBytes);
@@ -879,7 +886,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
 
-    const bool ok = ptx::mbar_wait(accum_bar, 0);
+    const bool ok = ptx::mbar_wait(accum_bar, 0, p.wait_polls);
     if (!ok && lane == 0) atomicCAS(p.status, 0, kGemmTimeoutEpilogue);
     ptx::tc_fence_after();
     const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);

@@ -23,6 +23,11 @@ void set_pdl_enabled(bool enabled);
 // fused register-streaming launches; off, they plan the same launch list as larger batches.
 bool fuse_small_rows_enabled();
 void set_fuse_small_rows_enabled(bool enabled);
+// Diagnostics of the device-timeout path, read when a GEMM plan is built: the poll budget of the
+// one-CTA-per-tile kernel's barrier waits (<= 0: the default), and a K block whose A load the
+// first CTA announces but never issues (-1: none).
+void set_wait_polls(int polls);
+void set_drop_load_kb(int kb);
 
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

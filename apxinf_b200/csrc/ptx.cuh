@@ -70,9 +70,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait. Returns false if the phase never completed.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+// Bounded wait. Returns false if the phase never completed within `limit` polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   return false;

@@ -122,7 +122,8 @@ __global__ void norm_rows_kernel(NormArgs a) {
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        y[i] = KIND == kNormLayer ? (x[i] - mean) * inv * w[i] + b[i] : x[i] * inv * w[i];
+        // operand order of the reference's layer_norm kernel (normalization.cuh:117-121)
+        y[i] = KIND == kNormLayer ? w[i] * (x[i] - mean) * inv + b[i] : x[i] * inv * w[i];
       }
     }
   } else {

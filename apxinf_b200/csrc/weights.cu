@@ -72,13 +72,17 @@ __global__ void normal_fill_kernel(__nv_bfloat16* dst, uint64_t key, uint64_t of
   }
 }
 
-__global__ void transpose_pack_kernel(const __nv_bfloat16* src, __nv_bfloat16* dst, int k, int n,
+__device__ __forceinline__ float widen(float v) { return v; }
+__device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__global__ void transpose_pack_kernel(const T* src, T* dst, int k, int n,
                                       long long ldk, int row_offset, int interleave, int slot) {
-  __shared__ __nv_bfloat16 tile[32][33];
+  __shared__ T tile[32][33];
   const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
     const int kk = k0 + r, nn = n0 + threadIdx.x;
-    tile[r][threadIdx.x] = (kk < k && nn < n) ? src[(long long)kk * n + nn] : __float2bfloat16(0.0f);
+    tile[r][threadIdx.x] = (kk < k && nn < n) ? src[(long long)kk * n + nn] : T(0.0f);
   }
   __syncthreads();
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
@@ -100,15 +104,15 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return r;
 }
 
-template <bool INT8>
-__global__ void quantize_weight_rows_kernel(const __nv_bfloat16* src, uint8_t* dst, float* scales,
+template <bool INT8, typename T>
+__global__ void quantize_weight_rows_kernel(const T* src, uint8_t* dst, float* scales,
                                             int cols, long long ld) {
   __shared__ float scratch[32];
   const int row = blockIdx.x;
-  const __nv_bfloat16* in = src + (long long)row * ld;
+  const T* in = src + (long long)row * ld;
   uint8_t* out = dst + (long long)row * ld;
   float amax = 0.0f;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) amax = fmaxf(amax, fabsf(__bfloat162float(in[c])));
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) amax = fmaxf(amax, fabsf(widen(in[c])));
   amax = block_max(amax, scratch);
   float scale;
   if (INT8) {
@@ -119,7 +123,7 @@ __global__ void quantize_weight_rows_kernel(const __nv_bfloat16* src, uint8_t* d
   if (threadIdx.x == 0) scales[row] = scale;
   const float inverse = __fdiv_rn(1.0f, scale);
   for (int c = threadIdx.x; c < ld; c += blockDim.x) {
-    const float w = c < cols ? __bfloat162float(in[c]) : 0.0f;
+    const float w = c < cols ? widen(in[c]) : 0.0f;
     if (INT8) {
       const float q = fminf(127.0f, fmaxf(-128.0f, roundf(__fdiv_rn(w, scale))));
       out[c] = static_cast<uint8_t>(static_cast<int8_t>(static_cast<int>(q)));
@@ -130,7 +134,25 @@ __global__ void quantize_weight_rows_kernel(const __nv_bfloat16* src, uint8_t* d
   }
 }
 
+__global__ void convert_kernel(const void* src, void* dst, long long count, int to_f32) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+    if (to_f32) {
+      static_cast<float*>(dst)[i] = __bfloat162float(static_cast<const __nv_bfloat16*>(src)[i]);
+    } else {
+      static_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(static_cast<const float*>(src)[i]);
+    }
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_convert(const void* src, void* dst, long long count, int to_f32, cudaStream_t stream) {
+  if (src == nullptr || dst == nullptr || count <= 0) return cudaErrorInvalidValue;
+  const int blocks = static_cast<int>(std::min<long long>((count + 255) / 256, 148 * 16));
+  convert_kernel<<<blocks, 256, 0, stream>>>(src, dst, count, to_f32);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_lcg_fill(void* dst_bf16, uint64_t seed, uint64_t offset, long long count,
                             cudaStream_t stream) {
@@ -153,30 +175,40 @@ cudaError_t launch_normal_fill(void* dst_bf16, uint64_t seed, uint64_t offset, l
 }
 
 cudaError_t launch_transpose_pack(const void* src, void* dst, int k, int n, long long ldk,
-                                  int row_offset, int interleave, int slot, cudaStream_t stream) {
+                                  int row_offset, int interleave, int slot, cudaStream_t stream,
+                                  int f32) {
   if (src == nullptr || dst == nullptr || k <= 0 || n <= 0 || ldk < k) return cudaErrorInvalidValue;
   if (interleave && (n % 64 != 0)) return cudaErrorInvalidValue;
   dim3 grid((n + 31) / 32, (k + 31) / 32);
-  transpose_pack_kernel<<<grid, dim3(32, 8), 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(src), reinterpret_cast<__nv_bfloat16*>(dst), k, n, ldk,
-      row_offset, interleave, slot);
+  if (f32) {
+    transpose_pack_kernel<float><<<grid, dim3(32, 8), 0, stream>>>(
+        reinterpret_cast<const float*>(src), reinterpret_cast<float*>(dst), k, n, ldk, row_offset,
+        interleave, slot);
+  } else {
+    transpose_pack_kernel<__nv_bfloat16><<<grid, dim3(32, 8), 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(src), reinterpret_cast<__nv_bfloat16*>(dst), k, n, ldk,
+        row_offset, interleave, slot);
+  }
   return cudaGetLastError();
 }
 
-cudaError_t launch_quantize_weight_rows(const void* src_bf16, void* dst, float* scales, int rows,
-                                        int cols, long long ld, int to_int8, cudaStream_t stream) {
-  if (src_bf16 == nullptr || dst == nullptr || scales == nullptr || rows <= 0 || cols <= 0 ||
-      ld < cols) {
+cudaError_t launch_quantize_weight_rows(const void* src, void* dst, float* scales, int rows,
+                                        int cols, long long ld, int to_int8, cudaStream_t stream,
+                                        int f32) {
+  if (src == nullptr || dst == nullptr || scales == nullptr || rows <= 0 || cols <= 0 || ld < cols) {
     return cudaErrorInvalidValue;
   }
-  if (to_int8) {
-    quantize_weight_rows_kernel<true><<<rows, 256, 0, stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(src_bf16), reinterpret_cast<uint8_t*>(dst), scales,
-        cols, ld);
+  auto* out = reinterpret_cast<uint8_t*>(dst);
+  auto* narrow = reinterpret_cast<const __nv_bfloat16*>(src);
+  auto* wide = reinterpret_cast<const float*>(src);
+  if (to_int8 && f32) {
+    quantize_weight_rows_kernel<true, float><<<rows, 256, 0, stream>>>(wide, out, scales, cols, ld);
+  } else if (to_int8) {
+    quantize_weight_rows_kernel<true, __nv_bfloat16><<<rows, 256, 0, stream>>>(narrow, out, scales, cols, ld);
+  } else if (f32) {
+    quantize_weight_rows_kernel<false, float><<<rows, 256, 0, stream>>>(wide, out, scales, cols, ld);
   } else {
-    quantize_weight_rows_kernel<false><<<rows, 256, 0, stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(src_bf16), reinterpret_cast<uint8_t*>(dst), scales,
-        cols, ld);
+    quantize_weight_rows_kernel<false, __nv_bfloat16><<<rows, 256, 0, stream>>>(narrow, out, scales, cols, ld);
   }
   return cudaGetLastError();
 }

@@ -21,18 +21,24 @@ cudaError_t launch_lcg_fill(void* dst_bf16, uint64_t seed, uint64_t offset, long
 cudaError_t launch_normal_fill(void* dst_bf16, uint64_t seed, uint64_t offset, long long count,
                                cudaStream_t stream);
 
-// src bf16 [k, n] row-major  ->  dst bf16 [*, ldk] rows map(n), columns 0..k-1.
+// bf16 -> f32 (to_f32 != 0) or f32 -> bf16 with round-to-nearest-even, element by element.
+cudaError_t launch_convert(const void* src, void* dst, long long count, int to_f32, cudaStream_t stream);
+
+// src [k, n] row-major  ->  dst [*, ldk] rows map(n), columns 0..k-1; both bf16, or both f32
+// when f32 != 0.
 // map(n) = row_offset + n, or with interleave != 0:
 //          (n / 64) * 128 + slot * 64 + n % 64   (gate/up interleave for fused GeGLU).
 cudaError_t launch_transpose_pack(const void* src, void* dst, int k, int n, long long ldk,
-                                  int row_offset, int interleave, int slot, cudaStream_t stream);
+                                  int row_offset, int interleave, int slot, cudaStream_t stream,
+                                  int f32 = 0);
 
-// Per-row (= per output channel) quantisation of a bf16 [rows, ld] matrix.
+// Per-row (= per output channel) quantisation of a bf16 (f32 when f32 != 0) [rows, ld] matrix.
 // E4M3: scale = absmax/448 (1 if the row is zero), q = e4m3(w * (1/scale))
 //       (crates/apxinf-model/src/pi05/fp8.rs:88-115).
 // INT8: scale = max(absmax/127, 1e-12), q = clamp(round_half_away(w/scale), -128, 127)
 //       (crates/apxinf-model/src/pi05/int8_weights.rs:92-123).
-cudaError_t launch_quantize_weight_rows(const void* src_bf16, void* dst, float* scales, int rows,
-                                        int cols, long long ld, int to_int8, cudaStream_t stream);
+cudaError_t launch_quantize_weight_rows(const void* src, void* dst, float* scales, int rows,
+                                        int cols, long long ld, int to_int8, cudaStream_t stream,
+                                        int f32 = 0);
 
 }  // namespace pi05

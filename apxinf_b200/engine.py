@@ -18,7 +18,7 @@ from typing import Dict, List, Optional
 import numpy as np
 
 from . import _lib
-from ._abi_decls import EngineOptions, Gemma, ModelConfig
+from ._abi_decls import EngineOptions, Gemma, HostTensor, ModelConfig, Observation, Signature
 from ._lib import check, lib
 
 DTYPES = {"bf16": 0, "fp8": 1, "int8": 2, "w8a8": 2}
@@ -213,6 +213,16 @@ class CapturedGraph:
                                            C.byref(size)), f"pi05_graph_read_tensor({name})")
         return out
 
+    def signature(self, name: str) -> Dict[str, object]:
+        """Statistics of a named bf16 intermediate of the last run: the per-stage line of the
+        reference's integrity probe (crates/apxinf-model/examples/pi05_integrity_probe.rs:19-51)."""
+        sig = Signature()
+        check(lib().pi05_graph_signature(self._h, name.encode(), C.byref(sig)),
+              f"pi05_graph_signature({name})")
+        return {"elements": int(sig.elements), "sum": sig.sum, "abs_checksum": sig.abs_checksum,
+                "l2": sig.l2, "max_abs": sig.max_abs,
+                "sample": np.array(sig.sample[:sig.sample_count], dtype=np.float32)}
+
     def update_patch_inputs(self, patches, token_ids, noise) -> None:
         """For graphs captured with `capture_infer_patches`: patches float32
         [batch, views * patches_per_view, 3 * patch_size**2] (VisionObservation::Patches,
@@ -280,6 +290,43 @@ class Pi05Runtime:
             runtime.set_activation_scale(site, scale)
         return runtime
 
+    @classmethod
+    def from_tensors(cls, config, tensors, dtype: str = "bf16", device: int = 0,
+                     fp8_act_scale: float = 1.0, int8_activations: str = "dynamic",
+                     activation_scales: Optional[Dict[str, float]] = None) -> "Pi05Runtime":
+        """Weights from host arrays instead of the generator: what the reference builds from a
+        checkpoint (Static*Pi05Weights::from_host over Pi05Weights::from_map). `tensors` maps
+        the synthetic layout's names to uint16 (bf16 bits) or float32 arrays, linear weights
+        [in, out]; apxinf_b200.checkpoint.tensor_table produces it."""
+        config = Pi05Config.from_any(config)
+        if dtype not in DTYPES:
+            raise ValueError(f"--dtype must be bf16, fp8 or int8, got {dtype}")
+        keep, table = [], (HostTensor * len(tensors))()
+        for slot, (name, value) in zip(table, tensors.items()):
+            array = value if isinstance(value, np.ndarray) else value.data
+            if array.dtype not in (np.uint16, np.float32):
+                raise ValueError(f"tensor `{name}` must be uint16 (bf16 bits) or float32, got {array.dtype}")
+            array = np.ascontiguousarray(array)
+            keep.append(array)
+            slot.name = name.encode()
+            slot.data = array.ctypes.data
+            slot.elements = array.size
+            slot.dtype = 1 if array.dtype == np.float32 else 0
+        c = config.to_c()
+        options = EngineOptions(dtype=DTYPES[dtype], device=device, seed=0, act_scale=fp8_act_scale,
+                                weight_dist=0, int8_activations=INT8_ACTIVATIONS[int8_activations])
+        handle = C.c_void_p()
+        code = lib().pi05_engine_create_from_tensors(C.byref(c), C.byref(options), table, len(tensors),
+                                                     C.byref(handle))
+        if code != 0:
+            # the library names a missing or mis-sized tensor in its message
+            detail = (lib().pi05_last_cuda_error() or b"").decode()
+            raise _lib.Pi05Error(code, "pi05_engine_create_from_tensors", detail)
+        runtime = cls(config, "int8" if dtype == "w8a8" else dtype, handle.value, device)
+        for site, scale in (activation_scales or {}).items():
+            runtime.set_activation_scale(site, scale)
+        return runtime
+
     def set_activation_scale(self, site: str, scale: float) -> None:
         """Static activation scale of one GEMM-input site (reference calibration names,
         crates/apxinf-model/src/pi05/runtime.rs:35-81); applies to graphs captured afterwards."""
@@ -322,3 +369,69 @@ class Pi05Runtime:
         check(lib().pi05_engine_capture(self._h, token_count, 2, batch, C.byref(handle)),
               "pi05_engine_capture")
         return CapturedGraph(self, handle.value, token_count, "patches", batch)
+
+
+class PolicyRuntime:
+    """The owning frontend over one Pi05Runtime: `infer` keeps one prepared plan keyed by
+    (token count, image layout), rebuilds it when the observation's shape changes and runs
+    eagerly when graph capture is unavailable — Pi05VlaRuntime::infer / prepare
+    (crates/apxinf-model/src/pi05/vla_runtime.rs:393-495). The cache lives in the library
+    (`pi05_runtime_infer`); this class only checks and passes host buffers."""
+
+    def __init__(self, runtime: Pi05Runtime):
+        self.runtime = runtime
+        handle = C.c_void_p()
+        check(lib().pi05_runtime_create(runtime._h, C.byref(handle)), "pi05_runtime_create")
+        self._h = handle.value
+
+    def close(self) -> None:
+        if self._h:
+            lib().pi05_runtime_destroy(self._h)
+            self._h = 0
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def infer(self, layout: str, image, token_ids: np.ndarray, noise: np.ndarray) -> np.ndarray:
+        """`layout` "nhwc" | "nchw" (uint8 images) or "patches" (float32 patch rows); `noise`
+        float32 or uint16 bf16 bits [horizon, action_dim]. Returns float32 [horizon, action_dim]."""
+        c = self.runtime.config
+        observation = Observation()
+        observation.token_count = int(token_ids.size)
+        tokens = np.ascontiguousarray(token_ids, dtype=np.uint32)
+        observation.token_ids = tokens.ctypes.data
+        if layout == "patches":
+            image = np.ascontiguousarray(image, dtype=np.float32)
+            expected = c.num_views * c.patches_per_view * 3 * c.patch_size ** 2
+            observation.image_layout = 2
+            observation.patches = image.ctypes.data
+        else:
+            if layout not in LAYOUTS:
+                raise ValueError(f"--image-input must be nhwc or nchw, got {layout}")
+            image = np.ascontiguousarray(image, dtype=np.uint8)
+            expected = c.num_views * c.image_size * c.image_size * 3
+            observation.image_layout = LAYOUTS[layout]
+            observation.images = image.ctypes.data
+        if image.size != expected:
+            raise ValueError(f"observation image has {image.size} elements, expected {expected}")
+        if noise.dtype == np.uint16:
+            observation.noise_dtype = 1
+        else:
+            noise = np.ascontiguousarray(noise, dtype=np.float32)
+            observation.noise_dtype = 0
+        noise = np.ascontiguousarray(noise)
+        if noise.size != c.action_horizon * c.action_dim:
+            raise ValueError(f"noise has {noise.size} elements, expected {c.action_horizon * c.action_dim}")
+        observation.noise = noise.ctypes.data
+        out = np.empty((c.action_horizon, c.action_dim), dtype=np.float32)
+        check(lib().pi05_runtime_infer(self._h, C.byref(observation), out.ctypes.data), "pi05_runtime_infer")
+        return out
+
+    def plan_info(self) -> Dict[str, int]:
+        values = [C.c_int32(0) for _ in range(4)]
+        check(lib().pi05_runtime_plan_info(self._h, *[C.byref(v) for v in values]), "pi05_runtime_plan_info")
+        return {"token_count": values[0].value, "image_layout": values[1].value,
+                "uses_graph": values[2].value, "builds": values[3].value}

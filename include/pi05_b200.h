@@ -269,6 +269,32 @@ typedef struct Pi05EngineOptions {
 } Pi05EngineOptions;
 int pi05_engine_create_ex(const Pi05ModelConfig* config, const Pi05EngineOptions* options,
                           Pi05Engine** out);
+/* The runtime from caller-provided weights instead of the synthetic generator: what the
+ * reference builds from a checkpoint (Pi05Weights::from_map, crates/apxinf-model/src/pi05/
+ * weights.rs:116-244, then Static*Pi05Weights::from_host). Tensors are host bf16 bit patterns
+ * or float32 (the reference's folded Gemma projections are float32: the FP8 and INT8 precisions
+ * quantise them from float32 as the reference does, bf16 storage rounds them to nearest even),
+ * linear weights in the reference's final [in, out] orientation, named as the reference's
+ * synthetic layout orders them: "vision.<i>.{q,k,v,o,fc1,fc2}.{weight,bias}",
+ * "vision.patch_embedding.{weight,bias}", "vision.position_embedding",
+ * "vision.projector.{weight,bias}", "token_embedding", "language.<i>.{q,k,v,o,gate,up,down}.weight",
+ * "action.<i>.{input_style,post_style}.{weight,bias}", "action.<i>.{q,...,down}.weight",
+ * "action.final_style.*", "action_in.*", "action_out.*", "time_mlp_in.*", "time_mlp_out.*", and
+ * optionally the LayerNorm parameters "vision.<i>.norm1.{weight,bias}", "vision.<i>.norm2.*",
+ * "vision.post_norm.*" (absent = 1 / 0). Packing, quantisation and upload are as for the
+ * synthetic weights. A missing or mis-sized tensor returns PI05_ERR_INVALID_VALUE and names it
+ * in pi05_last_cuda_error(). The host buffers are only read during the call. (apxinf_b200/
+ * checkpoint.py reads safetensors checkpoints into this table.) */
+enum { PI05_TENSOR_BF16 = 0, PI05_TENSOR_F32 = 1 };
+typedef struct Pi05HostTensor {
+  const char* name;
+  const void* data;
+  uint64_t elements;
+  int32_t dtype; /* PI05_TENSOR_* */
+} Pi05HostTensor;
+int pi05_engine_create_from_tensors(const Pi05ModelConfig* config, const Pi05EngineOptions* options,
+                                    const Pi05HostTensor* tensors, int32_t count, Pi05Engine** out);
+
 /* Static activation scale of one GEMM-input site, named as the reference's calibration table
  * (Pi05ActivationScales::from_calibration, crates/apxinf-model/src/pi05/runtime.rs:35-81):
  * "vision.patch_input", "vision.layers.<i>.attention_norm" / ".attention_output" / ".mlp_norm" /
@@ -326,6 +352,51 @@ const char* pi05_graph_launch_name(const Pi05Graph* graph, int32_t index);
 int pi05_graph_read_tensor(Pi05Graph* graph, const char* name, void* host, size_t capacity,
                            size_t* actual);
 
+/*
+ * Owning frontend (Pi05VlaRuntime / Pi05PreparedInference,
+ * crates/apxinf-model/src/pi05/vla_runtime.rs:393-495): pi05_runtime_infer keeps ONE prepared plan,
+ * keyed by (token_count, image_layout); an observation of another shape drops it and builds
+ * the new one (a workspace is large: two never coexist). Building tries CUDA-graph capture
+ * and falls back to running the same launch list eagerly when capture is unavailable. Noise
+ * given as float32 is rounded to the runtime's 16-bit input type on the host. The engine is
+ * borrowed and must outlive the runtime; one host thread at a time.
+ */
+/* Compute capability of a device as major * 10 + minor (100 on B200), -1 when it cannot be
+ * read: the input of the reference's automatic precision policy
+ * (crates/apxinf-model/src/pi05/vla_runtime.rs:628-639). */
+int pi05_device_sm(int32_t device);
+
+enum { PI05_NOISE_F32 = 0, PI05_NOISE_BF16 = 1 };
+typedef struct Pi05Observation {
+  int32_t token_count;
+  int32_t image_layout;       /* PI05_IMAGE_NHWC | PI05_IMAGE_NCHW | PI05_IMAGE_PATCHES */
+  const uint8_t* images;      /* u8 [views, S, S, 3] (or NCHW); unused for patches */
+  const float* patches;       /* f32 [views * patches_per_view, 3 * patch^2] for PI05_IMAGE_PATCHES */
+  const uint32_t* token_ids;  /* [token_count] */
+  const void* noise;          /* [horizon, action_dim] */
+  int32_t noise_dtype;        /* PI05_NOISE_* */
+} Pi05Observation;
+typedef struct Pi05Runtime Pi05Runtime;
+int pi05_runtime_create(Pi05Engine* engine, Pi05Runtime** out);
+void pi05_runtime_destroy(Pi05Runtime* runtime);
+/* infer_host_f32 (vla_runtime.rs:491-494): actions_out float32 [horizon, action_dim] on the host. */
+int pi05_runtime_infer(Pi05Runtime* runtime, const Pi05Observation* observation, float* actions_out);
+/* The cached plan: its shape, whether it replays a CUDA graph (0 = eager fallback) and how many
+ * plans this runtime has built so far. Any out pointer may be NULL. */
+int pi05_runtime_plan_info(const Pi05Runtime* runtime, int32_t* token_count, int32_t* image_layout,
+                           int32_t* uses_graph, int32_t* builds);
+
+/* Signature of a named bf16 intermediate of the last run ("patches", "vision.hidden", "prefix",
+ * "kv.<l>.k", "action.hidden", "state", ...): the statistics the reference's integrity probe
+ * prints per stage (crates/apxinf-model/examples/pi05_integrity_probe.rs:19-51). */
+typedef struct Pi05Signature {
+  uint64_t elements;
+  double sum, abs_checksum, l2, max_abs;
+  int32_t sample_count;  /* min(elements, 256) evenly spaced values */
+  float sample[256];
+} Pi05Signature;
+int pi05_graph_signature(Pi05Graph* graph, const char* name, Pi05Signature* out);
+
 /* Process-wide planning switches, for A/B measurements and tests; they apply to graphs captured
  * afterwards. "programmatic_dependent_launch" (default 1): launches carry the programmatic
  * stream-serialisation attribute. "fuse_small_rows" (default 1): graphs whose action expert has
@@ -333,7 +404,15 @@ int pi05_graph_read_tensor(Pi05Graph* graph, const char* name, void* host, size_
  * fused in; 0 plans the launch list larger batches use. "attention_cluster" (default 1):
  * key-split attention requests (few query rows) run as one launch of 8-CTA clusters that merge
  * their slices through distributed shared memory; 0 keeps the two-launch form with scratch.
- * Unknown names: PI05_ERR_INVALID_VALUE. */
+ * "wait_limit_polls" (default 0 = 2^24) and "drop_one_load" (default -1 = none) exercise the
+ * device-timeout contract without a fault: GEMM plans built afterwards give every barrier wait of
+ * the one-CTA-per-tile kernel that poll budget, and their first CTA announces the A load of that
+ * K block but never issues it, so the stage never fills, the bounded waits run out, the kernel
+ * records its status word, releases its TMEM and returns; the caller sees PI05_ERR_DEVICE_TIMEOUT
+ * at the next sync and the context stays usable.
+ * "force_capture_failure" (default 0): plans built by pi05_runtime_infer skip graph capture, as
+ * if the driver had refused it (exercises the eager fallback). Unknown names:
+ * PI05_ERR_INVALID_VALUE. */
 int pi05_set_tuning(const char* name, int32_t value);
 
 /* Last CUDA runtime error string seen by this library on the calling thread. */

@@ -475,6 +475,38 @@ class SyntheticWeights:
         return np.concatenate([self.get(n + ".bias") for n in names])
 
 
+class TableWeights:
+    """The same accessors over a name -> array table (what a checkpoint loader produces):
+    float32 arrays holding the values the runtime is given, linear weights [in, out]."""
+
+    def __init__(self, cfg: Pi05Config, table: Dict[str, np.ndarray]):
+        self.cfg = cfg
+        self.table = {k: np.asarray(v, dtype=F32) for k, v in table.items()}
+        self.layout = {k: (0, v.shape) for k, v in self.table.items()}
+
+    def get(self, name: str) -> np.ndarray:
+        """Linear weights stay as given (the quantised precisions read them as float32);
+        everything else is stored as bf16 by the runtime."""
+        value = self.table[name]
+        return value if (name.endswith(".weight") and value.ndim == 2) else round_bf16(value)
+
+    def rows(self, name: str, row_ids) -> np.ndarray:
+        return round_bf16(self.table[name][np.asarray(list(row_ids), dtype=np.int64)])
+
+    def packed(self, names) -> np.ndarray:
+        return np.concatenate([self.get(n + ".weight") for n in names], axis=1)
+
+    def packed_bias(self, names) -> Optional[np.ndarray]:
+        if (names[0] + ".bias") not in self.table:
+            return None
+        return np.concatenate([self.get(n + ".bias") for n in names])
+
+    def layer_norm(self, name: str):
+        if (name + ".weight") not in self.table:
+            return None
+        return round_bf16(self.table[name + ".weight"]), round_bf16(self.table[name + ".bias"])
+
+
 # ----------------------------------------------------------------------------
 # inputs of the bench / tests
 # ----------------------------------------------------------------------------
@@ -593,7 +625,7 @@ class Pi05Oracle:
             return self._prepared[key]
         w = self.w.packed(names)
         if self.o.dtype == "bf16":
-            prepared = (w, None)
+            prepared = (round_bf16(w), None)  # float32 (folded) checkpoint weights are stored as bf16
         elif self.o.dtype == "fp8":
             prepared = quantize_e4m3_channels(w, self.o.fp8_weight_scale)
         else:
@@ -642,12 +674,19 @@ class Pi05Oracle:
         return self.w.packed_bias(names)
 
     # ---- row ops -----------------------------------------------------------
-    def layer_norm(self, x):
+    def layer_norm(self, x, name: Optional[str] = None):
+        """normalization.cuh:96-122: w * (x - mean) * inv_std + b; synthetic weights have
+        gamma 1 / beta 0 (weights.rs:262-263), checkpoint tables carry `<name>.weight/.bias`."""
         eps = F32(self.cfg.layer_norm_eps)
         mean = x.mean(axis=1, dtype=F32, keepdims=True)
         centered = x - mean
         var = (centered * centered).mean(axis=1, dtype=F32, keepdims=True)
-        return (centered * (F32(1.0) / np.sqrt(var + eps))).astype(F32)  # gamma 1, beta 0
+        inv = F32(1.0) / np.sqrt(var + eps)
+        params = self.w.layer_norm(name) if name is not None and hasattr(self.w, "layer_norm") else None
+        if params is None:
+            return (centered * inv).astype(F32)
+        gamma, beta = params
+        return ((gamma[None, :] * centered) * inv + beta[None, :]).astype(F32)
 
     def rms_norm(self, x):
         eps = F32(self.cfg.rms_norm_eps)
@@ -710,7 +749,7 @@ class Pi05Oracle:
         self._keep("vision.embed", x)
         scale = 1.0 / math.sqrt(cfg.vision_head_dim)
         pp, heads, hd = cfg.patches_per_view, cfg.vision_heads, cfg.vision_head_dim
-        n = self.layer_norm(x)
+        n = self.layer_norm(x, "vision.0.norm1" if cfg.vision_depth else "vision.post_norm")
         for i in range(cfg.vision_depth):
             p = f"vision.{i}"
             names = [p + ".q", p + ".k", p + ".v"]
@@ -726,13 +765,13 @@ class Pi05Oracle:
                 attn[rows] = self.attention(q, k, v, scale, self.o.vision_round_scores)
             proj = self.linear(attn, p + ".o", site=f"vision.layers.{i}.attention_output")
             h = rs((proj + x) + self.bias(p + ".o")[None, :])
-            n2 = self.layer_norm(h)
+            n2 = self.layer_norm(h, p + ".norm2")
             f1 = self.linear(n2, p + ".fc1", direct=True, site=f"vision.layers.{i}.mlp_norm")
             act = gelu_tanh(f1 + self.bias(p + ".fc1")[None, :])
             f2 = self.linear(act, p + ".fc2", direct=True, site=f"vision.layers.{i}.mlp_activation")
             x = rs((f2 + h) + self.bias(p + ".fc2")[None, :])
             self._keep(f"vision.{i}.hidden", x)
-            n = self.layer_norm(x)
+            n = self.layer_norm(x, f"vision.{i + 1}.norm1" if i + 1 < cfg.vision_depth else "vision.post_norm")
         proj = self.linear(n, "vision.projector", direct=True, site="vision.post_norm")
         out = rs(proj + self.bias("vision.projector")[None, :])
         self._keep("vision.tokens", out)
