@@ -167,6 +167,14 @@ extern "C" int pi05_set_tuning(const char* name, int32_t value) {
     pi05::set_fuse_small_rows_enabled(value != 0);
   } else if (key == "attention_cluster") {
     pi05::set_fmha_rows_cluster_enabled(value != 0);
+  } else if (key == "fuse_norms") {
+    pi05::set_fuse_norms_enabled(value != 0);
+  } else if (key == "persistent_denoise") {
+    pi05::set_persistent_denoise_enabled(value != 0);
+  } else if (key == "denoise_wait_limit_polls") {
+    pi05::set_denoise_spin_limit(value);
+  } else if (key == "denoise_skip_arrival") {
+    pi05::set_denoise_skip_arrival(value);
   } else if (key == "wait_limit_polls") {
     pi05::set_wait_polls(value);
   } else if (key == "drop_one_load") {

@@ -921,6 +921,29 @@ int PreparedGraph::build(bool measuring) {
   // and epilogue of the velocity head. Seven launches per layer and step (norm, qkv, attention,
   // o, norm, gate_up, down) instead of nine, and three fewer per step.
   const bool fuse_rows = fuse_small_rows_enabled() && Ra <= 16 && ac.width <= 1024 && ac.width % 8 == 0 && c.action_dim % 8 == 0;
+  // ... and the whole loop, all steps and layers, goes into ONE cooperative launch whose stages
+  // are these projections and attentions (denoise_persistent.cuh); the adaptive norms then run
+  // as the staging step of the projection that reads them. Where the launch list does not
+  // qualify (or the device cannot launch cooperatively) the same list runs launch by launch.
+  const bool persistent = fuse_rows && persistent_denoise_enabled() && B_ == 1 &&
+                          (prec == kPrecFp8 || prec == kPrecBf16);
+  // the fused norms need the register-resident staging step: rows x chunks within its budget
+  const bool fused_norms = fuse_rows && (persistent || fuse_norms_enabled()) &&
+                           !(prec == kPrecInt8 && !e_->static_int8()) &&
+                           Ra * (ac.width / 8) <= kSkinnyFastItems * 32 * kSkinnyMaxWarps;
+  const int denoise_stage_capacity = S_ * (2 + 5 * ac.depth);
+  const int denoise_tiles = (H_ * qh + 15) / 16;
+  void* denoise_table = nullptr;
+  unsigned* denoise_zero = nullptr;
+  float* denoise_scratch = nullptr;
+  const size_t denoise_zero_bytes = 256 + static_cast<size_t>(denoise_tiles) * 4;
+  if (persistent) {
+    denoise_table = arena_.alloc(static_cast<size_t>(denoise_stage_capacity) * sizeof(DenoiseStage));
+    denoise_zero = static_cast<unsigned*>(arena_.alloc(denoise_zero_bytes));
+    denoise_scratch = static_cast<float*>(arena_.alloc(static_cast<size_t>(denoise_tiles) * kRowsCluster *
+                                                       rows_partial_floats(hd) * sizeof(float)));
+  }
+  const size_t denoise_first_op = ops_.size();
   // GEMM of <= 16 rows whose bf16 input `src` [Ra, k] is normalised / quantised while staged
   auto fused_problem = [&](const Linear& w, const void* src, int k, int prologue, const void* style,
                            const std::string& site) {
@@ -953,11 +976,14 @@ int PreparedGraph::build(bool measuring) {
         q.ldc = ac.width;
         PI05_TRY(add_gemm("action.in", q));
       }
-      // The two adaRMSNorms of a layer stay launches of their own: as a staging step of the
-      // 80-128 CTAs of the following projection they cost each of those CTAs what the 10-CTA
-      // kernel costs once (measured: 2.5-4 us added to a 3.4 us projection, against about 2 us
-      // for the dependent-launched norm kernel).
-      PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, style_ptr(0, step), c.rms_norm_eps, &na, asite(0, "attention_norm")));
+      // As launches of their own the two adaRMSNorms of a layer stay launches: as a staging step
+      // of the 80-128 CTAs of the following projection they cost each of those CTAs what the
+      // 10-CTA kernel costs once (measured: 2.5-4 us added to a 3.4 us projection, against about
+      // 2 us for the dependent-launched norm kernel). As stages of the persistent kernel they
+      // would each cost a grid barrier, so there they are the projections' staging step.
+      if (!fused_norms) {
+        PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, style_ptr(0, step), c.rms_norm_eps, &na, asite(0, "attention_norm")));
+      }
       for (int l = 0; l < ac.depth; ++l) {
         const Engine::ActionLayer& w = e_->action[l];
         const uint16_t* attn_style = static_cast<const uint16_t*>(style_ptr(2 * l, step));
@@ -966,18 +992,22 @@ int PreparedGraph::build(bool measuring) {
         {
           // q|k|v projection with RoPE, Q rows and the K/V-cache rows written by its epilogue
           GemmProblem q;
-          q.op = op_of(prec);
-          q.M = Ra;
-          q.N = w.qkv.n;
-          q.K = static_cast<int>(std::min<long long>(w.qkv.ldk, na.ld));
-          q.a = GemmOperand{na.data, Ra, na.ld, 0, 0};
-          q.b = GemmOperand{w.qkv.w, w.qkv.n, w.qkv.ldk, 0, 0};
-          q.col_scale = w.qkv.col_scale;
-          q.row_scale = prec == kPrecInt8 && !e_->static_int8() ? na.row_scale : nullptr;
-          q.alpha = e_->static_scales() ? na.scale : 1.0f;
-          q.status = e_->status();
-          q.b_static = true;
-          q.force_skinny = 1;
+          if (fused_norms) {
+            q = fused_problem(w.qkv, ha, ac.width, kProAdaNorm, attn_style, asite(l, "attention_norm"));
+          } else {
+            q.op = op_of(prec);
+            q.M = Ra;
+            q.N = w.qkv.n;
+            q.K = static_cast<int>(std::min<long long>(w.qkv.ldk, na.ld));
+            q.a = GemmOperand{na.data, Ra, na.ld, 0, 0};
+            q.b = GemmOperand{w.qkv.w, w.qkv.n, w.qkv.ldk, 0, 0};
+            q.col_scale = w.qkv.col_scale;
+            q.row_scale = prec == kPrecInt8 && !e_->static_int8() ? na.row_scale : nullptr;
+            q.alpha = e_->static_scales() ? na.scale : 1.0f;
+            q.status = e_->status();
+            q.b_static = true;
+            q.force_skinny = 1;
+          }
           q.out = qkv_a;  // unused by the RoPE epilogue, kept as a valid pointer
           q.ldc = qw + 2 * hd;
           q.mode = kEpiRope;
@@ -998,10 +1028,21 @@ int PreparedGraph::build(bool measuring) {
                            v_cache[l], hd, (long long)cache_rows * hd, 0, H_ * qh, cache_rows, hd, B_, 1, scale_g,
                            logits_a, &attn_a, hd, (long long)H_ * qw, 0));
         PI05_TRY(linear("action.o", attn_a, Ra, w.o, kEpiGateResidual, ha, ac.width, kOutBf16, ha, attn_style + 2 * ac.width, nullptr, 1, 1.0f));
-        PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, mlp_style, c.rms_norm_eps, &na, asite(l, "mlp_norm")));
-        PI05_TRY(linear_to_act("action.gate_up", na, Ra, w.gate_up, kEpiGeglu, &act_a, asite(l, "mlp_activation")));
+        if (fused_norms) {
+          GemmProblem g = fused_problem(w.gate_up, ha, ac.width, kProAdaNorm, mlp_style, asite(l, "mlp_norm"));
+          act_a.scale = e_->scale_of(asite(l, "mlp_activation"));
+          g.out = act_a.data;
+          g.ldc = act_a.ld;
+          g.mode = kEpiGeglu;
+          g.out_type = prec == kPrecBf16 ? kOutBf16 : prec == kPrecFp8 ? kOutE4m3 : kOutS8;
+          g.out_inv_scale = 1.0f / act_a.scale;
+          PI05_TRY(add_gemm("action.gate_up", g));
+        } else {
+          PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, mlp_style, c.rms_norm_eps, &na, asite(l, "mlp_norm")));
+          PI05_TRY(linear_to_act("action.gate_up", na, Ra, w.gate_up, kEpiGeglu, &act_a, asite(l, "mlp_activation")));
+        }
         PI05_TRY(linear("action.down", act_a, Ra, w.down, kEpiGateResidual, ha, ac.width, kOutBf16, ha, mlp_style + 2 * ac.width, nullptr, 1, 1.0f));
-        if (l + 1 < ac.depth) {
+        if (l + 1 < ac.depth && !fused_norms) {
           PI05_TRY(norm_to_act("action.ada_norm", ha, Ra, ac.width, kNormAda, next_style, c.rms_norm_eps, &na, asite(l + 1, "attention_norm")));
         }
       }
@@ -1058,6 +1099,73 @@ int PreparedGraph::build(bool measuring) {
       add_kernel("euler", [=](cudaStream_t s) { return launch_euler(st, velocity, count, dt, s); });
     }
   }
+  if (persistent && !measuring_) {
+    PI05_TRY(fold_denoise(denoise_first_op, denoise_table, denoise_stage_capacity, denoise_zero,
+                          denoise_zero_bytes, denoise_scratch, denoise_tiles));
+  }
+  return kPi05Ok;
+}
+
+// Turns ops_[first, end) — the denoise loop planned as one launch per projection / attention —
+// into the stage table of the persistent kernel and one op that launches it. Leaves the list as
+// it is (every op is a valid launch) when an op is of another kind, a stage wants more CTAs than
+// a cooperative launch may have here, or the table does not fit.
+int PreparedGraph::fold_denoise(size_t first, void* table, int capacity, unsigned* zero_base,
+                                size_t zero_bytes, float* scratch, int tiles) {
+  if (first >= ops_.size()) return kPi05Ok;
+  std::vector<DenoiseStage> stages;
+  int stage_smem = 0, epoch = 0;
+  for (size_t i = first; i < ops_.size(); ++i) {
+    const Op& op = ops_[i];
+    DenoiseStage st{};
+    if (op.is_gemm && op.plan.skinny) {
+      st.kind = op.plan.block_n == 16 ? kStageGemm2 : kStageGemm1;
+      st.ctas = static_cast<int>(op.plan.grid.x);
+      st.threads = op.plan.threads;
+      st.gemm = op.plan.skinny_params;
+      stage_smem = std::max(stage_smem, op.plan.smem_bytes);
+    } else if (op.is_fmha && op.fmha.rows_cluster && op.fmha.key_split) {
+      FmhaRowsParams rows;
+      std::memcpy(&rows, op.fmha.rows_params, sizeof(rows));
+      if (rows.tiles > tiles || static_cast<int>(op.fmha.grid.x) != rows.tiles * kRowsCluster) return kPi05Ok;
+      st.kind = kStageAttention;
+      st.ctas = static_cast<int>(op.fmha.grid.x);
+      st.threads = kRowsThreads;
+      st.epoch = epoch++;
+      st.attention = rows;
+      stage_smem = std::max(stage_smem, op.fmha.rows_smem);
+    } else {
+      return kPi05Ok;
+    }
+    stages.push_back(st);
+  }
+  if (static_cast<int>(stages.size()) > capacity) return kPi05Ok;
+  DenoisePlan plan;
+  plan.op = op_of(e_->precision());
+  plan.smem_bytes = denoise_smem_bytes(stage_smem);
+  plan.grid = denoise_max_grid(plan.op, plan.smem_bytes, e_->device());
+  for (const DenoiseStage& st : stages) {
+    if (st.ctas > plan.grid || st.threads > kDenoiseThreads) return kPi05Ok;
+  }
+  denoise_stages_ = std::move(stages);
+  PI05_CUDA(cudaMemcpyAsync(table, denoise_stages_.data(), denoise_stages_.size() * sizeof(DenoiseStage),
+                            cudaMemcpyHostToDevice, e_->stream()));
+  plan.params.stages = static_cast<const DenoiseStage*>(table);
+  plan.params.count = static_cast<int>(denoise_stages_.size());
+  plan.params.barrier = zero_base;
+  plan.params.tile_flags = zero_base + 64;
+  plan.params.scratch = scratch;
+  plan.params.status = e_->status();
+  plan.params.spin_limit = denoise_spin_limit();
+  plan.params.skip_arrival = denoise_skip_arrival();
+  plan.zero_base = zero_base;
+  plan.zero_bytes = zero_bytes;
+  Op folded;
+  folded.name = "action.denoise";
+  folded.stage = ops_[first].stage;
+  folded.launch = [plan](cudaStream_t s) { return denoise_plan_launch(plan, s); };
+  ops_.erase(ops_.begin() + static_cast<std::ptrdiff_t>(first), ops_.end());
+  ops_.push_back(std::move(folded));
   return kPi05Ok;
 }
 

@@ -19,6 +19,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "denoise_persistent.h"
 #include "fmha.h"
 #include "gemm.h"
 
@@ -159,6 +160,9 @@ class PreparedGraph {
   std::vector<Op> ops_;
   int stage_ = 0;
   bool measuring_ = false;
+  std::vector<DenoiseStage> denoise_stages_;  // host copy of the persistent kernel's stage table
+  int fold_denoise(size_t first, void* table, int capacity, unsigned* zero_base, size_t zero_bytes,
+                   float* scratch, int tiles);
   bool styles_only_ = false;
   cudaGraph_t graph_ = nullptr;
   cudaGraphExec_t exec_ = nullptr;

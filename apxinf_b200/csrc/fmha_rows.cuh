@@ -117,10 +117,32 @@ __device__ __forceinline__ float2 ld_peer_f2(uint32_t address) {
 
 }  // namespace rows_detail
 
-__global__ void __launch_bounds__(kRowsThreads, 1) fmha_rows_cluster_kernel(const FmhaRowsParams p) {
+// The body has two callers. The stand-alone kernel runs it in clusters of 8 CTAs and merges the
+// key slices through distributed shared memory (kCluster). The persistent denoise kernel
+// (denoise_persistent.cuh) runs it as a stage on CTAs 0 .. 8 * tiles - 1 of a cooperative launch
+// without clusters: the eight slices of a tile leave their partials in a global scratch, count
+// themselves on the tile's flag, wait (bounded) for the other seven and merge from L2.
+// `ctx`: cta (slice = cta % 8, tile = cta / 8), tid, sync(), wait() for the producer of Q and the
+// cache rows; without clusters also scratch / flag / target of the tile exchange and the bounded
+// wait `wait_flag(flag, target)`.
+struct RowsLaunchCtx {
+  int cta, tid;
+  __device__ __forceinline__ void sync() const { __syncthreads(); }
+  __device__ __forceinline__ void wait() const { pdl_wait(); }
+  // unused by the cluster merge
+  float* scratch = nullptr;
+  unsigned* flags = nullptr;
+  unsigned target = 0;
+  __device__ __forceinline__ void wait_flag(const unsigned*, unsigned) const {}
+};
+
+// floats one slice leaves in the scratch: the partial output tile, then its row maxima and sums
+__host__ __device__ constexpr int rows_partial_floats(int hd) { return 16 * hd + 32; }
+
+template <bool kCluster, class Ctx>
+__device__ __forceinline__ void fmha_rows_body(const FmhaRowsParams& p, uint8_t* rows_smem, const Ctx& ctx) {
   using namespace rows_detail;
-  pdl_launch_dependents();
-  extern __shared__ __align__(128) uint8_t rows_smem[];
+  const int tid = ctx.tid;
   const int hd = p.head_dim;
   const int qs = rows_q_stride(hd), vs = rows_v_stride(hd);
   const int kc = p.slice_keys;
@@ -134,10 +156,10 @@ __global__ void __launch_bounds__(kRowsThreads, 1) fmha_rows_cluster_kernel(cons
   float* s_m = s_sum + kRowsWarps * 16;           // [16] slice maximum (unscaled scores)
   float* s_l = s_m + 16;                          // [16] slice sum relative to s_m
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const uint32_t rank = cluster_rank();
-  const int cluster_id = blockIdx.x / kRowsCluster;
+  const uint32_t rank = static_cast<uint32_t>(ctx.cta % kRowsCluster);  // = %cluster_ctarank in clusters of 8
+  const int cluster_id = ctx.cta / kRowsCluster;
   const int tile = cluster_id % p.tiles;
   const int sample = cluster_id / p.tiles;
   const int row0 = tile * 16;
@@ -145,12 +167,12 @@ __global__ void __launch_bounds__(kRowsThreads, 1) fmha_rows_cluster_kernel(cons
   const int keys_here = max(0, min(kc, p.keys - key0));
   const int chunks = hd / 8;  // 16-byte chunks per row
 
-  pdl_wait();
+  ctx.wait();
 
   // ---- everything this CTA reads, requested at once: Q tile + K slice, then V slice ----
   {
     const __nv_bfloat16* qb = p.q + static_cast<long long>(sample) * p.q_sb1;
-    for (int i = threadIdx.x; i < 16 * chunks; i += kRowsThreads) {
+    for (int i = tid; i < 16 * chunks; i += kRowsThreads) {
       const int r = i / chunks, c = i - r * chunks;
       const int row = row0 + r;
       uint8_t* dst = q_tile + r * qs + c * 16;
@@ -162,7 +184,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) fmha_rows_cluster_kernel(cons
       }
     }
     const __nv_bfloat16* kb = p.k + static_cast<long long>(sample) * p.k_sb1;
-    for (int i = threadIdx.x; i < kc * chunks; i += kRowsThreads) {
+    for (int i = tid; i < kc * chunks; i += kRowsThreads) {
       const int r = i / chunks, c = i - r * chunks;
       uint8_t* dst = k_tile + r * qs + c * 16;
       if (r < keys_here) {
@@ -173,7 +195,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) fmha_rows_cluster_kernel(cons
     }
     cp_async_commit();
     const __nv_bfloat16* vb = p.v + static_cast<long long>(sample) * p.v_sb1;
-    for (int i = threadIdx.x; i < kc * chunks; i += kRowsThreads) {
+    for (int i = tid; i < kc * chunks; i += kRowsThreads) {
       const int r = i / chunks, c = i - r * chunks;
       uint8_t* dst = v_tile + r * vs + c * 16;
       if (r < keys_here) {
@@ -185,7 +207,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) fmha_rows_cluster_kernel(cons
     cp_async_commit();
   }
   cp_async_wait<1>();  // Q and K have landed (this thread's part)
-  __syncthreads();
+  ctx.sync();
 
   // ---- S = Q K^T: warp w takes the 8-key tiles w, w + 8, ... of the slice ----
   const float scale_log2 = p.scale * 1.4426950408889634f;
@@ -228,7 +250,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) fmha_rows_cluster_kernel(cons
     s_max[warp * 16 + g] = local_max[0];
     s_max[warp * 16 + g + 8] = local_max[1];
   }
-  __syncthreads();
+  ctx.sync();
   float row_max[2] = {-3.0e38f, -3.0e38f};
 #pragma unroll
   for (int w = 0; w < kRowsWarps; ++w) {
@@ -265,15 +287,15 @@ __global__ void __launch_bounds__(kRowsThreads, 1) fmha_rows_cluster_kernel(cons
     s_sum[warp * 16 + g + 8] = local_sum[1];
   }
   cp_async_wait<0>();  // V has landed (this thread's part)
-  __syncthreads();
-  if (threadIdx.x < 16) {
+  ctx.sync();
+  if (tid < 16) {
     float total = 0.0f, m = -3.0e38f;
     for (int w = 0; w < kRowsWarps; ++w) {
-      total += s_sum[w * 16 + threadIdx.x];
-      m = fmaxf(m, s_max[w * 16 + threadIdx.x]);
+      total += s_sum[w * 16 + tid];
+      m = fmaxf(m, s_max[w * 16 + tid]);
     }
-    s_m[threadIdx.x] = m;
-    s_l[threadIdx.x] = total;
+    s_m[tid] = m;
+    s_l[tid] = total;
   }
 
   // ---- O = P V: warp w takes the 16-dim pairs of tiles w, w + 8, ... ----
@@ -306,11 +328,33 @@ __global__ void __launch_bounds__(kRowsThreads, 1) fmha_rows_cluster_kernel(cons
   }
 
   // ---- merge the eight slices: this CTA finishes head dims [rank * hd / 8, (rank + 1) * hd / 8) ----
-  cluster_sync();
+  const float* tile_scratch = nullptr;
+  if constexpr (kCluster) {
+    cluster_sync();
+  } else {
+    // partials to the scratch, one arrival per CTA on the tile's flag, bounded wait for all eight
+    ctx.sync();
+    float* mine = ctx.scratch + (static_cast<long long>(cluster_id) * kRowsCluster + rank) * rows_partial_floats(hd);
+    for (int i = tid; i < 16 * hd / 4; i += kRowsThreads) {
+      __stcg(reinterpret_cast<float4*>(mine) + i, reinterpret_cast<const float4*>(o_tile)[i]);
+    }
+    if (tid < 16) {
+      __stcg(mine + 16 * hd + tid, s_m[tid]);
+      __stcg(mine + 16 * hd + 16 + tid, s_l[tid]);
+    }
+    __threadfence();
+    ctx.sync();
+    if (tid == 0) {
+      atomicAdd(ctx.flags + cluster_id, 1u);
+      ctx.wait_flag(ctx.flags + cluster_id, ctx.target);
+    }
+    ctx.sync();
+    tile_scratch = ctx.scratch + static_cast<long long>(cluster_id) * kRowsCluster * rows_partial_floats(hd);
+  }
   {
     const int dims_here = hd / kRowsCluster;     // multiple of 2
     const int pairs = dims_here / 2;
-    for (int item = threadIdx.x; item < 16 * pairs; item += kRowsThreads) {
+    for (int item = tid; item < 16 * pairs; item += kRowsThreads) {
       const int r = item / pairs;
       const int d = static_cast<int>(rank) * dims_here + (item - r * pairs) * 2;
       const int row = row0 + r;
@@ -319,14 +363,26 @@ __global__ void __launch_bounds__(kRowsThreads, 1) fmha_rows_cluster_kernel(cons
       float m_all = -3.0e38f;
 #pragma unroll
       for (int c = 0; c < kRowsCluster; ++c) {
-        m_s[c] = ld_peer_f(peer_address(s_m + r, c));
+        if constexpr (kCluster) {
+          m_s[c] = ld_peer_f(peer_address(s_m + r, c));
+        } else {
+          m_s[c] = __ldcg(tile_scratch + c * rows_partial_floats(hd) + 16 * hd + r);
+        }
         m_all = fmaxf(m_all, m_s[c]);
       }
       float total = 0.0f, o0 = 0.0f, o1 = 0.0f;
 #pragma unroll
       for (int c = 0; c < kRowsCluster; ++c) {
-        const float l = ld_peer_f(peer_address(s_l + r, c));
-        const float2 o = ld_peer_f2(peer_address(o_tile + r * hd + d, c));
+        float l;
+        float2 o;
+        if constexpr (kCluster) {
+          l = ld_peer_f(peer_address(s_l + r, c));
+          o = ld_peer_f2(peer_address(o_tile + r * hd + d, c));
+        } else {
+          const float* part = tile_scratch + c * rows_partial_floats(hd);
+          l = __ldcg(part + 16 * hd + 16 + r);
+          o = __ldcg(reinterpret_cast<const float2*>(part + r * hd + d));
+        }
         const float w = exp2f((m_s[c] - m_all) * scale_log2);
         total = fmaf(w, l, total);
         o0 = fmaf(w, o.x, o0);
@@ -351,7 +407,14 @@ __global__ void __launch_bounds__(kRowsThreads, 1) fmha_rows_cluster_kernel(cons
     }
   }
   // nobody leaves while a peer may still read its partials
-  cluster_sync();
+  if constexpr (kCluster) cluster_sync();
+}
+
+static __global__ void __launch_bounds__(kRowsThreads, 1) fmha_rows_cluster_kernel(const FmhaRowsParams p) {
+  pdl_launch_dependents();
+  extern __shared__ __align__(128) uint8_t rows_smem_base[];
+  const RowsLaunchCtx ctx{static_cast<int>(blockIdx.x), static_cast<int>(threadIdx.x)};
+  fmha_rows_body<true>(p, rows_smem_base, ctx);
 }
 
 }  // namespace pi05

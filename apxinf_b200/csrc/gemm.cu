@@ -21,6 +21,15 @@ bool pdl_enabled() { return g_pdl_enabled; }
 void set_pdl_enabled(bool enabled) { g_pdl_enabled = enabled; }
 bool fuse_small_rows_enabled() { return g_fuse_small_rows; }
 void set_fuse_small_rows_enabled(bool enabled) { g_fuse_small_rows = enabled; }
+namespace {
+// Off: as the staging step of the 80-128 CTAs of the projection that reads it, an adaptive norm
+// costs every one of them about 250 dependent instructions per (row, 8-element chunk) item
+// (measured: 4.8 us added to the q|k|v and gate|up projections of the B=1 action expert, against
+// about 3 us for the 10-CTA norm launch in front of them).
+bool g_fuse_norms = false;
+}
+bool fuse_norms_enabled() { return g_fuse_norms; }
+void set_fuse_norms_enabled(bool enabled) { g_fuse_norms = enabled; }
 
 namespace {
 
@@ -228,9 +237,11 @@ int skinny_plan_build(const GemmProblem& q, GemmPlan* plan) {
   // K over `ksplit` warps (up to four 64-byte steps in flight each), and as many column groups
   // per CTA as keeps the grid near one CTA per SM: the activation staging (and a fused
   // producer) then runs once per 16-64 columns instead of once per 8-16
-  const int ksplit = std::max(1, std::min(kSkinnyMaxWarps, (p.steps + kSkinnyUnroll - 1) / kSkinnyUnroll));
+  int ksplit = std::max(1, std::min(kSkinnyMaxWarps, (p.steps + kSkinnyUnroll - 1) / kSkinnyUnroll));
   const int total_groups = (q.N + 8 * ntw - 1) / (8 * ntw);
   const int groups = std::max(1, std::min(kSkinnyMaxWarps / ksplit, (total_groups + 147) / 148));
+  // a fused producer is spread over the CTA's threads: give it all sixteen warps
+  if (q.prologue != kProNone) ksplit = std::max(ksplit, kSkinnyMaxWarps / groups);
   p.groups = groups;
   p.ksplit = ksplit;
   const int warps = groups * ksplit;

@@ -186,6 +186,8 @@ constexpr int kSkinnyUnroll = 4;      // 64-byte K steps a warp keeps in flight 
 // before the dependency wait (capping CTAs at 8 warps, so that a successor's CTAs always fit
 // beside them, measured 25 % slower: 13.0 against 10.6 ms for the whole B=1 forward).
 constexpr int kSkinnyMaxWarps = 16;
+// (row, 8-element chunk) items a thread may hold in registers through a fused producer
+constexpr int kSkinnyFastItems = 4;
 
 // `raw_stride`: row pitch of the bf16 copy of the producer's input (fused prologues), else 0;
 // `style_bytes`: the adaptive norm's scale | shift vectors (2 K bf16), else 0
@@ -198,13 +200,24 @@ __host__ __device__ constexpr int skinny_smem_bytes(int a_stride, int warps, int
 // A CTA holds `groups` column groups (NTW tiles of 8 packed weight rows each); the `ksplit`
 // warps of a group share its K range. grid.x = ceil(column groups / groups),
 // block = 32 * groups * ksplit. All warps take part in staging the activations.
-template <int OP, int NTW>
-__global__ void __launch_bounds__(32 * kSkinnyMaxWarps)
-gemm_skinny_kernel(const SkinnyParams p) {
+//
+// The body is shared by two callers through `ctx`: the stand-alone kernel below (one launch per
+// projection, ordered by programmatic dependent launch) and the persistent denoise kernel
+// (denoise_persistent.cuh: the same projections as stages of one cooperative launch, ordered
+// by a grid barrier). `ctx` gives the CTA index, the thread index and count of the threads
+// taking part, their barrier, and the wait for the producer of the activations. Everything an
+// earlier stage may have written is read at L2 (ld.global.cg), never through L1.
+struct SkinnyLaunchCtx {
+  int cta, tid, threads;
+  __device__ __forceinline__ void sync() const { __syncthreads(); }
+  __device__ __forceinline__ void wait() const { pdl_wait(); }
+};
+
+template <int OP, int NTW, class Ctx>
+__device__ __forceinline__ void skinny_body(const SkinnyParams& p, uint8_t* skinny_smem, const Ctx& ctx) {
   constexpr int kElem = OP == kOpBf16 ? 2 : 1;
-  pdl_launch_dependents();
-  extern __shared__ __align__(16) uint8_t skinny_smem[];
-  const int warps = blockDim.x >> 5;
+  const int tid = ctx.tid, nthreads = ctx.threads, cta = ctx.cta;
+  const int warps = nthreads >> 5;
   const int ksplit = p.ksplit;
   uint8_t* a_tile = skinny_smem;                                          // [16][a_stride]
   uint32_t* red = reinterpret_cast<uint32_t*>(a_tile + 16 * p.a_stride);  // [warps][NTW][128]
@@ -213,12 +226,12 @@ gemm_skinny_kernel(const SkinnyParams p) {
   float* s_rowscale = s_stat + 16;                                        // [16]
   uint8_t* raw_tile = reinterpret_cast<uint8_t*>(s_rowscale + 16);        // [M][raw_stride] bf16 (prologues)
 
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int group_in_cta = warp / ksplit;
   const int kslice = warp - group_in_cta * ksplit;
-  const int group = blockIdx.x * p.groups + group_in_cta;
+  const int group = cta * p.groups + group_in_cta;
 
   // packed weight rows of this warp's tiles
   int n0[NTW];
@@ -260,16 +273,17 @@ gemm_skinny_kernel(const SkinnyParams p) {
   uint8_t* style_tile = raw_tile + 16 * p.raw_stride;  // [2][K] bf16: scale | shift
   if (p.prologue == kProAdaNorm) {
     const int chunks = (2 * p.K) >> 3;
-    for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
+    for (int i = tid; i < chunks; i += nthreads) {
       *reinterpret_cast<uint4*>(style_tile + i * 16) =
           __ldg(reinterpret_cast<const uint4*>(p.style) + i);
     }
   }
   float pre_scale[NTW], pre_bias[NTW], pre_gate[NTW], pre_cos = 1.0f, pre_sin = 0.0f;
+  int en[NTW];         // output columns of the epilogue item this thread finishes first
+  bool mine = false;   // ... if it has one
   {
-    const int eg = threadIdx.x >> 7, e = threadIdx.x & 127;
-    const int egroup = blockIdx.x * p.groups + eg;
-    int en[NTW];
+    const int eg = tid >> 7, e = tid & 127;
+    const int egroup = cta * p.groups + eg;
     if constexpr (NTW == 2) {
       const int per_block = p.tile_offset / 8;
       const int block = egroup / per_block;
@@ -278,7 +292,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
     } else {
       en[0] = egroup * 8 + (e & 7);
     }
-    const bool mine = eg < p.groups && (e >> 3) < p.M;
+    mine = eg < p.groups && (e >> 3) < p.M;
 #pragma unroll
     for (int j = 0; j < NTW; ++j) {
       const bool in = mine && en[j] < p.N;
@@ -298,35 +312,53 @@ gemm_skinny_kernel(const SkinnyParams p) {
     }
   }
 
-  pdl_wait();
+  ctx.wait();
+
+  // the residual element of the thread's first epilogue item: asked for now, used at the end
+  float pre_extra[NTW];
+#pragma unroll
+  for (int j = 0; j < NTW; ++j) pre_extra[j] = 0.0f;
+  if ((p.mode == kEpiBiasResidual || p.mode == kEpiGateResidual || p.mode == kEpiEuler) && mine &&
+      !out_is_raw(p.out_type)) {
+    const int row = (tid & 127) >> 3;
+#pragma unroll
+    for (int j = 0; j < NTW; ++j) {
+      if (en[j] < p.N) {
+        pre_extra[j] = __bfloat162float(__ldcg(p.residual + static_cast<long long>(row) * p.ldc + en[j]));
+      }
+    }
+  }
 
   // ---- activations -> shared memory in the operand type ----
   {
     // zero the rows beyond M and each row's tail (the weight stream reads zeros there too, but a
     // NaN pattern in stale shared memory times zero would still poison the sum)
     const int words = 16 * p.a_stride / 16;
-    for (int i = threadIdx.x; i < words; i += blockDim.x) {
+    for (int i = tid; i < words; i += nthreads) {
       reinterpret_cast<uint4*>(a_tile)[i] = make_uint4(0, 0, 0, 0);
     }
-    if (threadIdx.x < 16) s_rowscale[threadIdx.x] = 1.0f;
-    // global -> shared copy of the rows, four 16-byte loads in flight per thread
+    if (tid < 16) s_rowscale[tid] = 1.0f;
+    // global -> shared copy of the rows: up to eight 16-byte loads in flight per thread, so the
+    // ten rows of the widest projection (4096 e4m3 = 2560 chunks over 512 threads) cost one L2
+    // round trip, not two
+    constexpr int kCopyDepth = 8;
     auto copy_rows = [&](uint8_t* dst, int dst_stride, int row_bytes, long long src_pitch) {
       const int chunks = row_bytes / 16;
       const int total = p.M * chunks;
       const uint8_t* src = reinterpret_cast<const uint8_t*>(p.a);
-      for (int i0 = threadIdx.x; i0 < total; i0 += 4 * blockDim.x) {
-        uint4 v[4];
+      for (int i0 = tid; i0 < total; i0 += kCopyDepth * nthreads) {
+        uint4 v[kCopyDepth];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i0 + u * blockDim.x;
+        for (int u = 0; u < kCopyDepth; ++u) {
+          const int i = i0 + u * nthreads;
           if (i < total) {
             const int r = i / chunks, c = i - r * chunks;
             v[u] = skinny::ldg_l2(src + r * src_pitch + c * 16);
           }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i0 + u * blockDim.x;
+        for (int u = 0; u < kCopyDepth; ++u) {
+          const int i = i0 + u * nthreads;
           if (i < total) {
             const int r = i / chunks, c = i - r * chunks;
             *reinterpret_cast<uint4*>(dst + r * dst_stride + c * 16) = v[u];
@@ -335,14 +367,83 @@ gemm_skinny_kernel(const SkinnyParams p) {
       }
     };
     if (p.prologue == kProNone) {
-      __syncthreads();  // the zero fill above and the rows below overlap in a_tile
+      ctx.sync();  // the zero fill above and the rows below overlap in a_tile
       copy_rows(a_tile, p.a_stride, p.kbytes, p.lda * kElem);
-      if (p.row_scale != nullptr && threadIdx.x < p.M) s_rowscale[threadIdx.x] = p.row_scale[threadIdx.x];
+      if (p.row_scale != nullptr && tid < p.M) s_rowscale[tid] = __ldcg(p.row_scale + tid);
+    } else if (!(OP == kOpS8 && p.dynamic_rows) && p.M * (p.K >> 3) <= kSkinnyFastItems * nthreads) {
+      // Producer fused into the staging, the short way: every thread keeps its (row, 8-element
+      // chunk) items in registers from the global load to the operand-type store, so a tile costs
+      // one L2 round trip, one barrier (row statistics by shuffles inside 32-chunk segments, the
+      // segments' partials through shared memory, added in a fixed order by every thread that
+      // needs the row) and a few hundred instructions per thread.
+      const int chunks = p.K >> 3;
+      const int items = p.M * chunks;
+      const bool normed = p.prologue == kProAdaNorm || p.prologue == kProRmsNorm;
+      const int seg = chunks >= 32 ? 32 : chunks;
+      const int parts = (chunks + 31) >> 5;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(p.a);
+      uint4 held[kSkinnyFastItems];
+#pragma unroll
+      for (int j = 0; j < kSkinnyFastItems; ++j) {
+        const int item = tid + j * nthreads;
+        held[j] = make_uint4(0, 0, 0, 0);
+        if (item < items) {
+          const int r = item / chunks, c = item - r * chunks;
+          held[j] = skinny::ldg_l2(src + static_cast<long long>(r) * p.lda * 2 + c * 16);
+        }
+      }
+      if (normed) {
+#pragma unroll
+        for (int j = 0; j < kSkinnyFastItems; ++j) {
+          const int item = tid + j * nthreads;
+          if (j * nthreads < items) {  // uniform over the CTA: whole warps take the shuffles
+            float x[8];
+            skinny::unpack8(held[j], x);
+            float sq = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sq += x[e] * x[e];
+            for (int o = seg >> 1; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            const int r = item / chunks, c = item - r * chunks;
+            if (item < items && (c & (seg - 1)) == 0) s_part[r * 16 + (c >> 5)] = sq;
+          }
+        }
+      }
+      ctx.sync();  // statistics partials, the style vectors and the zero fill are in place
+#pragma unroll
+      for (int j = 0; j < kSkinnyFastItems; ++j) {
+        const int item = tid + j * nthreads;
+        if (item < items) {
+          const int r = item / chunks, c = item - r * chunks;
+          float inv = 1.0f;
+          if (normed) {
+            float total = 0.0f;
+            for (int part = 0; part < parts; ++part) total += s_part[r * 16 + part];
+            inv = rsqrtf(total / static_cast<float>(p.K) + p.eps);
+          }
+          float y[8];
+          skinny::unpack8(held[j], y);
+          if (p.prologue == kProAdaNorm) {
+            float sc[8], sh[8];
+            skinny::unpack8(*reinterpret_cast<const uint4*>(style_tile + c * 16), sc);
+            skinny::unpack8(*reinterpret_cast<const uint4*>(style_tile + p.K * 2 + c * 16), sh);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = (y[e] * inv) * (1.0f + sc[e]) + sh[e];
+          } else if (normed) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = y[e] * inv;
+          }
+          if constexpr (OP == kOpS8) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = round_bf16(y[e]);
+          }
+          skinny::store_staged<OP>(a_tile + r * p.a_stride, c, y, p.a_inv_scale);
+        }
+      }
     } else {
       // The producer's bf16 input rows come to shared memory first (one round trip for the whole
       // tile); then one warp per row: statistic by shuffles, transform, operand-type store.
       copy_rows(raw_tile, p.raw_stride, p.K * 2, p.lda * 2);
-      __syncthreads();
+      ctx.sync();
       const int chunks = p.K >> 3;
       const bool normed = p.prologue == kProAdaNorm || p.prologue == kProRmsNorm;
       // Every thread takes (row, 8-element chunk) items, so the ten rows of a tile are spread
@@ -380,7 +481,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
       // items are laid out so that a warp's 32 lanes cover whole segments: padded to a multiple of 32
       const int padded_items = (items + 31) & ~31;
       if (normed) {
-        for (int item = threadIdx.x; item < padded_items; item += blockDim.x) {
+        for (int item = tid; item < padded_items; item += nthreads) {
           float sq = 0.0f;
           const int r = item / chunks, c = item - r * chunks;
           if (item < items) {
@@ -392,16 +493,16 @@ gemm_skinny_kernel(const SkinnyParams p) {
           sq = segment_reduce(sq, false);
           if (item < items && (c & (seg - 1)) == 0) s_part[r * 16 + (c >> 5)] = sq;
         }
-        __syncthreads();
-        if (threadIdx.x < p.M) {
+        ctx.sync();
+        if (tid < p.M) {
           float total = 0.0f;
-          for (int part = 0; part < parts; ++part) total += s_part[threadIdx.x * 16 + part];
-          s_stat[threadIdx.x] = rsqrtf(total / static_cast<float>(p.K) + p.eps);
+          for (int part = 0; part < parts; ++part) total += s_part[tid * 16 + part];
+          s_stat[tid] = rsqrtf(total / static_cast<float>(p.K) + p.eps);
         }
-        __syncthreads();
+        ctx.sync();
       }
       if (OP == kOpS8 && p.dynamic_rows) {
-        for (int item = threadIdx.x; item < padded_items; item += blockDim.x) {
+        for (int item = tid; item < padded_items; item += nthreads) {
           float amax = 0.0f;
           const int r = item / chunks, c = item - r * chunks;
           if (item < items) {
@@ -413,14 +514,14 @@ gemm_skinny_kernel(const SkinnyParams p) {
           amax = segment_reduce(amax, true);
           if (item < items && (c & (seg - 1)) == 0) s_part[r * 16 + (c >> 5)] = amax;
         }
-        __syncthreads();
-        if (threadIdx.x < p.M) {
+        ctx.sync();
+        if (tid < p.M) {
           float amax = 0.0f;
-          for (int part = 0; part < parts; ++part) amax = fmaxf(amax, s_part[threadIdx.x * 16 + part]);
-          s_rowscale[threadIdx.x] = fmaxf(amax / 127.0f, 1.0e-12f);
+          for (int part = 0; part < parts; ++part) amax = fmaxf(amax, s_part[tid * 16 + part]);
+          s_rowscale[tid] = fmaxf(amax / 127.0f, 1.0e-12f);
         }
-        __syncthreads();
-        for (int item = threadIdx.x; item < items; item += blockDim.x) {
+        ctx.sync();
+        for (int item = tid; item < items; item += nthreads) {
           const int r = item / chunks, c = item - r * chunks;
           float y[8];
           transformed(r, c, normed ? s_stat[r] : 1.0f, y);
@@ -434,7 +535,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
           *reinterpret_cast<uint2*>(a_tile + r * p.a_stride + c * 8) = make_uint2(lo, hi);
         }
       } else {
-        for (int item = threadIdx.x; item < items; item += blockDim.x) {
+        for (int item = tid; item < items; item += nthreads) {
           const int r = item / chunks, c = item - r * chunks;
           float y[8];
           transformed(r, c, normed ? s_stat[r] : 1.0f, y);
@@ -442,7 +543,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
         }
       }
     }
-    __syncthreads();
+    ctx.sync();
   }
 
   // ---- main loop: fragments from registers (weights) and shared memory (activations) ----
@@ -478,14 +579,14 @@ gemm_skinny_kernel(const SkinnyParams p) {
     *reinterpret_cast<uint2*>(mine + g * 8 + 2 * t) = make_uint2(acc[j][0], acc[j][1]);
     *reinterpret_cast<uint2*>(mine + (g + 8) * 8 + 2 * t) = make_uint2(acc[j][2], acc[j][3]);
   }
-  __syncthreads();
+  ctx.sync();
   // ---- epilogue: one (row, column of each tile) per thread; 128 per group cover 16 x 8 ----
-  for (int item = threadIdx.x; item < p.groups * 128; item += blockDim.x) {
+  for (int item = tid; item < p.groups * 128; item += nthreads) {
     const int eg = item >> 7, e = item & 127;
     const int row = e >> 3, col = e & 7;
     if (row >= p.M) continue;
     // this item's tiles (the thread's own warp may belong to another group)
-    const int egroup = blockIdx.x * p.groups + eg;
+    const int egroup = cta * p.groups + eg;
     if constexpr (NTW == 2) {
       const int per_block = p.tile_offset / 8;
       const int block = egroup / per_block;
@@ -514,7 +615,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
     if (p.out_type == kOutS32) continue;
 
     const float row_factor = p.alpha * s_rowscale[row];
-    const bool preloaded = item == static_cast<int>(threadIdx.x);
+    const bool preloaded = item == static_cast<int>(tid);
     float bias[NTW], gate[NTW];
 #pragma unroll
     for (int j = 0; j < NTW; ++j) {
@@ -596,7 +697,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
       } else {
         const float extra =
             (p.mode == kEpiBiasResidual || p.mode == kEpiGateResidual || p.mode == kEpiEuler)
-                ? __bfloat162float(p.residual[index])
+                ? (preloaded ? pre_extra[j] : __bfloat162float(__ldcg(p.residual + index)))
                 : 0.0f;
         switch (p.mode) {
           case kEpiBiasGelu: o = gelu_tanh_f(round_bf16(v[j]) + bias[j]); break;
@@ -610,6 +711,16 @@ gemm_skinny_kernel(const SkinnyParams p) {
       store(p.out, index, o);
     }
   }
+}
+
+template <int OP, int NTW>
+__global__ void __launch_bounds__(32 * kSkinnyMaxWarps)
+gemm_skinny_kernel(const SkinnyParams p) {
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) uint8_t skinny_smem_base[];
+  const SkinnyLaunchCtx ctx{static_cast<int>(blockIdx.x), static_cast<int>(threadIdx.x),
+                            static_cast<int>(blockDim.x)};
+  skinny_body<OP, NTW>(p, skinny_smem_base, ctx);
 }
 
 }  // namespace pi05

@@ -23,6 +23,10 @@ void set_pdl_enabled(bool enabled);
 // fused register-streaming launches; off, they plan the same launch list as larger batches.
 bool fuse_small_rows_enabled();
 void set_fuse_small_rows_enabled(bool enabled);
+// With at most 16 action rows: the adaptive RMSNorms as the staging step of the projections
+// that read them, or as launches of their own (default).
+bool fuse_norms_enabled();
+void set_fuse_norms_enabled(bool enabled);
 // Diagnostics of the device-timeout path, read when a GEMM plan is built: the poll budget of the
 // one-CTA-per-tile kernel's barrier waits (<= 0: the default), and a K block whose A load the
 // first CTA announces but never issues (-1: none).

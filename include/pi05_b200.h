@@ -404,6 +404,15 @@ int pi05_graph_signature(Pi05Graph* graph, const char* name, Pi05Signature* out)
  * fused in; 0 plans the launch list larger batches use. "attention_cluster" (default 1):
  * key-split attention requests (few query rows) run as one launch of 8-CTA clusters that merge
  * their slices through distributed shared memory; 0 keeps the two-launch form with scratch.
+ * "fuse_norms" (default 0): with at most 16 action rows the adaptive RMSNorms run as the staging
+ * step of the projections that read them instead of as launches of their own (measured slower).
+ * "persistent_denoise" (default 0; measured slower than the launches it replaces): BF16 / FP8 graphs of one observation whose action expert has
+ * at most 16 rows run the whole denoise loop (every step, layer, projection and attention) as
+ * the stages of one cooperative launch ordered by a grid barrier; 0 keeps one launch per
+ * projection. "denoise_wait_limit_polls" (default 0 = 2^21): poll budget of that kernel's
+ * barrier waits, after which it records PI05_ERR_DEVICE_TIMEOUT's status and returns.
+ * "denoise_skip_arrival" (default -1 = none): diagnostics of that kernel's timeout path, CTA 0
+ * leaves out its arrival after that stage, so the barrier never completes and every wait runs out.
  * "wait_limit_polls" (default 0 = 2^24) and "drop_one_load" (default -1 = none) exercise the
  * device-timeout contract without a fault: GEMM plans built afterwards give every barrier wait of
  * the one-CTA-per-tile kernel that poll budget, and their first CTA announces the A load of that
