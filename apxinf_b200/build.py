@@ -26,6 +26,9 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-O3,-pthread",
     "--expt-relaxed-constexpr",
 ]
+# extra compiler flags for experiments (e.g. -DNAME, -Xptxas -v); never set for the library that
+# is shipped
+NVCC_FLAGS += os.environ.get("PI05_NVCC_EXTRA", "").split()
 
 
 def _nvcc() -> str:

@@ -170,10 +170,25 @@ __device__ __forceinline__ void fmha_rows_body(const FmhaRowsParams& p, uint8_t*
   ctx.wait();
 
   // ---- everything this CTA reads, requested at once: Q tile + K slice, then V slice ----
+  // (row, 16-byte chunk) items are walked with a fixed row step where the thread count is a
+  // multiple of the chunks per row (every head dimension that is a power of two), so that no
+  // item costs a division: these launches are bound by instructions per warp.
   {
+    const int row_step = kRowsThreads / chunks;
+    const bool regular = row_step * chunks == kRowsThreads;
+    const int first_row = tid / chunks, my_chunk = tid - first_row * chunks;
+    auto for_each_item = [&](int rows, auto&& body) {
+      if (regular) {
+        for (int r = first_row; r < rows; r += row_step) body(r, my_chunk);
+      } else {
+        for (int i = tid; i < rows * chunks; i += kRowsThreads) {
+          const int r = i / chunks;
+          body(r, i - r * chunks);
+        }
+      }
+    };
     const __nv_bfloat16* qb = p.q + static_cast<long long>(sample) * p.q_sb1;
-    for (int i = tid; i < 16 * chunks; i += kRowsThreads) {
-      const int r = i / chunks, c = i - r * chunks;
+    for_each_item(16, [&](int r, int c) {
       const int row = row0 + r;
       uint8_t* dst = q_tile + r * qs + c * 16;
       if (row < p.rows) {
@@ -182,28 +197,26 @@ __device__ __forceinline__ void fmha_rows_body(const FmhaRowsParams& p, uint8_t*
       } else {
         *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
       }
-    }
-    const __nv_bfloat16* kb = p.k + static_cast<long long>(sample) * p.k_sb1;
-    for (int i = tid; i < kc * chunks; i += kRowsThreads) {
-      const int r = i / chunks, c = i - r * chunks;
+    });
+    const __nv_bfloat16* kb = p.k + static_cast<long long>(sample) * p.k_sb1 + static_cast<long long>(key0) * p.k_ld;
+    for_each_item(kc, [&](int r, int c) {
       uint8_t* dst = k_tile + r * qs + c * 16;
       if (r < keys_here) {
-        cp_async16(dst, kb + static_cast<long long>(key0 + r) * p.k_ld + c * 8);
+        cp_async16(dst, kb + static_cast<long long>(r) * p.k_ld + c * 8);
       } else {
         *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
       }
-    }
+    });
     cp_async_commit();
-    const __nv_bfloat16* vb = p.v + static_cast<long long>(sample) * p.v_sb1;
-    for (int i = tid; i < kc * chunks; i += kRowsThreads) {
-      const int r = i / chunks, c = i - r * chunks;
+    const __nv_bfloat16* vb = p.v + static_cast<long long>(sample) * p.v_sb1 + static_cast<long long>(key0) * p.v_ld;
+    for_each_item(kc, [&](int r, int c) {
       uint8_t* dst = v_tile + r * vs + c * 16;
       if (r < keys_here) {
-        cp_async16(dst, vb + static_cast<long long>(key0 + r) * p.v_ld + c * 8);
+        cp_async16(dst, vb + static_cast<long long>(r) * p.v_ld + c * 8);
       } else {
         *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
       }
-    }
+    });
     cp_async_commit();
   }
   cp_async_wait<1>();  // Q and K have landed (this thread's part)

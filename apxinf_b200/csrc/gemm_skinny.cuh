@@ -331,43 +331,59 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, uint8_t* skin
 
   // ---- activations -> shared memory in the operand type ----
   {
-    // zero the rows beyond M and each row's tail (the weight stream reads zeros there too, but a
-    // NaN pattern in stale shared memory times zero would still poison the sum)
-    const int words = 16 * p.a_stride / 16;
-    for (int i = tid; i < words; i += nthreads) {
-      reinterpret_cast<uint4*>(a_tile)[i] = make_uint4(0, 0, 0, 0);
+    // Zero what the main loop reads but nothing below writes: the rows beyond M (a NaN pattern in
+    // stale shared memory times a zero weight would still poison a sum) and, when K does not end
+    // on a 64-byte step, each row's tail. Neither overlaps the rows staged below.
+    {
+      uint4* beyond = reinterpret_cast<uint4*>(a_tile + p.M * p.a_stride);
+      const int words = (16 - p.M) * p.a_stride / 16;
+      for (int i = tid; i < words; i += nthreads) beyond[i] = make_uint4(0, 0, 0, 0);
+      const int tail = p.steps * 4 - p.kbytes / 16;  // 16-byte chunks between K and the last step's end
+      if (tail > 0) {
+        for (int i = tid; i < p.M * tail; i += nthreads) {
+          const int r = i / tail, c = i - r * tail;
+          *reinterpret_cast<uint4*>(a_tile + r * p.a_stride + p.kbytes + c * 16) = make_uint4(0, 0, 0, 0);
+        }
+      }
     }
     if (tid < 16) s_rowscale[tid] = 1.0f;
     // global -> shared copy of the rows: up to eight 16-byte loads in flight per thread, so the
     // ten rows of the widest projection (4096 e4m3 = 2560 chunks over 512 threads) cost one L2
-    // round trip, not two
+    // round trip, not two. (row, chunk) of a thread's items are walked, not divided out: these
+    // launches are bound by the instructions each warp has to get through.
     constexpr int kCopyDepth = 8;
     auto copy_rows = [&](uint8_t* dst, int dst_stride, int row_bytes, long long src_pitch) {
       const int chunks = row_bytes / 16;
       const int total = p.M * chunks;
       const uint8_t* src = reinterpret_cast<const uint8_t*>(p.a);
+      const int dr = nthreads / chunks, dc = nthreads - dr * chunks;  // one stride of the walk
+      int r = tid / chunks, c = tid - r * chunks;
       for (int i0 = tid; i0 < total; i0 += kCopyDepth * nthreads) {
         uint4 v[kCopyDepth];
+        int r0 = r, c0 = c;
 #pragma unroll
         for (int u = 0; u < kCopyDepth; ++u) {
-          const int i = i0 + u * nthreads;
-          if (i < total) {
-            const int r = i / chunks, c = i - r * chunks;
-            v[u] = skinny::ldg_l2(src + r * src_pitch + c * 16);
+          if (i0 + u * nthreads < total) v[u] = skinny::ldg_l2(src + r * src_pitch + c * 16);
+          r += dr;
+          c += dc;
+          if (c >= chunks) {
+            c -= chunks;
+            ++r;
           }
         }
 #pragma unroll
         for (int u = 0; u < kCopyDepth; ++u) {
-          const int i = i0 + u * nthreads;
-          if (i < total) {
-            const int r = i / chunks, c = i - r * chunks;
-            *reinterpret_cast<uint4*>(dst + r * dst_stride + c * 16) = v[u];
+          if (i0 + u * nthreads < total) *reinterpret_cast<uint4*>(dst + r0 * dst_stride + c0 * 16) = v[u];
+          r0 += dr;
+          c0 += dc;
+          if (c0 >= chunks) {
+            c0 -= chunks;
+            ++r0;
           }
         }
       }
     };
     if (p.prologue == kProNone) {
-      ctx.sync();  // the zero fill above and the rows below overlap in a_tile
       copy_rows(a_tile, p.a_stride, p.kbytes, p.lda * kElem);
       if (p.row_scale != nullptr && tid < p.M) s_rowscale[tid] = __ldcg(p.row_scale + tid);
     } else if (!(OP == kOpS8 && p.dynamic_rows) && p.M * (p.K >> 3) <= kSkinnyFastItems * nthreads) {
