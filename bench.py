@@ -64,8 +64,8 @@ UNIT = "action chunks/s"
 # profiles/gemm_umma_persistent_e4m3_gate_up_batch64_dram_traffic.md, together with the git blob
 # id of the kernel source that was profiled: the bench line reports the traffic only while the
 # kernel source is still that one (null otherwise: a stale figure says nothing).
-GATE_UP_DRAM_BYTES_BATCH64 = 276.02e6 + 508.51e6
-GATE_UP_PROFILED_KERNEL_BLOB = "a7b660da6592"  # git hash-object apxinf_b200/csrc/gemm_umma.cuh (first 12)
+GATE_UP_DRAM_BYTES_BATCH64 = 275.2e6 + 506.5e6
+GATE_UP_PROFILED_KERNEL_BLOB = "51caafcfd0f8"  # git hash-object apxinf_b200/csrc/gemm_umma.cuh (first 12)
 
 
 def kernel_source_blob() -> str:
