@@ -105,3 +105,33 @@ def test_static_scratch_wants_a_stream_of_the_current_device():
     with pytest.raises(Pi05Error) as info:
         K.gemm(a, b, out, op=L.OP_BF16, force_split_k=2, static_scratch=True, stream=other)
     assert info.value.code == -1
+
+
+def test_static_scratch_is_capturable_after_the_first_call():
+    """After one eager call per device the entry point neither allocates nor synchronises: it
+    can be captured into a CUDA graph in global capture mode (where an allocation or a
+    synchronising call would fail the capture), and the graph replays to the same result."""
+    from apxinf_b200 import _lib as L, kernels as K
+    gen = torch.Generator().manual_seed(7)
+    M, N, Kd = 24, 512, 2048
+    a = torch.randn(M, Kd, generator=gen).to(torch.bfloat16).cuda()
+    b = (torch.randn(N, Kd, generator=gen) * 0.05).to(torch.bfloat16).cuda()
+    want = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    got = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    status = K.new_status()
+    K.gemm(a, b, want, op=L.OP_BF16, force_split_k=4, static_scratch=True, status=status)  # eager, first
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream, capture_error_mode="global"):
+        K.gemm(a, b, got, op=L.OP_BF16, force_split_k=4, static_scratch=True, status=status)
+    for _ in range(2):
+        got.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        assert torch.equal(got, want)
+    del graph
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after >= free_before - (4 << 20)  # the graph object itself, nothing per call
