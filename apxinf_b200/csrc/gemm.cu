@@ -92,9 +92,14 @@ const void* kernel_ptr(int* smem, int* threads) {
   auto kernel = &gemm_umma_kernel<OP, BLOCK_N, STAGES, SWAP, B_MN, EPI_WARPS>;
   *threads = gemm_threads(EPI_WARPS);
   *smem = gemm_smem_bytes(BLOCK_N, STAGES);
-  // per device, idempotent and cheap: set on every plan build
-  cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                       gemm_smem_bytes(BLOCK_N, STAGES));
+  // per device and kernel, once: plans may be built while a stream of the thread is capturing
+  static bool done[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < 64 && !done[device]) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         gemm_smem_bytes(BLOCK_N, STAGES));
+    done[device] = true;
+  }
   return reinterpret_cast<const void*>(kernel);
 }
 

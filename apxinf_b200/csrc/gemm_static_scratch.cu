@@ -62,7 +62,14 @@ extern "C" int pi05_gemm_static_scratch(const Pi05GemmArgs* args, void* cuda_str
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   // The scratch address is the current device's copy: a stream of another device would run
   // the kernel there with this device's pointer.
-  if (stream != nullptr && stream != cudaStreamLegacy && stream != cudaStreamPerThread) {
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (stream != nullptr && stream != cudaStreamLegacy && stream != cudaStreamPerThread &&
+      cudaStreamIsCapturing(stream, &capturing) != cudaSuccess) {
+    return record_cuda(cudaGetLastError());
+  }
+  // (a capturing stream is not asked for its device: the query is not a capturable call)
+  if (stream != nullptr && stream != cudaStreamLegacy && stream != cudaStreamPerThread &&
+      capturing == cudaStreamCaptureStatusNone) {
     int current = -1, stream_device = -1;
     cudaError_t err = cudaGetDevice(&current);
     if (err == cudaSuccess) err = cudaStreamGetDevice(stream, &stream_device);

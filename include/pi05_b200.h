@@ -159,6 +159,8 @@ int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream);
  *
  * The first call on each device looks up the array's device address (with that device
  * current) and remembers it; make that first call during set-up, before any stream capture.
+ * Later calls may be captured into a CUDA graph (the stream's device is then not checked: a
+ * capturing stream cannot be queried for it).
  * Every call shares the one array and the counters are cleared on the stream before each
  * launch, so two calls that can overlap on the GPU (different streams, or one stream captured
  * into concurrently running graphs) race on it: serialise them on one stream.

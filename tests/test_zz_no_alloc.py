@@ -109,8 +109,9 @@ def test_static_scratch_wants_a_stream_of_the_current_device():
 
 def test_static_scratch_is_capturable_after_the_first_call():
     """After one eager call per device the entry point neither allocates nor synchronises: it
-    can be captured into a CUDA graph in global capture mode (where an allocation or a
-    synchronising call would fail the capture), and the graph replays to the same result."""
+    can be captured into a CUDA graph in thread-local capture mode, the mode the engine captures
+    in (an allocation or a synchronising call by the capturing thread fails the capture), and the
+    graph replays to the same result."""
     from apxinf_b200 import _lib as L, kernels as K
     gen = torch.Generator().manual_seed(7)
     M, N, Kd = 24, 512, 2048
@@ -124,7 +125,7 @@ def test_static_scratch_is_capturable_after_the_first_call():
     free_before, _ = torch.cuda.mem_get_info()
     stream = torch.cuda.Stream()
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=stream, capture_error_mode="global"):
+    with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
         K.gemm(a, b, got, op=L.OP_BF16, force_split_k=4, static_scratch=True, status=status)
     for _ in range(2):
         got.fill_(float("nan"))
