@@ -599,6 +599,7 @@ int PreparedGraph::norm_to_act(const char* name, const void* x, int rows, int co
   a.eps = eps;
   a.inv_scale = 1.0f / out->scale;
   a.kind = kind;
+  a.static_params = 1;  // weights, and the style vectors built once outside the launch list
   const int prec = e_->precision();
   a.out = prec == kPrecBf16 ? kRowBf16
           : prec == kPrecFp8 ? kRowE4m3

@@ -66,12 +66,27 @@ __device__ __forceinline__ float block_reduce(float v, float* scratch) {
 template <int KIND, int OUT>
 __global__ void norm_rows_kernel(NormArgs a) {
   pdl_launch_dependents();
-  pdl_wait();
   __shared__ float scratch[32];
   const int row = blockIdx.x;
   const int vec = threadIdx.x;
   const int nvec = a.cols >> 3;
   const bool active = vec < nvec;
+  // per-column parameters: fetched before the dependency wait when nothing on the stream writes them
+  uint4 pw = make_uint4(0, 0, 0, 0), pb = make_uint4(0, 0, 0, 0);
+  auto fetch_params = [&]() {
+    if (!active) return;
+    if (KIND == kNormAda) {
+      const __nv_bfloat16* style = reinterpret_cast<const __nv_bfloat16*>(a.style);
+      pw = __ldg(reinterpret_cast<const uint4*>(style) + vec);
+      pb = __ldg(reinterpret_cast<const uint4*>(style + a.cols) + vec);
+    } else {
+      if (a.weight != nullptr) pw = __ldg(reinterpret_cast<const uint4*>(a.weight) + vec);
+      if (KIND == kNormLayer && a.bias != nullptr) pb = __ldg(reinterpret_cast<const uint4*>(a.bias) + vec);
+    }
+  };
+  if (a.static_params) fetch_params();
+  pdl_wait();
+  if (!a.static_params) fetch_params();
   const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(a.input) + (long long)row * a.cols;
   float x[8];
   if (active) {
@@ -102,20 +117,19 @@ __global__ void norm_rows_kernel(NormArgs a) {
   if (active) {
     float w[8], b[8];
     if (KIND == kNormAda) {
-      const __nv_bfloat16* style = reinterpret_cast<const __nv_bfloat16*>(a.style);
-      unpack8(reinterpret_cast<const uint4*>(style)[vec], w);
-      unpack8(reinterpret_cast<const uint4*>(style + a.cols)[vec], b);
+      unpack8(pw, w);
+      unpack8(pb, b);
 #pragma unroll
       for (int i = 0; i < 8; ++i) y[i] = (x[i] * inv) * (1.0f + w[i]) + b[i];
     } else {
       if (a.weight != nullptr) {
-        unpack8(reinterpret_cast<const uint4*>(a.weight)[vec], w);
+        unpack8(pw, w);
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) w[i] = 1.0f;
       }
       if (KIND == kNormLayer && a.bias != nullptr) {
-        unpack8(reinterpret_cast<const uint4*>(a.bias)[vec], b);
+        unpack8(pb, b);
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) b[i] = 0.0f;

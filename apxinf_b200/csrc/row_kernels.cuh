@@ -33,6 +33,10 @@ struct NormArgs {
   float eps;
   float inv_scale;      // 1 / activation scale for kRowE4m3 and kRowInt8Static
   int kind, out;
+  // != 0: weight / bias / style are written by no kernel of the stream (the engine computes
+  // its style vectors once, outside the replayed launch list), so they are read ahead of the
+  // programmatic-dependency wait and their round trip overlaps the predecessor's tail
+  int static_params;
 };
 cudaError_t launch_norm(const NormArgs& args, cudaStream_t stream);
 
