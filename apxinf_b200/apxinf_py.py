@@ -104,28 +104,33 @@ class Model:
                calibration: Optional[str] = None, tactics: Optional[str] = None,
                seed: int = 0) -> "Model":
         """Synthetic weights from `seed` (crates/apxinf-py/src/lib.rs:265-343). `calibration` may
-        be "uniform:<scale>" (one FP8 activation scale everywhere); `tactics` is accepted and
-        ignored (there is no tuning database here)."""
+        be "uniform:<scale>" (one FP8 activation scale everywhere) or the path of a calibration
+        json (one scale per named activation site); `tactics` is accepted and ignored (there is
+        no tuning database here)."""
         if model not in ("pi05", "pi0.5"):
             raise ValueError(f"apxinf_py.random: unknown model `{model}`")
         if precision not in _PRECISIONS:
             raise ValueError(f"apxinf_py: unsupported precision `{precision}` "
                              "(expected `bf16`, `fp8` or `int8`)")
         index = _parse_device(device)
-        scale = 1.0
-        if calibration is not None:
-            if not calibration.startswith("uniform:"):
-                raise NotImplementedError("apxinf_py.random: calibration files are not supported; "
-                                          "use `uniform:<scale>`")
+        scale, scales = 1.0, None
+        config = Pi05Config(num_views=num_views, image_size=image_size,
+                            action_horizon=action_horizon, action_dim=action_dim,
+                            num_flow_steps=num_flow_steps, max_token_len=max_token_len)
+        if calibration is not None and calibration.startswith("uniform:"):
             try:
                 scale = float(calibration[len("uniform:"):])
             except ValueError:
                 raise ValueError(f"apxinf_py.random: invalid uniform FP8 scale in `{calibration}`")
-        config = Pi05Config(num_views=num_views, image_size=image_size,
-                            action_horizon=action_horizon, action_dim=action_dim,
-                            num_flow_steps=num_flow_steps, max_token_len=max_token_len)
+        elif calibration is not None:
+            # a calibration json: one scale per named activation site, all of them required
+            try:
+                with open(calibration, "r", encoding="utf-8") as handle:
+                    scales = _checkpoint.calibration_scales(config, _checkpoint.calibration_from_json(handle.read()))
+            except (OSError, _checkpoint.CheckpointError) as error:
+                raise RuntimeError(str(error))
         runtime = Pi05Runtime.random(config, dtype=_PRECISIONS[precision], seed=seed, device=index,
-                                     fp8_act_scale=scale)
+                                     fp8_act_scale=scale, activation_scales=scales)
         return Model(runtime, config, index)
 
     # ---- inference ----------------------------------------------------------------------

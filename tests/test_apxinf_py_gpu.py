@@ -60,3 +60,24 @@ def test_argument_errors(model):
         model.infer_rgb(rgb, "hwc", ids, noise)
     with pytest.raises(ValueError, match=r"patches expected shape \[512, 588\]"):
         model._infer_patches(np.zeros((512, 592), dtype=np.float32), ids, noise)
+
+
+def test_random_model_takes_a_calibration_file(tmp_path):
+    """`calibration` is "uniform:<scale>" or a json with one scale per named activation site
+    (crates/apxinf-py/src/lib.rs:265-343): a file that sets every site to the uniform value gives
+    the same actions bit for bit, a file with a site missing is refused by name."""
+    import json
+    from apxinf_b200 import apxinf_py, checkpoint
+    from apxinf_b200.engine import Pi05Config
+    sites = checkpoint.site_names(Pi05Config())
+    path = tmp_path / "calibration.json"
+    path.write_text(json.dumps({"scales": {name: 0.05 for name in sites}}))
+    by_file = apxinf_py.Model.random("pi05", precision="fp8", calibration=str(path), seed=3)
+    uniform = apxinf_py.Model.random("pi05", precision="fp8", calibration="uniform:0.05", seed=3)
+    rgb, ids, noise = _inputs(uniform, 5)
+    assert np.array_equal(by_file.infer_rgb(rgb, "nhwc", ids, noise), uniform.infer_rgb(rgb, "nhwc", ids, noise))
+    by_file.close()
+    uniform.close()
+    path.write_text(json.dumps({name: 0.05 for name in sites[1:]}))
+    with pytest.raises(RuntimeError, match="missing π0.5 FP8 activation scale `vision.layers.0.attention_norm`"):
+        apxinf_py.Model.random("pi05", precision="fp8", calibration=str(path))
