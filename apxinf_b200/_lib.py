@@ -9,7 +9,9 @@ import ctypes as C
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "libpi05_b200.so"
+# PI05_LIB_PATH: another build of the library (A/B measurements of two builds on one machine)
+import os as _os
+LIB_PATH = Path(_os.environ["PI05_LIB_PATH"]) if _os.environ.get("PI05_LIB_PATH") else _PKG / "libpi05_b200.so"
 
 OP_BF16, OP_E4M3, OP_S8 = 0, 1, 2
 OUT_BF16, OUT_E4M3, OUT_F32, OUT_S32 = 0, 1, 2, 3
