@@ -105,7 +105,12 @@ const void* kernel_ptr(int* smem, int* threads) {
 
 template <int OP, int BLOCK_N, int STAGES, bool B_MN>
 const void* persistent_ptr(int* smem, int* threads) {
-  constexpr int kEpiWarps = 12;  // 3 warps per scheduler hide the TMEM / residual round trips
+  // Eight epilogue warps. Twelve were a gain while the epilogue was bound by TMEM round trips;
+  // measured again on the batched step (three back-to-back pairs on one box: 457.8 / 461.5 /
+  // 465.2 against 455.6 / 461.4 / 460.4 action chunks/s, gate|up at 0.887 against 0.868 of the
+  // tensor peak) and on the B=1 forward (9.75 against 9.79 ms) eight are level or ahead, with
+  // fewer waiting warps to feed under the power cap. Sixteen spill under the register cap.
+  constexpr int kEpiWarps = 8;
   auto kernel = &gemm_umma_persistent_kernel<OP, BLOCK_N, STAGES, B_MN, kEpiWarps>;
   *threads = gemm_threads(kEpiWarps);
   *smem = gemm_smem_bytes(BLOCK_N, STAGES);

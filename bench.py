@@ -61,16 +61,19 @@ UNIT = "action chunks/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one language.gate_up launch at batch 64, from
 # the single-pass ncu capture summarised in
-# profiles/gemm_umma_persistent_e4m3_gate_up_batch64_dram_traffic.md, together with the git blob
-# id of the kernel source that was profiled: the bench line reports the traffic only while the
+# profiles/gemm_umma_persistent_e4m3_gate_up_batch64_dram_traffic.md, together with a digest
+# of the kernel and planner sources that were profiled: the bench line reports the traffic only while the
 # kernel source is still that one (null otherwise: a stale figure says nothing).
-GATE_UP_DRAM_BYTES_BATCH64 = 275.2e6 + 506.5e6
-GATE_UP_PROFILED_KERNEL_BLOB = "51caafcfd0f8"  # git hash-object apxinf_b200/csrc/gemm_umma.cuh (first 12)
+GATE_UP_DRAM_BYTES_BATCH64 = 272.8e6 + 505.1e6
+GATE_UP_PROFILED_KERNEL_BLOB = "cab2bc93b009"  # kernel_source_blob() of the profiled build
 
 
 def kernel_source_blob() -> str:
-    data = (ROOT / "apxinf_b200" / "csrc" / "gemm_umma.cuh").read_bytes()
-    return hashlib.sha1(b"blob %d\0" % len(data) + data).hexdigest()[:12]
+    """Digest of the sources that decide the profiled launch: the kernel and its planner."""
+    h = hashlib.sha1()
+    for name in ("gemm_umma.cuh", "gemm.cu"):
+        h.update((ROOT / "apxinf_b200" / "csrc" / name).read_bytes())
+    return h.hexdigest()[:12]
 
 
 def algorithmic_work(cfg, token_count: int, batch: int, weight_bytes: int):
