@@ -197,8 +197,152 @@ __global__ void norm_rows_kernel(NormArgs a) {
   }
 }
 
+// Many rows (the batched forward: tens of thousands of 1152- or 2048-wide rows): one WARP per
+// row, eight rows per CTA, VPL 16-byte vectors per lane. All of a row's loads are in flight at
+// once, the statistics are warp shuffles (no barrier, no shared memory), and a CTA keeps 18-32 KB
+// of reads in flight instead of 2-4 KB, which is what an HBM-bound row kernel needs on this part.
+// Same arithmetic per element as norm_rows_kernel; only the order of the row sums differs.
+constexpr int kWarpRows = 8;
+
+template <int KIND, int OUT, int VPL>
+__global__ void __launch_bounds__(32 * kWarpRows) norm_rows_warp_kernel(NormArgs a) {
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * kWarpRows + warp;
+  const int nvec = a.cols >> 3;
+  pdl_wait();
+  if (row >= a.rows) return;
+  const uint4* in = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.input) + row * a.cols);
+  float x[VPL][8];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int v = lane + 32 * j;
+    if (v < nvec) {
+      unpack8(in[v], x[j]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[j][i] = 0.0f;
+    }
+  }
+  const float inv_cols = 1.0f / static_cast<float>(a.cols);
+  float mean = 0.0f;
+  if (KIND == kNormLayer) {
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += x[j][i];
+    }
+    mean = warp_sum(s) * inv_cols;
+  }
+  float sq = 0.0f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    if (lane + 32 * j < nvec) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float c = x[j][i] - mean;
+        sq += c * c;
+      }
+    }
+  }
+  const float inv = rsqrtf(warp_sum(sq) * inv_cols + a.eps);
+
+  float amax = 0.0f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int v = lane + 32 * j;
+    if (v < nvec) {
+      float w[8], b[8];
+      if (KIND == kNormAda) {
+        const __nv_bfloat16* style = reinterpret_cast<const __nv_bfloat16*>(a.style);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(style) + v), w);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(style + a.cols) + v), b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[j][i] = (x[j][i] * inv) * (1.0f + w[i]) + b[i];
+      } else {
+        if (a.weight != nullptr) {
+          unpack8(__ldg(reinterpret_cast<const uint4*>(a.weight) + v), w);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w[i] = 1.0f;
+        }
+        if (KIND == kNormLayer && a.bias != nullptr) {
+          unpack8(__ldg(reinterpret_cast<const uint4*>(a.bias) + v), b);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) b[i] = 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          x[j][i] = KIND == kNormLayer ? w[i] * (x[j][i] - mean) * inv + b[i] : x[j][i] * inv * w[i];
+        }
+      }
+      if (OUT == kRowInt8) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          x[j][i] = rb(x[j][i]);
+          amax = fmaxf(amax, fabsf(x[j][i]));
+        }
+      }
+    }
+  }
+  float scale = 1.0f;
+  if (OUT == kRowInt8) {
+    scale = fmaxf(warp_max(amax) / 127.0f, 1.0e-12f);
+    if (lane == 0) a.row_scale[row] = scale;
+  }
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int v = lane + 32 * j;
+    if (v >= nvec) continue;
+    const float(&y)[8] = x[j];
+    if (OUT == kRowBf16) {
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.output) + row * a.cols)[v] = pack8(y);
+    } else {
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (OUT == kRowE4m3) {
+          lo |= static_cast<uint32_t>(e4m3_of(y[i] * a.inv_scale)) << (8 * i);
+          hi |= static_cast<uint32_t>(e4m3_of(y[4 + i] * a.inv_scale)) << (8 * i);
+        } else if (OUT == kRowInt8Static) {
+          lo |= s8_of(rb(y[i]) * a.inv_scale) << (8 * i);
+          hi |= s8_of(rb(y[4 + i]) * a.inv_scale) << (8 * i);
+        } else {
+          const float q0 = fminf(127.0f, fmaxf(-128.0f, roundf(y[i] / scale)));
+          const float q1 = fminf(127.0f, fmaxf(-128.0f, roundf(y[4 + i] / scale)));
+          lo |= (static_cast<uint32_t>(static_cast<int>(q0)) & 0xffu) << (8 * i);
+          hi |= (static_cast<uint32_t>(static_cast<int>(q1)) & 0xffu) << (8 * i);
+        }
+      }
+      reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(a.output) + row * a.cols)[v] = make_uint2(lo, hi);
+    }
+  }
+}
+
+template <int KIND, int OUT>
+cudaError_t launch_norm_warp(const NormArgs& a, cudaStream_t stream) {
+  const int vpl = ((a.cols >> 3) + 31) / 32;
+  const dim3 grid((a.rows + kWarpRows - 1) / kWarpRows), block(32 * kWarpRows);
+  if (vpl <= 4) return launch_pdl(norm_rows_warp_kernel<KIND, OUT, 4>, grid, block, 0, stream, a);
+  if (vpl <= 5) return launch_pdl(norm_rows_warp_kernel<KIND, OUT, 5>, grid, block, 0, stream, a);
+  return launch_pdl(norm_rows_warp_kernel<KIND, OUT, 8>, grid, block, 0, stream, a);
+}
+
 template <int KIND>
 cudaError_t launch_norm_kind(const NormArgs& a, int threads, cudaStream_t stream) {
+  // a warp per row pays once there are rows enough to fill the SMs with such CTAs
+  const bool by_warp = a.rows >= 1024 && (a.cols >> 3) <= 8 * 32;
+  if (by_warp) {
+    switch (a.out) {
+      case kRowBf16: return launch_norm_warp<KIND, kRowBf16>(a, stream);
+      case kRowE4m3: return launch_norm_warp<KIND, kRowE4m3>(a, stream);
+      case kRowInt8: return launch_norm_warp<KIND, kRowInt8>(a, stream);
+      case kRowInt8Static: return launch_norm_warp<KIND, kRowInt8Static>(a, stream);
+      default: return cudaErrorInvalidValue;
+    }
+  }
   switch (a.out) {
     case kRowBf16:
       return launch_pdl(norm_rows_kernel<KIND, kRowBf16>, dim3(a.rows), dim3(threads), 0, stream, a);
