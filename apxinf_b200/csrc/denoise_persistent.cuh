@@ -158,9 +158,9 @@ __global__ void __launch_bounds__(kDenoiseThreads, 1) denoise_persistent_kernel(
     if (cta < st.ctas) {
       if (tid < st.threads) {
         if (st.kind == kStageGemm1) {
-          skinny_body<OP, 1>(st.gemm, work, ctx);
+          skinny_body<OP, 1, true>(st.gemm, work, ctx);
         } else if (st.kind == kStageGemm2) {
-          skinny_body<OP, 2>(st.gemm, work, ctx);
+          skinny_body<OP, 2, true>(st.gemm, work, ctx);
         } else {
           fmha_rows_body<false>(st.attention, work, ctx);
         }

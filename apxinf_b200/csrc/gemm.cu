@@ -160,12 +160,20 @@ const void* select_kernel(int block_n, bool swap, bool b_mn, bool multi_wave, in
 
 namespace {
 
-template <int OP, int NTW>
-const void* skinny_ptr(int /*smem*/) {
-  auto kernel = &gemm_skinny_kernel<OP, NTW>;
+template <int OP, int NTW, bool PRO>
+const void* skinny_ptr_of() {
+  auto kernel = &gemm_skinny_kernel<OP, NTW, PRO>;
   // plans of different K share the kernel: allow the largest tile any of them may ask for
   cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   return reinterpret_cast<const void*>(kernel);
+}
+
+// Launches without a fused producer (nearly all) run a kernel that does not contain that code:
+// measured on the B=1 forward, 9.75 -> 9.58 ms, for no change but a shorter instruction stream.
+template <int OP>
+const void* skinny_ptr(int ntw, bool producer) {
+  if (producer) return ntw == 2 ? skinny_ptr_of<OP, 2, true>() : skinny_ptr_of<OP, 1, true>();
+  return ntw == 2 ? skinny_ptr_of<OP, 2, false>() : skinny_ptr_of<OP, 1, false>();
 }
 
 bool needs_skinny(const GemmProblem& q) {
@@ -259,9 +267,10 @@ int skinny_plan_build(const GemmProblem& q, GemmPlan* plan) {
                                      q.prologue == kProAdaNorm ? q.K * 4 : 0);
   if (smem > 227 * 1024) return kPi05ErrUnsupported;
   const void* kernel = nullptr;
-  if (q.op == kOpBf16) kernel = ntw == 2 ? skinny_ptr<kOpBf16, 2>(smem) : skinny_ptr<kOpBf16, 1>(smem);
-  if (q.op == kOpE4m3) kernel = ntw == 2 ? skinny_ptr<kOpE4m3, 2>(smem) : skinny_ptr<kOpE4m3, 1>(smem);
-  if (q.op == kOpS8) kernel = ntw == 2 ? skinny_ptr<kOpS8, 2>(smem) : skinny_ptr<kOpS8, 1>(smem);
+  const bool producer = q.prologue != kProNone;
+  if (q.op == kOpBf16) kernel = skinny_ptr<kOpBf16>(ntw, producer);
+  if (q.op == kOpE4m3) kernel = skinny_ptr<kOpE4m3>(ntw, producer);
+  if (q.op == kOpS8) kernel = skinny_ptr<kOpS8>(ntw, producer);
   plan->skinny = true;
   plan->kernel = kernel;
   plan->threads = 32 * warps;

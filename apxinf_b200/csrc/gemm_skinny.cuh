@@ -213,9 +213,13 @@ struct SkinnyLaunchCtx {
   __device__ __forceinline__ void wait() const { pdl_wait(); }
 };
 
-template <int OP, int NTW, class Ctx>
+// PRO: the fused producers (prologue != kProNone) are compiled in. The projections without one,
+// which are nearly all launches, run the variant without that code: fewer registers and a
+// shorter instruction stream for launches that are bound by exactly that.
+template <int OP, int NTW, bool PRO, class Ctx>
 __device__ __forceinline__ void skinny_body(const SkinnyParams& p, uint8_t* skinny_smem, const Ctx& ctx) {
   constexpr int kElem = OP == kOpBf16 ? 2 : 1;
+  const int mode = p.mode;  // (a compile-time epilogue on top of PRO measured no further gain)
   const int tid = ctx.tid, nthreads = ctx.threads, cta = ctx.cta;
   const int warps = nthreads >> 5;
   const int ksplit = p.ksplit;
@@ -271,7 +275,7 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, uint8_t* skin
   // (to shared memory) and the per-column scale / bias / gate and RoPE factors of the output
   // element this thread will finish.
   uint8_t* style_tile = raw_tile + 16 * p.raw_stride;  // [2][K] bf16: scale | shift
-  if (p.prologue == kProAdaNorm) {
+  if (PRO && p.prologue == kProAdaNorm) {
     const int chunks = (2 * p.K) >> 3;
     for (int i = tid; i < chunks; i += nthreads) {
       *reinterpret_cast<uint4*>(style_tile + i * 16) =
@@ -300,7 +304,7 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, uint8_t* skin
       pre_bias[j] = p.bias != nullptr && in ? __bfloat162float(p.bias[en[j]]) : 0.0f;
       pre_gate[j] = p.gate != nullptr && in ? __bfloat162float(p.gate[en[j]]) : 0.0f;
     }
-    if (p.mode == kEpiRope && mine && en[0] < p.N) {
+    if (mode == kEpiRope && mine && en[0] < p.N) {
       const int half = p.head_dim >> 1;
       const int head = en[0] / p.head_dim;
       if (head < p.q_heads + 1) {
@@ -318,7 +322,7 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, uint8_t* skin
   float pre_extra[NTW];
 #pragma unroll
   for (int j = 0; j < NTW; ++j) pre_extra[j] = 0.0f;
-  if ((p.mode == kEpiBiasResidual || p.mode == kEpiGateResidual || p.mode == kEpiEuler) && mine &&
+  if ((mode == kEpiBiasResidual || mode == kEpiGateResidual || mode == kEpiEuler) && mine &&
       !out_is_raw(p.out_type)) {
     const int row = (tid & 127) >> 3;
 #pragma unroll
@@ -383,9 +387,11 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, uint8_t* skin
         }
       }
     };
-    if (p.prologue == kProNone) {
+    if (!PRO || p.prologue == kProNone) {
       copy_rows(a_tile, p.a_stride, p.kbytes, p.lda * kElem);
       if (p.row_scale != nullptr && tid < p.M) s_rowscale[tid] = __ldcg(p.row_scale + tid);
+    } else if constexpr (!PRO) {
+      // unreachable: plans with a fused producer take the PRO variant
     } else if (!(OP == kOpS8 && p.dynamic_rows) && p.M * (p.K >> 3) <= kSkinnyFastItems * nthreads) {
       // Producer fused into the staging, the short way: every thread keeps its (row, 8-element
       // chunk) items in registers from the global load to the operand-type store, so a tile costs
@@ -660,7 +666,7 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, uint8_t* skin
         reinterpret_cast<float*>(base)[index] = o;
       }
     };
-    if (p.mode == kEpiGeglu) {
+    if (mode == kEpiGeglu) {
       if constexpr (NTW == 2) {
         const int n = n0[0] + col;  // packed gate row; its feature index is the output column
         if (n < p.N) {
@@ -671,7 +677,7 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, uint8_t* skin
       }
       continue;
     }
-    if (p.mode == kEpiRope) {
+    if (mode == kEpiRope) {
       if constexpr (NTW == 2) {
         // columns n and n + head_dim / 2 of one head: (a, b) -> (a cos - b sin, b cos + a sin)
         const int n = n0[0] + col;
@@ -712,10 +718,10 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, uint8_t* skin
         o = v[j];
       } else {
         const float extra =
-            (p.mode == kEpiBiasResidual || p.mode == kEpiGateResidual || p.mode == kEpiEuler)
+            (mode == kEpiBiasResidual || mode == kEpiGateResidual || mode == kEpiEuler)
                 ? (preloaded ? pre_extra[j] : __bfloat162float(__ldcg(p.residual + index)))
                 : 0.0f;
-        switch (p.mode) {
+        switch (mode) {
           case kEpiBiasGelu: o = gelu_tanh_f(round_bf16(v[j]) + bias[j]); break;
           case kEpiBiasSilu: o = silu_f(round_bf16(v[j]) + bias[j]); break;
           case kEpiBiasResidual: o = (round_bf16(v[j]) + extra) + bias[j]; break;
@@ -729,14 +735,14 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, uint8_t* skin
   }
 }
 
-template <int OP, int NTW>
+template <int OP, int NTW, bool PRO>
 __global__ void __launch_bounds__(32 * kSkinnyMaxWarps)
 gemm_skinny_kernel(const SkinnyParams p) {
   pdl_launch_dependents();
   extern __shared__ __align__(16) uint8_t skinny_smem_base[];
   const SkinnyLaunchCtx ctx{static_cast<int>(blockIdx.x), static_cast<int>(threadIdx.x),
                             static_cast<int>(blockDim.x)};
-  skinny_body<OP, NTW>(p, skinny_smem_base, ctx);
+  skinny_body<OP, NTW, PRO>(p, skinny_smem_base, ctx);
 }
 
 }  // namespace pi05
