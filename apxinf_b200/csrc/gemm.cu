@@ -87,9 +87,9 @@ int encode_operand_map(CUtensorMap* map, int op, const void* ptr, uint64_t inner
 
 namespace {
 
-template <int OP, int BLOCK_N, int STAGES, bool SWAP, bool B_MN, int EPI_WARPS = 8>
+template <int OP, int BLOCK_N, int STAGES, bool SWAP, bool B_MN, int EPI_WARPS = 8, int FIXED_MODE = -1>
 const void* kernel_ptr(int* smem, int* threads) {
-  auto kernel = &gemm_umma_kernel<OP, BLOCK_N, STAGES, SWAP, B_MN, EPI_WARPS>;
+  auto kernel = &gemm_umma_kernel<OP, BLOCK_N, STAGES, SWAP, B_MN, EPI_WARPS, FIXED_MODE>;
   *threads = gemm_threads(EPI_WARPS);
   *smem = gemm_smem_bytes(BLOCK_N, STAGES);
   // per device and kernel, once: plans may be built while a stream of the thread is capturing
@@ -134,8 +134,22 @@ const void* select_persistent(int block_n, bool b_mn, int* smem, int* threads) {
   return nullptr;
 }
 
+// The epilogues that SigLIP and the prefix run in every layer (plain store, bias + GELU, bias +
+// residual) have kernels of their own for the bf16 and FP8 forward, without the other
+// epilogues' code.
+template <int OP, int BLOCK_N, int STAGES>
+const void* plain_ptr(int mode, int* smem, int* threads) {
+  if constexpr (OP == kOpBf16 || OP == kOpE4m3) {
+    if (mode == kEpiStore) return kernel_ptr<OP, BLOCK_N, STAGES, false, false, 8, kEpiStore>(smem, threads);
+    if (mode == kEpiBiasGelu) return kernel_ptr<OP, BLOCK_N, STAGES, false, false, 8, kEpiBiasGelu>(smem, threads);
+    if (mode == kEpiBiasResidual)
+      return kernel_ptr<OP, BLOCK_N, STAGES, false, false, 8, kEpiBiasResidual>(smem, threads);
+  }
+  return kernel_ptr<OP, BLOCK_N, STAGES, false, false>(smem, threads);
+}
+
 template <int OP>
-const void* select_kernel(int block_n, bool swap, bool b_mn, bool multi_wave, int* smem,
+const void* select_kernel(int block_n, bool swap, bool b_mn, bool multi_wave, int mode, int* smem,
                           int* threads) {
   if (b_mn) {
     if constexpr (OP == kOpBf16 || OP == kOpE4m3) {
@@ -150,9 +164,9 @@ const void* select_kernel(int block_n, bool swap, bool b_mn, bool multi_wave, in
     if (block_n == 64) return kernel_ptr<OP, 64, 8, true, false>(smem, threads);
     return nullptr;
   }
-  if (block_n == 64) return kernel_ptr<OP, 64, 8, false, false>(smem, threads);
-  if (block_n == 128) return kernel_ptr<OP, 128, 6, false, false>(smem, threads);
-  if (block_n == 256) return kernel_ptr<OP, 256, 4, false, false>(smem, threads);
+  if (block_n == 64) return plain_ptr<OP, 64, 8>(mode, smem, threads);
+  if (block_n == 128) return plain_ptr<OP, 128, 6>(mode, smem, threads);
+  if (block_n == 256) return plain_ptr<OP, 256, 4>(mode, smem, threads);
   return nullptr;
 }
 
@@ -365,9 +379,9 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   const bool multi_wave = q.force_two_per_sm >= 0 ? q.force_two_per_sm != 0 : tiles_planned > 148;
   int smem = 0, threads = 0;
   const void* kernel = nullptr;
-  if (q.op == kOpBf16) kernel = select_kernel<kOpBf16>(block_n, swap, q.b_mn_major, multi_wave, &smem, &threads);
-  if (q.op == kOpE4m3) kernel = select_kernel<kOpE4m3>(block_n, swap, q.b_mn_major, multi_wave, &smem, &threads);
-  if (q.op == kOpS8) kernel = select_kernel<kOpS8>(block_n, swap, q.b_mn_major, multi_wave, &smem, &threads);
+  if (q.op == kOpBf16) kernel = select_kernel<kOpBf16>(block_n, swap, q.b_mn_major, multi_wave, q.mode, &smem, &threads);
+  if (q.op == kOpE4m3) kernel = select_kernel<kOpE4m3>(block_n, swap, q.b_mn_major, multi_wave, q.mode, &smem, &threads);
+  if (q.op == kOpS8) kernel = select_kernel<kOpS8>(block_n, swap, q.b_mn_major, multi_wave, q.mode, &smem, &threads);
   if (kernel == nullptr) return kPi05ErrUnsupported;
   plan->threads = threads;
   plan->persistent = false;

@@ -686,7 +686,9 @@ __device__ __forceinline__ void epilogue_swapped(const GemmParams& p,
   }
 }
 
-template <int OP, int BLOCK_N, int STAGES, bool SWAP, bool B_MN, int EPI_WARPS>
+// FIXED_MODE >= 0 compiles the kernel for that one epilogue (the launch's p.mode must equal it):
+// the forward's most frequent epilogues get kernels that hold no other epilogue's code.
+template <int OP, int BLOCK_N, int STAGES, bool SWAP, bool B_MN, int EPI_WARPS, int FIXED_MODE = -1>
 __global__ void __launch_bounds__(gemm_threads(EPI_WARPS), EPI_WARPS == 4 ? 2 : 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
@@ -703,6 +705,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr uint32_t kTmemCols = tmem_cols_for(BLOCK_N);
   constexpr uint32_t kIdesc =
       ptx::make_idesc(T::kCFormat, T::kFormat, T::kFormat, 0, B_MN ? 1 : 0, 128, BLOCK_N);
+
+  const int mode = FIXED_MODE >= 0 ? FIXED_MODE : p.mode;
 
   pdl_launch_dependents();
 
@@ -925,7 +929,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     if (!run_epilogue) {
       // another split finishes this tile
-    } else if (p.mode == kEpiGeglu) {
+    } else if (mode == kEpiGeglu) {
       if constexpr (!SWAP) {
         epilogue_geglu_normal<OP, BLOCK_N, kHalves>(p, acc, gi, tile_b, out_base, sr, half, s_scale);
       } else {
@@ -987,7 +991,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     epilogue_normal<OP, BLOCK_N, MODE, kHalves>(p, acc, gi, tile_b, out_base, sr, half, s_scale,  \
                                                 s_bias, s_gate, [] {});                           \
     break;
-      switch (p.mode) {
+      switch (mode) {
         PI05_EPI_CASE(kEpiStore)
         PI05_EPI_CASE(kEpiBiasGelu)
         PI05_EPI_CASE(kEpiBiasSilu)
@@ -1004,7 +1008,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     epilogue_swapped<OP, BLOCK_N, MODE, kHalves>(p, acc, gi, tile_b, out_base, half, sw_scale,   \
                                                  sw_bias, sw_gate, s_scale);                      \
     break;
-      switch (p.mode) {
+      switch (mode) {
         PI05_EPI_CASE(kEpiStore)
         PI05_EPI_CASE(kEpiBiasGelu)
         PI05_EPI_CASE(kEpiBiasSilu)
