@@ -228,6 +228,9 @@ __device__ __forceinline__ uint8_t out_byte(const GemmParams& p, float o) {
   return p.out_type == kOutS8 ? to_s8(round_bf16(o) * p.out_inv_scale)
                               : to_e4m3(o * p.out_inv_scale);
 }
+__device__ __forceinline__ uint8_t out_byte_as(int out_type, const GemmParams& p, float o) {
+  return out_type == kOutS8 ? to_s8(round_bf16(o) * p.out_inv_scale) : to_e4m3(o * p.out_inv_scale);
+}
 
 // outputs that skip the fused epilogue: the scaled accumulator itself
 __device__ __forceinline__ bool out_is_raw(int out_type) { return out_type == kOutF32 || out_type == kOutF16; }
@@ -246,9 +249,11 @@ __device__ __forceinline__ void store_one(const GemmParams& p, long long index, 
 
 // Store 16 consecutive columns of one row; vectorised when the destination is
 // 16-byte aligned and the whole chunk is in range.
+template <int OUT = -1>
 __device__ __forceinline__ void store_chunk16(const GemmParams& p, long long index, int valid,
                                               const float (&o)[16]) {
-  if (p.out_type == kOutBf16) {
+  const int out_type = OUT >= 0 ? OUT : p.out_type;  // OUT >= 0: the one type this kernel writes
+  if (out_type == kOutBf16) {
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + index;
     if (valid == 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
       uint32_t w[8];
@@ -265,22 +270,22 @@ __device__ __forceinline__ void store_chunk16(const GemmParams& p, long long ind
         if (t < valid) dst[t] = __float2bfloat16(o[t]);
       }
     }
-  } else if (out_is_byte(p)) {
+  } else if ((out_type == kOutE4m3 || out_type == kOutS8)) {
     uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + index;
     if (valid == 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
       uint32_t w[4];
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
-        w[t] = (uint32_t)out_byte(p, o[4 * t]) |
-               ((uint32_t)out_byte(p, o[4 * t + 1]) << 8) |
-               ((uint32_t)out_byte(p, o[4 * t + 2]) << 16) |
-               ((uint32_t)out_byte(p, o[4 * t + 3]) << 24);
+        w[t] = (uint32_t)out_byte_as(out_type, p, o[4 * t]) |
+               ((uint32_t)out_byte_as(out_type, p, o[4 * t + 1]) << 8) |
+               ((uint32_t)out_byte_as(out_type, p, o[4 * t + 2]) << 16) |
+               ((uint32_t)out_byte_as(out_type, p, o[4 * t + 3]) << 24);
       }
       *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
     } else {
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
-        if (t < valid) dst[t] = out_byte(p, o[t]);
+        if (t < valid) dst[t] = out_byte_as(out_type, p, o[t]);
       }
     }
   } else {
@@ -294,10 +299,12 @@ __device__ __forceinline__ void store_chunk16(const GemmParams& p, long long ind
 
 // 16 consecutive bf16 of one row as floats (vector loads when aligned).
 // Eight consecutive outputs of one row (valid may be <= 0 or > 8).
+template <int OUT = -1>
 __device__ __forceinline__ void store_chunk8(const GemmParams& p, long long index, int valid,
                                              const float (&o)[8]) {
   if (valid <= 0) return;
-  if (p.out_type == kOutBf16) {
+  const int out_type = OUT >= 0 ? OUT : p.out_type;  // OUT >= 0: the one type this kernel writes
+  if (out_type == kOutBf16) {
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + index;
     if (valid >= 8 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
       uint32_t w[4];
@@ -313,25 +320,25 @@ __device__ __forceinline__ void store_chunk8(const GemmParams& p, long long inde
         if (t < valid) dst[t] = __float2bfloat16(o[t]);
       }
     }
-  } else if (out_is_byte(p)) {
+  } else if ((out_type == kOutE4m3 || out_type == kOutS8)) {
     uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + index;
     if (valid >= 8 && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
       uint32_t w[2];
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
-        w[t] = (uint32_t)out_byte(p, o[4 * t]) |
-               ((uint32_t)out_byte(p, o[4 * t + 1]) << 8) |
-               ((uint32_t)out_byte(p, o[4 * t + 2]) << 16) |
-               ((uint32_t)out_byte(p, o[4 * t + 3]) << 24);
+        w[t] = (uint32_t)out_byte_as(out_type, p, o[4 * t]) |
+               ((uint32_t)out_byte_as(out_type, p, o[4 * t + 1]) << 8) |
+               ((uint32_t)out_byte_as(out_type, p, o[4 * t + 2]) << 16) |
+               ((uint32_t)out_byte_as(out_type, p, o[4 * t + 3]) << 24);
       }
       *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
     } else {
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
-        if (t < valid) dst[t] = out_byte(p, o[t]);
+        if (t < valid) dst[t] = out_byte_as(out_type, p, o[t]);
       }
     }
-  } else if (p.out_type == kOutF16) {
+  } else if (out_type == kOutF16) {
     __half* dst = reinterpret_cast<__half*>(p.out) + index;
     if (valid >= 8 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
       uint32_t w[4];
@@ -347,7 +354,7 @@ __device__ __forceinline__ void store_chunk8(const GemmParams& p, long long inde
         if (t < valid) dst[t] = __float2half_rn(o[t]);
       }
     }
-  } else if (p.out_type == kOutF32) {
+  } else if (out_type == kOutF32) {
     float* dst = reinterpret_cast<float*>(p.out) + index;
     if (valid >= 8 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
       reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
@@ -397,7 +404,8 @@ __device__ __forceinline__ void lds16(const float* src, float (&x)[16]) {
 // Where the epilogue reads the accumulator from: this CTA's TMEM (one split) or
 // the sum over all splits' partial tiles in global memory, added in split order
 // so the result does not depend on which split arrived last.
-template <int OP, int BLOCK_N>
+// PARTIAL = false: a kernel that never splits K; only the TMEM path is compiled.
+template <int OP, int BLOCK_N, bool PARTIAL = true>
 struct AccSource {
   uint32_t taddr_row;
   const uint32_t* partial_row;  // this thread's row in split 0, or null
@@ -405,7 +413,7 @@ struct AccSource {
   int splits;
 
   __device__ __forceinline__ void load16(int col0, uint32_t (&raw)[16]) const {
-    if (partial_row == nullptr) {
+    if (!PARTIAL || partial_row == nullptr) {
       ptx::tmem_ld_16(taddr_row + col0, raw);
       return;
     }
@@ -456,7 +464,7 @@ struct AccSource {
     }
   }
   __device__ __forceinline__ void wait() const {
-    if (partial_row == nullptr) ptx::tmem_ld_wait();
+    if (!PARTIAL || partial_row == nullptr) ptx::tmem_ld_wait();
   }
 };
 
@@ -485,9 +493,10 @@ __device__ __forceinline__ void load_row16_packed(const __nv_bfloat16* src, int 
 // a bf16 chunk leaves as one 32-byte store, and the residual (or position) values of the next round are
 // requested before the current one is processed, the first round's even before the
 // accumulator is complete (`wait_acc`), so their latency hides behind the mainloop.
-template <int OP, int BLOCK_N, int MODE, int HALVES, typename WaitAcc>
+// OUT >= 0 fixes the output type at compile time (the launch's p.out_type must equal it).
+template <int OP, int BLOCK_N, int MODE, int HALVES, int OUT = -1, bool PARTIAL, typename WaitAcc>
 __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
-                                                const AccSource<OP, BLOCK_N>& acc, int r,
+                                                const AccSource<OP, BLOCK_N, PARTIAL>& acc, int r,
                                                 int tile_b, long long out_base, float sr, int half,
                                                 const float* s_scale, const float* s_bias,
                                                 const float* s_gate, WaitAcc&& wait_acc) {
@@ -496,6 +505,7 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
   constexpr int kChunks = BLOCK_N / 16;
   constexpr int kPerWarp = (kChunks + HALVES - 1) / HALVES;
   constexpr int kRounds = (kPerWarp + 1) / 2;
+  const int out_type = OUT >= 0 ? OUT : p.out_type;
   const bool row_ok = r < p.rows_a;
   const bool has_scale = p.col_scale != nullptr;
   const __nv_bfloat16* extra_row = nullptr;
@@ -533,7 +543,7 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
       const int c0 = tile_b * BLOCK_N + cc * 16;
       const int valid = row_ok && cc < kChunks ? min(16, p.rows_b - c0) : 0;
       const long long index = out_base + (long long)r * p.ldc + c0;
-      if (valid > 0 && p.out_type == kOutS32) {
+      if (valid > 0 && out_type == kOutS32) {
         int* dst = reinterpret_cast<int*>(p.out) + index;
 #pragma unroll
         for (int t = 0; t < 16; ++t) {
@@ -541,7 +551,7 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
         }
       } else if (valid > 0) {
         uint32_t packed[8];  // bf16 pairs of the 16 columns, for one 32-byte store
-        const bool wide = p.out_type == kOutBf16 && valid == 16 &&
+        const bool wide = out_type == kOutBf16 && valid == 16 &&
                           ((reinterpret_cast<uintptr_t>(p.out) + 2 * index) & 31u) == 0;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {  // eight columns at a time keeps the temporaries in registers
@@ -555,7 +565,7 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
             o[0] *= s0.x; o[1] *= s0.y; o[2] *= s0.z; o[3] *= s0.w;
             o[4] *= s1.x; o[5] *= s1.y; o[6] *= s1.z; o[7] *= s1.w;
           }
-          if (!out_is_raw(p.out_type)) {
+          if (!out_is_raw(out_type)) {
             const float4 b0 = reinterpret_cast<const float4*>(s_bias + j)[0];
             const float4 b1 = reinterpret_cast<const float4*>(s_bias + j)[1];
             const float bias[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
@@ -570,7 +580,7 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
               const float2 x = __bfloat1622float2(e[t]);
-              if (MODE == kEpiBiasGelu && p.out_type == kOutE4m3) {
+              if (MODE == kEpiBiasGelu && out_type == kOutE4m3) {
                 o[2 * t] = gelu_tanh_fast(round_bf16(o[2 * t]) + bias[2 * t]);
                 o[2 * t + 1] = gelu_tanh_fast(round_bf16(o[2 * t + 1]) + bias[2 * t + 1]);
               } else {
@@ -586,7 +596,7 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
               packed[4 * h + t] = *reinterpret_cast<const uint32_t*>(&pair);
             }
           } else {
-            store_chunk8(p, index + 8 * h, valid - 8 * h, o);
+            store_chunk8<OUT>(p, index + 8 * h, valid - 8 * h, o);
           }
         }
         if (wide) {
@@ -607,12 +617,12 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
 
 // GeGLU epilogue, thread = one output row: packed columns [128t, 128t+64) are gate features,
 // [128t+64, 128t+128) the matching up features.
-template <int OP, int BLOCK_N, int HALVES>
+template <int OP, int BLOCK_N, int HALVES, int OUT = -1, bool PARTIAL>
 __device__ __forceinline__ void epilogue_geglu_normal(const GemmParams& p,
-                                                      const AccSource<OP, BLOCK_N>& acc, int r,
+                                                      const AccSource<OP, BLOCK_N, PARTIAL>& acc, int r,
                                                       int tile_b, long long out_base, float sr,
                                                       int half, const float* s_scale) {
-  const bool fast = p.out_type == kOutE4m3;
+  const bool fast = (OUT >= 0 ? OUT : p.out_type) == kOutE4m3;
 #pragma unroll 1
   for (int it = half; it < BLOCK_N / 32; it += HALVES) {
     const int pair = it >> 2, sub = it & 3;
@@ -634,15 +644,15 @@ __device__ __forceinline__ void epilogue_geglu_normal(const GemmParams& p,
       o[t] = (fast ? gelu_tanh_fast(g) : gelu_tanh_f(g)) * u;
     }
     if (r < p.rows_a && cg < p.rows_b) {
-      store_chunk16(p, out_base + (long long)r * p.ldc + oc, 16, o);
+      store_chunk16<OUT>(p, out_base + (long long)r * p.ldc + oc, 16, o);
     }
   }
 }
 
 // Thread = one output column (weight row), TMEM columns = output rows.
-template <int OP, int BLOCK_N, int MODE, int HALVES>
+template <int OP, int BLOCK_N, int MODE, int HALVES, bool PARTIAL>
 __device__ __forceinline__ void epilogue_swapped(const GemmParams& p,
-                                                 const AccSource<OP, BLOCK_N>& acc, int c,
+                                                 const AccSource<OP, BLOCK_N, PARTIAL>& acc, int c,
                                                  int tile_b, long long out_base, int half,
                                                  float sc, float bias, float gate,
                                                  const float* s_rowscale) {
@@ -706,7 +716,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr uint32_t kIdesc =
       ptx::make_idesc(T::kCFormat, T::kFormat, T::kFormat, 0, B_MN ? 1 : 0, 128, BLOCK_N);
 
-  const int mode = FIXED_MODE >= 0 ? FIXED_MODE : p.mode;
+  // A kernel compiled for one epilogue also fixes what that epilogue writes in the forward (FP8
+  // activations after bias + GELU of an FP8 GEMM, bf16 otherwise) and never splits K.
+  constexpr bool kLean = FIXED_MODE >= 0;
+  static_assert(!kLean || !SWAP, "single-epilogue kernels: activations on the 128-row side");
+  constexpr int kFixedOut =
+      !kLean ? -1 : (OP == kOpE4m3 && FIXED_MODE == kEpiBiasGelu) ? kOutE4m3 : kOutBf16;
+  const int mode = kLean ? FIXED_MODE : p.mode;
 
   pdl_launch_dependents();
 
@@ -895,9 +911,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::tc_fence_after();
     const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
 
-    AccSource<OP, BLOCK_N> acc{taddr_row, nullptr, 0, 1};
+    AccSource<OP, BLOCK_N, !kLean> acc{taddr_row, nullptr, 0, 1};
     bool run_epilogue = true;
-    if (p.split_k > 1) {
+    if (!kLean && p.split_k > 1) {
       const long long tile_id = ((long long)batch * gridDim.y + tile_b) * gridDim.x + tile_a;
       uint32_t* tile_ws = p.partials + tile_id * p.split_k * (128LL * BLOCK_N);
       uint32_t* mine = tile_ws + (long long)split * (128LL * BLOCK_N) + row_in_tile * BLOCK_N;
@@ -988,8 +1004,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     } else if constexpr (!SWAP) {
 #define PI05_EPI_CASE(MODE)                                                                       \
   case MODE:                                                                                      \
-    epilogue_normal<OP, BLOCK_N, MODE, kHalves>(p, acc, gi, tile_b, out_base, sr, half, s_scale,  \
-                                                s_bias, s_gate, [] {});                           \
+    epilogue_normal<OP, BLOCK_N, MODE, kHalves, kFixedOut>(p, acc, gi, tile_b, out_base, sr, half, \
+                                                           s_scale, s_bias, s_gate, [] {});        \
     break;
       switch (mode) {
         PI05_EPI_CASE(kEpiStore)
@@ -1038,7 +1054,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // works on tile i+1 and the TMA warp runs ahead through the shared-memory ring.
 // Normal orientation only (activations on the 128-row side), no split-K.
 // ---------------------------------------------------------------------------
-template <int OP, int BLOCK_N, int STAGES, bool B_MN, int EPI_WARPS>
+// FIXED_MODE >= 0: compiled for that one epilogue and for the output type the forward writes
+// after it (FP8 after GeGLU or bias + GELU of an FP8 GEMM, bf16 otherwise).
+template <int OP, int BLOCK_N, int STAGES, bool B_MN, int EPI_WARPS, int FIXED_MODE = -1>
 __global__ void __launch_bounds__(gemm_threads(EPI_WARPS), 1)
 gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             const __grid_constant__ CUtensorMap tmap_b, const GemmParams p,
@@ -1051,6 +1069,10 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr int kBlockK = 128 / T::kElemBytes;
   constexpr int kStageBBytes = BLOCK_N * 128;
   constexpr int kStageBytes = kStageABytes + kStageBBytes;
+  constexpr int kFixedOut = FIXED_MODE < 0 ? -1
+                            : (OP == kOpE4m3 && (FIXED_MODE == kEpiBiasGelu || FIXED_MODE == kEpiGeglu))
+                                ? kOutE4m3
+                                : kOutBf16;
   constexpr uint32_t kTmemCols = 2 * BLOCK_N <= 32    ? 32u
                                  : 2 * BLOCK_N <= 64  ? 64u
                                  : 2 * BLOCK_N <= 128 ? 128u
@@ -1213,17 +1235,19 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
       };
       const uint32_t taddr_row =
           tmem_base + buf * BLOCK_N + (static_cast<uint32_t>(quarter * 32) << 16);
-      AccSource<OP, BLOCK_N> acc{taddr_row, nullptr, 0, 1};
-      if (p.mode == kEpiGeglu) {
+      AccSource<OP, BLOCK_N, false> acc{taddr_row, nullptr, 0, 1};
+      const int mode = FIXED_MODE >= 0 ? FIXED_MODE : p.mode;
+      if (mode == kEpiGeglu) {
         wait_acc();
-        epilogue_geglu_normal<OP, BLOCK_N, kHalves>(p, acc, gi, tb, out_base, sr, half, s_scale);
+        epilogue_geglu_normal<OP, BLOCK_N, kHalves, kFixedOut>(p, acc, gi, tb, out_base, sr, half,
+                                                               s_scale);
       } else {
 #define PI05_EPI_CASE(MODE)                                                                    \
   case MODE:                                                                                   \
-    epilogue_normal<OP, BLOCK_N, MODE, kHalves>(p, acc, gi, tb, out_base, sr, half, s_scale,   \
-                                                s_bias, s_gate, wait_acc);                     \
+    epilogue_normal<OP, BLOCK_N, MODE, kHalves, kFixedOut>(p, acc, gi, tb, out_base, sr, half, \
+                                                           s_scale, s_bias, s_gate, wait_acc); \
     break;
-        switch (p.mode) {
+        switch (mode) {
           PI05_EPI_CASE(kEpiStore)
           PI05_EPI_CASE(kEpiBiasGelu)
           PI05_EPI_CASE(kEpiBiasSilu)
