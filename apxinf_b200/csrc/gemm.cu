@@ -127,6 +127,8 @@ const void* persistent_lean_ptr(int lean_mode, int* smem, int* threads) {
     if (lean_mode == kEpiBiasResidual)
       return persistent_ptr<OP, BLOCK_N, STAGES, false, kEpiBiasResidual>(smem, threads);
     if (lean_mode == kEpiGeglu) return persistent_ptr<OP, BLOCK_N, STAGES, false, kEpiGeglu>(smem, threads);
+    if (lean_mode == kEpiGateResidual)
+      return persistent_ptr<OP, BLOCK_N, STAGES, false, kEpiGateResidual>(smem, threads);
   }
   return persistent_ptr<OP, BLOCK_N, STAGES, false>(smem, threads);
 }
@@ -146,8 +148,8 @@ const void* select_persistent(int block_n, bool b_mn, int lean_mode, int* smem, 
   return nullptr;
 }
 
-// The epilogues that SigLIP and the prefix run in every layer (plain store, bias + GELU, bias +
-// residual) have kernels of their own for the bf16 and FP8 forward: no other epilogue's code, no
+// The epilogues that SigLIP, the prefix and the batched action expert run in every layer (plain
+// store, bias + GELU, bias + residual, gated residual) have kernels of their own for the bf16 and FP8 forward: no other epilogue's code, no
 // split-K exchange, one output type (`lean_mode` is the epilogue, or -1 for the general kernel).
 // Measured on the FP8 B=1 forward: 9.53 -> 9.05 ms for the shorter instruction stream alone.
 template <int OP, int BLOCK_N, int STAGES>
@@ -157,6 +159,8 @@ const void* plain_ptr(int mode, int* smem, int* threads) {
     if (mode == kEpiBiasGelu) return kernel_ptr<OP, BLOCK_N, STAGES, false, false, 8, kEpiBiasGelu>(smem, threads);
     if (mode == kEpiBiasResidual)
       return kernel_ptr<OP, BLOCK_N, STAGES, false, false, 8, kEpiBiasResidual>(smem, threads);
+    if (mode == kEpiGateResidual)
+      return kernel_ptr<OP, BLOCK_N, STAGES, false, false, 8, kEpiGateResidual>(smem, threads);
   }
   return kernel_ptr<OP, BLOCK_N, STAGES, false, false>(smem, threads);
 }
@@ -395,7 +399,8 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   // the single-epilogue kernels write what the forward writes after that epilogue and never split
   const int lean_out = (q.op == kOpE4m3 && q.mode == kEpiBiasGelu) ? kOutE4m3 : kOutBf16;
   const bool lean_epilogue =
-      q.mode == kEpiStore || q.mode == kEpiBiasGelu || q.mode == kEpiBiasResidual;
+      q.mode == kEpiStore || q.mode == kEpiBiasGelu || q.mode == kEpiBiasResidual ||
+      q.mode == kEpiGateResidual;
   const int lean_mode = (lean_epilogue && !swap && !q.b_mn_major && q.force_split_k <= 1 &&
                          q.out_type == lean_out && (q.op == kOpBf16 || q.op == kOpE4m3))
                             ? q.mode
