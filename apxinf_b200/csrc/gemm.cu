@@ -121,7 +121,7 @@ const void* persistent_ptr(int* smem, int* threads) {
 
 template <int OP, int BLOCK_N, int STAGES>
 const void* persistent_lean_ptr(int lean_mode, int* smem, int* threads) {
-  if constexpr (OP == kOpBf16 || OP == kOpE4m3) {
+  {
     if (lean_mode == kEpiStore) return persistent_ptr<OP, BLOCK_N, STAGES, false, kEpiStore>(smem, threads);
     if (lean_mode == kEpiBiasGelu) return persistent_ptr<OP, BLOCK_N, STAGES, false, kEpiBiasGelu>(smem, threads);
     if (lean_mode == kEpiBiasResidual)
@@ -154,7 +154,7 @@ const void* select_persistent(int block_n, bool b_mn, int lean_mode, int* smem, 
 // Measured on the FP8 B=1 forward: 9.53 -> 9.05 ms for the shorter instruction stream alone.
 template <int OP, int BLOCK_N, int STAGES>
 const void* plain_ptr(int mode, int* smem, int* threads) {
-  if constexpr (OP == kOpBf16 || OP == kOpE4m3) {
+  {
     if (mode == kEpiStore) return kernel_ptr<OP, BLOCK_N, STAGES, false, false, 8, kEpiStore>(smem, threads);
     if (mode == kEpiBiasGelu) return kernel_ptr<OP, BLOCK_N, STAGES, false, false, 8, kEpiBiasGelu>(smem, threads);
     if (mode == kEpiBiasResidual)
@@ -397,12 +397,13 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   int smem = 0, threads = 0;
   const void* kernel = nullptr;
   // the single-epilogue kernels write what the forward writes after that epilogue and never split
-  const int lean_out = (q.op == kOpE4m3 && q.mode == kEpiBiasGelu) ? kOutE4m3 : kOutBf16;
+  const int act_out = q.op == kOpE4m3 ? kOutE4m3 : q.op == kOpS8 ? kOutS8 : kOutBf16;
+  const int lean_out = q.mode == kEpiBiasGelu ? act_out : kOutBf16;
   const bool lean_epilogue =
       q.mode == kEpiStore || q.mode == kEpiBiasGelu || q.mode == kEpiBiasResidual ||
       q.mode == kEpiGateResidual;
   const int lean_mode = (lean_epilogue && !swap && !q.b_mn_major && q.force_split_k <= 1 &&
-                         q.out_type == lean_out && (q.op == kOpBf16 || q.op == kOpE4m3))
+                         q.out_type == lean_out)
                             ? q.mode
                             : -1;
   if (q.op == kOpBf16) kernel = select_kernel<kOpBf16>(block_n, swap, q.b_mn_major, multi_wave, lean_mode, &smem, &threads);
@@ -510,11 +511,10 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   if (plan->multi_wave_candidate && split == 1) {
     const void* persistent = nullptr;
     // GeGLU too has a kernel of its own here (FP8 out of an FP8 GEMM, bf16 out of a bf16 one)
-    const int geglu_out = q.op == kOpE4m3 ? kOutE4m3 : kOutBf16;
+    const int geglu_out = act_out;
     const int persistent_lean =
         lean_mode >= 0 ? lean_mode
-        : (q.mode == kEpiGeglu && !q.b_mn_major && q.out_type == geglu_out &&
-           (q.op == kOpBf16 || q.op == kOpE4m3))
+        : (q.mode == kEpiGeglu && !q.b_mn_major && q.out_type == geglu_out)
             ? static_cast<int>(kEpiGeglu)
             : -1;
     if (q.op == kOpBf16) persistent = select_persistent<kOpBf16>(block_n, q.b_mn_major, persistent_lean, &smem, &threads);

@@ -716,12 +716,12 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr uint32_t kIdesc =
       ptx::make_idesc(T::kCFormat, T::kFormat, T::kFormat, 0, B_MN ? 1 : 0, 128, BLOCK_N);
 
-  // A kernel compiled for one epilogue also fixes what that epilogue writes in the forward (FP8
-  // activations after bias + GELU of an FP8 GEMM, bf16 otherwise) and never splits K.
+  // A kernel compiled for one epilogue also fixes what that epilogue writes in the forward (FP8 /
+  // int8 activations after bias + GELU of an FP8 / int8 GEMM, bf16 otherwise) and never splits K.
   constexpr bool kLean = FIXED_MODE >= 0;
   static_assert(!kLean || !SWAP, "single-epilogue kernels: activations on the 128-row side");
   constexpr int kFixedOut =
-      !kLean ? -1 : (OP == kOpE4m3 && FIXED_MODE == kEpiBiasGelu) ? kOutE4m3 : kOutBf16;
+      !kLean ? -1 : FIXED_MODE != kEpiBiasGelu ? kOutBf16 : OP == kOpE4m3 ? kOutE4m3 : OP == kOpS8 ? kOutS8 : kOutBf16;
   const int mode = kLean ? FIXED_MODE : p.mode;
 
   pdl_launch_dependents();
@@ -1055,7 +1055,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // Normal orientation only (activations on the 128-row side), no split-K.
 // ---------------------------------------------------------------------------
 // FIXED_MODE >= 0: compiled for that one epilogue and for the output type the forward writes
-// after it (FP8 after GeGLU or bias + GELU of an FP8 GEMM, bf16 otherwise).
+// after it (FP8 / int8 after GeGLU or bias + GELU of an FP8 / int8 GEMM, bf16 otherwise).
 template <int OP, int BLOCK_N, int STAGES, bool B_MN, int EPI_WARPS, int FIXED_MODE = -1>
 __global__ void __launch_bounds__(gemm_threads(EPI_WARPS), 1)
 gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -1070,9 +1070,10 @@ gemm_umma_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr int kStageBBytes = BLOCK_N * 128;
   constexpr int kStageBytes = kStageABytes + kStageBBytes;
   constexpr int kFixedOut = FIXED_MODE < 0 ? -1
-                            : (OP == kOpE4m3 && (FIXED_MODE == kEpiBiasGelu || FIXED_MODE == kEpiGeglu))
-                                ? kOutE4m3
-                                : kOutBf16;
+                            : !(FIXED_MODE == kEpiBiasGelu || FIXED_MODE == kEpiGeglu) ? kOutBf16
+                            : OP == kOpE4m3                                          ? kOutE4m3
+                            : OP == kOpS8                                            ? kOutS8
+                                                                                     : kOutBf16;
   constexpr uint32_t kTmemCols = 2 * BLOCK_N <= 32    ? 32u
                                  : 2 * BLOCK_N <= 64  ? 64u
                                  : 2 * BLOCK_N <= 128 ? 128u
