@@ -179,6 +179,8 @@ extern "C" int pi05_set_tuning(const char* name, int32_t value) {
     pi05::set_wait_polls(value);
   } else if (key == "drop_one_load") {
     pi05::set_drop_load_kb(value);
+  } else if (key == "single_epilogue_kernels") {
+    pi05::set_single_epilogue_kernels_enabled(value != 0);
   } else if (key == "force_capture_failure") {
     g_force_capture_failure = value != 0;
   } else {

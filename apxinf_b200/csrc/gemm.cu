@@ -14,9 +14,11 @@ bool g_pdl_enabled = true;
 bool g_fuse_small_rows = true;
 uint32_t g_wait_polls = ptx::kSpinLimit;
 int g_drop_load_kb = -1;
+bool g_single_epilogue = true;
 }
 void set_wait_polls(int polls) { g_wait_polls = polls > 0 ? static_cast<uint32_t>(polls) : ptx::kSpinLimit; }
 void set_drop_load_kb(int kb) { g_drop_load_kb = kb; }
+void set_single_epilogue_kernels_enabled(bool enabled) { g_single_epilogue = enabled; }
 bool pdl_enabled() { return g_pdl_enabled; }
 void set_pdl_enabled(bool enabled) { g_pdl_enabled = enabled; }
 bool fuse_small_rows_enabled() { return g_fuse_small_rows; }
@@ -402,7 +404,7 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   const bool lean_epilogue =
       q.mode == kEpiStore || q.mode == kEpiBiasGelu || q.mode == kEpiBiasResidual ||
       q.mode == kEpiGateResidual;
-  const int lean_mode = (lean_epilogue && !swap && !q.b_mn_major && q.force_split_k <= 1 &&
+  const int lean_mode = (g_single_epilogue && lean_epilogue && !swap && !q.b_mn_major && q.force_split_k <= 1 &&
                          q.out_type == lean_out)
                             ? q.mode
                             : -1;
@@ -514,7 +516,7 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
     const int geglu_out = act_out;
     const int persistent_lean =
         lean_mode >= 0 ? lean_mode
-        : (q.mode == kEpiGeglu && !q.b_mn_major && q.out_type == geglu_out)
+        : (g_single_epilogue && q.mode == kEpiGeglu && !q.b_mn_major && q.out_type == geglu_out)
             ? static_cast<int>(kEpiGeglu)
             : -1;
     if (q.op == kOpBf16) persistent = select_persistent<kOpBf16>(block_n, q.b_mn_major, persistent_lean, &smem, &threads);

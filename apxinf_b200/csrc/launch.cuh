@@ -32,6 +32,9 @@ void set_fuse_norms_enabled(bool enabled);
 // first CTA announces but never issues (-1: none).
 void set_wait_polls(int polls);
 void set_drop_load_kb(int kb);
+// GEMM plans built afterwards take the kernels compiled for one epilogue where one fits
+// (default), or always the general kernel.
+void set_single_epilogue_kernels_enabled(bool enabled);
 
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

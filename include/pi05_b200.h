@@ -421,6 +421,9 @@ int pi05_graph_signature(Pi05Graph* graph, const char* name, Pi05Signature* out)
  * K block but never issues it, so the stage never fills, the bounded waits run out, the kernel
  * records its status word, releases its TMEM and returns; the caller sees PI05_ERR_DEVICE_TIMEOUT
  * at the next sync and the context stays usable.
+ * "single_epilogue_kernels" (default 1): GEMM plans built afterwards run, where one fits, a
+ * tcgen05 kernel compiled for their one epilogue and output type (same arithmetic, a shorter
+ * instruction stream); 0 always plans the general kernel.
  * "force_capture_failure" (default 0): plans built by pi05_runtime_infer skip graph capture, as
  * if the driver had refused it (exercises the eager fallback). Unknown names:
  * PI05_ERR_INVALID_VALUE. */

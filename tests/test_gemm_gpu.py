@@ -357,3 +357,64 @@ def test_persistent_kernel_raster_groups_cover_every_tile(M, N, Kd, batch):
     assert st.item() == 0
     want = torch.matmul(ad.float(), bd.float().transpose(1, 2)).round().to(torch.int32)  # exact: |sum| < 2^24
     assert torch.equal(out, want)
+
+
+def _tuning(name, value):
+    from apxinf_b200._lib import lib
+    assert lib().pi05_set_tuning(name.encode(), int(value)) == 0
+
+
+@pytest.mark.parametrize("op", [0, 1, 2])
+@pytest.mark.parametrize("mode", [0, 1, 3, 5, 6])
+@pytest.mark.parametrize("M,N,Kd", [(300, 200, 320), (522, 1152, 1152), (2600, 1536, 256)])
+def test_single_epilogue_kernels_give_the_general_kernel_bits(op, mode, M, N, Kd):
+    """Launches that fit a kernel compiled for one epilogue and output type (the default plan)
+    against the general kernel planned for the same call: the same arithmetic, so the same
+    bits. Covers one wave of tiles with ragged edges, the B=1 SigLIP shape and a multi-wave
+    shape that runs the persistent kernel; activation outputs (after GELU / GeGLU) in the
+    operand's own 8-bit type."""
+    L, K = _lib()
+    if mode == L.EPI_GEGLU:
+        N = (N + 127) // 128 * 128
+    gen = torch.Generator().manual_seed(7000 + 13 * op + mode + M)
+    a, _ = make_operand(M, Kd, op, gen, 0.5)
+    if op == L.OP_S8:
+        a = torch.randint(-20, 21, (M, Kd), generator=gen, dtype=torch.int8)
+        b = torch.randint(-20, 21, (N, Kd), generator=gen, dtype=torch.int8)
+    else:
+        b, _ = make_operand(N, Kd, op, gen, 0.05)
+    n_out = N // 2 if mode == L.EPI_GEGLU else N
+    bias = (torch.randn(N, generator=gen) * 0.1).to(torch.bfloat16).cuda()
+    gate = torch.randn(N, generator=gen).to(torch.bfloat16).cuda()
+    residual = torch.randn(M, n_out, generator=gen).to(torch.bfloat16)
+    col_scale = (torch.rand(N, generator=gen) * 0.01 + 0.001).cuda()
+    activation = mode in (L.EPI_BIAS_GELU, L.EPI_GEGLU)
+    if activation and op == L.OP_E4M3:
+        out_type, dtype = L.OUT_E4M3, torch.uint8
+    elif activation and op == L.OP_S8:
+        out_type, dtype = L.OUT_S8, torch.int8
+    else:
+        out_type, dtype = L.OUT_BF16, torch.bfloat16
+    ad, bd = a.cuda(), b.cuda()
+
+    def run():
+        if dtype == torch.bfloat16:
+            out = residual.cuda().clone()
+        else:
+            out = torch.zeros(M, n_out, dtype=dtype, device="cuda")
+        st = K.gemm(ad, bd, out, op=op, mode=mode, out_type=out_type, bias=None if mode == L.EPI_GEGLU else bias,
+                    residual=out if mode in (L.EPI_BIAS_RESIDUAL, L.EPI_GATE_RESIDUAL) else None,
+                    gate=gate if mode == L.EPI_GATE_RESIDUAL else None, col_scale=col_scale,
+                    alpha=0.5, out_inv_scale=8.0, force_swap=0)
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        return out.cpu()
+
+    single = run()
+    _tuning("single_epilogue_kernels", 0)
+    try:
+        general = run()
+    finally:
+        _tuning("single_epilogue_kernels", 1)
+    assert torch.equal(single.view(torch.uint8), general.view(torch.uint8))
+    assert single.view(torch.uint8).float().std().item() > 0  # not all one value
