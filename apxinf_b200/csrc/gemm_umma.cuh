@@ -494,7 +494,8 @@ __device__ __forceinline__ void load_row16_packed(const __nv_bfloat16* src, int 
 // requested before the current one is processed, the first round's even before the
 // accumulator is complete (`wait_acc`), so their latency hides behind the mainloop.
 // OUT >= 0 fixes the output type at compile time (the launch's p.out_type must equal it).
-template <int OP, int BLOCK_N, int MODE, int HALVES, int OUT = -1, bool PARTIAL, typename WaitAcc>
+template <int OP, int BLOCK_N, int MODE, int HALVES, int OUT = -1, int PER_ROUND = 2, bool PARTIAL,
+          typename WaitAcc>
 __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
                                                 const AccSource<OP, BLOCK_N, PARTIAL>& acc, int r,
                                                 int tile_b, long long out_base, float sr, int half,
@@ -504,7 +505,9 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
       MODE == kEpiBiasResidual || MODE == kEpiBiasPos || MODE == kEpiGateResidual;
   constexpr int kChunks = BLOCK_N / 16;
   constexpr int kPerWarp = (kChunks + HALVES - 1) / HALVES;
-  constexpr int kRounds = (kPerWarp + 1) / 2;
+  // chunks per TMEM round trip
+  constexpr int kPerRound = PER_ROUND;
+  constexpr int kRounds = (kPerWarp + kPerRound - 1) / kPerRound;
   const int out_type = OUT >= 0 ? OUT : p.out_type;
   const bool row_ok = r < p.rows_a;
   const bool has_scale = p.col_scale != nullptr;
@@ -513,9 +516,9 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
     extra_row = MODE == kEpiBiasPos ? p.pos + (long long)(r % p.pos_rows) * p.pos_ld
                                     : p.residual + out_base + (long long)r * p.ldc;
   }
-  uint4 ahead[2][2];  // residual / position values (16 bf16 per chunk) of the round to come
+  uint4 ahead[kPerRound][2];  // residual / position values (16 bf16 per chunk) of the round to come
   auto fetch_extra = [&](int round, int u, uint4 (&dst)[2]) {
-    const int cc = half + (2 * round + u) * HALVES;
+    const int cc = half + (kPerRound * round + u) * HALVES;
     const int c0 = tile_b * BLOCK_N + cc * 16;
     if (kExtra && row_ok && cc < kChunks && c0 < p.rows_b) {
       load_row16_packed(extra_row + c0, min(16, p.rows_b - c0), dst);
@@ -524,22 +527,22 @@ __device__ __forceinline__ void epilogue_normal(const GemmParams& p,
       dst[1] = make_uint4(0, 0, 0, 0);
     }
   };
-  fetch_extra(0, 0, ahead[0]);
-  fetch_extra(0, 1, ahead[1]);
+#pragma unroll
+  for (int u = 0; u < kPerRound; ++u) fetch_extra(0, u, ahead[u]);
   wait_acc();
 #pragma unroll 1
   for (int round = 0; round < kRounds; ++round) {
-    uint32_t raw[2][16];
+    uint32_t raw[kPerRound][16];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
+    for (int u = 0; u < kPerRound; ++u) {
       // always issued (a conditional TMEM load would push the array to local memory); a slot
       // beyond the tile re-reads the last chunk and is ignored below
-      acc.load16(min(half + (2 * round + u) * HALVES, kChunks - 1) * 16, raw[u]);
+      acc.load16(min(half + (kPerRound * round + u) * HALVES, kChunks - 1) * 16, raw[u]);
     }
     acc.wait();
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int cc = half + (2 * round + u) * HALVES;
+    for (int u = 0; u < kPerRound; ++u) {
+      const int cc = half + (kPerRound * round + u) * HALVES;
       const int c0 = tile_b * BLOCK_N + cc * 16;
       const int valid = row_ok && cc < kChunks ? min(16, p.rows_b - c0) : 0;
       const long long index = out_base + (long long)r * p.ldc + c0;
@@ -719,6 +722,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // A kernel compiled for one epilogue also fixes what that epilogue writes in the forward (FP8 /
   // int8 activations after bias + GELU of an FP8 / int8 GEMM, bf16 otherwise) and never splits K.
   constexpr bool kLean = FIXED_MODE >= 0;
+  // Chunks per TMEM round trip in the epilogue: the narrow single-epilogue kernels run as one
+  // partial wave of CTAs that execute their epilogue once, where a loop body of one chunk (half
+  // the code) beat two chunks per round trip (FP8 B=1 forward 8.88 -> 8.82 ms); the 256-wide
+  // tiles of the batched step keep two (one was 0.2-2 % slower there).
+  constexpr int kPerRound = kLean && BLOCK_N <= 128 ? 1 : 2;
   static_assert(!kLean || !SWAP, "single-epilogue kernels: activations on the 128-row side");
   constexpr int kFixedOut =
       !kLean ? -1 : FIXED_MODE != kEpiBiasGelu ? kOutBf16 : OP == kOpE4m3 ? kOutE4m3 : OP == kOpS8 ? kOutS8 : kOutBf16;
@@ -1004,8 +1012,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     } else if constexpr (!SWAP) {
 #define PI05_EPI_CASE(MODE)                                                                       \
   case MODE:                                                                                      \
-    epilogue_normal<OP, BLOCK_N, MODE, kHalves, kFixedOut>(p, acc, gi, tile_b, out_base, sr, half, \
-                                                           s_scale, s_bias, s_gate, [] {});        \
+    epilogue_normal<OP, BLOCK_N, MODE, kHalves, kFixedOut, kPerRound>(                            \
+        p, acc, gi, tile_b, out_base, sr, half, s_scale, s_bias, s_gate, [] {});                  \
     break;
       switch (mode) {
         PI05_EPI_CASE(kEpiStore)
