@@ -64,6 +64,7 @@ class GemmArgs(C.Structure):
         ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
         ("rope_tokens", C.c_int32), ("rope_q_heads", C.c_int32), ("rope_head_dim", C.c_int32),
         ("rope_position_offset", C.c_int32), ("rope_cache_rows", C.c_int32), ("dt", C.c_float),
+        ("k_slices", C.c_int32),
     ]
 
 

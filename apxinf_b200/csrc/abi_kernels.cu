@@ -61,6 +61,7 @@ extern "C" int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream) {
   q.force_split_k = args->force_split_k;
   q.b_blocked = args->b_blocked != 0;
   q.force_skinny = args->force_skinny;
+  q.k_slices = args->k_slices > 1 ? args->k_slices : 1;
   q.prologue = args->prologue;
   q.style = args->style;
   q.eps = args->eps;

@@ -473,20 +473,21 @@ int PreparedGraph::linear(const char* name, const Act& in, int rows, const Linea
   q.N = w.n;
   q.K = static_cast<int>(std::min<long long>(w.ldk, in.ld));
   // A few hundred rows against a very long K (the B=1 language.down: 522 x 2048 x 16384) give
-  // too few output tiles for the SMs: the K range goes in two halves as a batch of two GEMMs
-  // writing fp32 partial products, and one row kernel adds them and applies the residual.
+  // too few output tiles for the SMs: the K range goes in as many slices as fill one wave of
+  // CTAs (three for that shape: 5 x 8 tiles x 3 = 120), each writing fp32 partial products, and
+  // one row kernel adds them and applies the residual.
   {
     const int block_k = 128 / elem_size(prec);
     const long long tiles256 = (long long)((rows + 127) / 128) * ((w.n + 255) / 256);
-    const bool long_k = q.K / block_k >= 96 && (q.K / 2) % block_k == 0;
+    const bool long_k = q.K / block_k >= 96;
+    const int slices = static_cast<int>(std::max<long long>(2, std::min<long long>(4, 148 / std::max<long long>(1, tiles256))));
     if (nb0 == 1 && mode == kEpiBiasResidual && out_type == kOutBf16 && gate == nullptr && pos == nullptr &&
         rows > 64 && tiles256 <= 74 && long_k && w.n % 8 == 0 && d_k_partials_ != nullptr &&
-        (size_t)rows * w.n * 2 * sizeof(float) <= k_partials_bytes_) {
+        (size_t)rows * w.n * slices * sizeof(float) <= k_partials_bytes_) {
       GemmProblem h = q;
-      h.K = q.K / 2;
-      h.nb0 = 2;
-      h.a = GemmOperand{in.data, rows, in.ld, h.K, 0};
-      h.b = GemmOperand{w.w, w.n, w.ldk, h.K, 0};
+      h.k_slices = slices;
+      h.a = GemmOperand{in.data, rows, in.ld, 0, 0};
+      h.b = GemmOperand{w.w, w.n, w.ldk, 0, 0};
       h.out = d_k_partials_;
       h.ldc = w.n;
       h.out_sb0 = (long long)rows * w.n;
@@ -505,7 +506,7 @@ int PreparedGraph::linear(const char* name, const Act& in, int rows, const Linea
       const int cols = w.n;
       const void* bias = w.bias;
       add_kernel((std::string(name) + ".sum").c_str(), [=](cudaStream_t s) {
-        return launch_sum_partials(partials, 2, count, cols, residual, bias, out, s);
+        return launch_sum_partials(partials, slices, count, cols, residual, bias, out, s);
       });
       return kPi05Ok;
     }
@@ -748,7 +749,7 @@ int PreparedGraph::build(bool measuring) {
   d_time_emb_ = arena_.alloc((size_t)S_ * ac.width * 2);
   d_partials_ = arena_.alloc(kSplitScratchBytes);
   // fp32 partial products of a K-halved GEMM (B=1 prefill only: a few hundred rows)
-  k_partials_bytes_ = Rp <= 640 ? (size_t)Rp * lg.width * 2 * sizeof(float) : 0;
+  k_partials_bytes_ = Rp <= 640 ? (size_t)Rp * lg.width * 4 * sizeof(float) : 0;
   d_k_partials_ = k_partials_bytes_ > 0 ? arena_.alloc(k_partials_bytes_) : nullptr;
   d_tile_counters_ = static_cast<int*>(arena_.alloc((size_t)kSplitMaxTiles * 4));
   note("state", d_state_, (size_t)Ra * c.action_dim * 2);

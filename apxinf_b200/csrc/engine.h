@@ -177,7 +177,7 @@ class PreparedGraph {
   void* d_time_emb_ = nullptr;
   void* d_partials_ = nullptr;      // split-K scratch shared by every GEMM of the graph
   int* d_tile_counters_ = nullptr;
-  void* d_k_partials_ = nullptr;    // fp32 [2][rows][width] of a K-halved GEMM, or null
+  void* d_k_partials_ = nullptr;    // fp32 [<= 4][rows][width] of a K-sliced GEMM, or null
   size_t k_partials_bytes_ = 0;
   uint16_t* h_out_ = nullptr;  // pinned
 };

@@ -221,7 +221,7 @@ bool skinny_fits(const GemmProblem& q) {
                        (reinterpret_cast<uintptr_t>(q.b.ptr) & 15u) == 0 &&
                        (q.b.ld * es) % 16 == 0 && ((long long)q.K * es) % 16 == 0 &&
                        (q.a.ld * (q.prologue != kProNone ? 2 : es)) % 16 == 0;
-  if (q.M > 16 || q.b_mn_major || q.b_blocked || q.nb0 * q.nb1 != 1 || q.mode == kEpiBiasPos || !aligned) {
+  if (q.M > 16 || q.b_mn_major || q.b_blocked || q.nb0 * q.nb1 != 1 || q.k_slices > 1 || q.mode == kEpiBiasPos || !aligned) {
     return false;
   }
   if (q.prologue != kProNone) {
@@ -352,6 +352,10 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   if (q.mode == kEpiBiasPos && (q.pos == nullptr || q.pos_rows <= 0)) return kPi05ErrInvalidValue;
   if (q.b_mn_major && q.op == kOpS8) return kPi05ErrUnsupported;
   if (q.b_blocked && (q.b_mn_major || q.nb0 * q.nb1 != 1)) return kPi05ErrUnsupported;
+  if (q.k_slices > 1 && (q.nb0 * q.nb1 != 1 || q.b_blocked || q.b_mn_major || q.force_split_k > 1)) {
+    return kPi05ErrUnsupported;
+  }
+  const int k_slices = q.k_slices > 1 ? q.k_slices : 1;
 
   const int es = elem_bytes(q.op);
   const int block_k = 128 / es;
@@ -368,7 +372,7 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
       // tiles cost MMA time but buy CTAs. Up to two CTAs share an SM (296 slots): use the
       // widest tile that still fills them, and 256 once there is more than a wave anyway.
       const long long tiles_m = (q.M + 127) / 128;
-      const long long batches = (long long)q.nb0 * q.nb1;
+      const long long batches = (long long)q.nb0 * q.nb1 * k_slices;
       const long long tiles256 = tiles_m * ((q.N + 255) / 256) * batches;
       const long long tiles128 = tiles_m * ((q.N + 127) / 128) * batches;
       // more than a wave of 256-wide tiles that also fills its last wave to four fifths (the
@@ -394,8 +398,10 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
 
   // more output tiles than SMs: two shallow-ring CTAs per SM overlap epilogue and main loop
   const long long tiles_planned = (long long)((swap ? q.N : q.M) + 127) / 128 *
-                                  (((swap ? q.M : q.N) + block_n - 1) / block_n) * q.nb0 * q.nb1;
-  const bool multi_wave = q.force_two_per_sm >= 0 ? q.force_two_per_sm != 0 : tiles_planned > 148;
+                                  (((swap ? q.M : q.N) + block_n - 1) / block_n) * q.nb0 * q.nb1 * k_slices;
+  // (K slices run the one-CTA-per-tile kernel: the persistent one walks plain batches)
+  const bool multi_wave =
+      k_slices > 1 ? false : q.force_two_per_sm >= 0 ? q.force_two_per_sm != 0 : tiles_planned > 148;
   int smem = 0, threads = 0;
   const void* kernel = nullptr;
   // the single-epilogue kernels write what the forward writes after that epilogue and never split
@@ -453,6 +459,12 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   p.rows_b = swap ? q.M : q.N;
   p.num_kb = (q.K + block_k - 1) / block_k;
   p.nb0 = q.nb0;
+  p.k_slice_kb = 0;
+  if (k_slices > 1) {
+    p.k_slice_kb = (p.num_kb + k_slices - 1) / k_slices;
+    p.num_kb = p.k_slice_kb;
+    p.nb0 = k_slices;
+  }
   p.out = q.out;
   p.ldc = q.ldc;
   p.out_sb0 = q.out_sb0;
@@ -476,7 +488,7 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   p.drop_load_kb = g_drop_load_kb;
 
   const int tiles_x = (p.rows_a + 127) / 128, tiles_y = (p.rows_b + block_n - 1) / block_n;
-  const long long tiles = (long long)tiles_x * tiles_y * q.nb0 * q.nb1;
+  const long long tiles = (long long)tiles_x * tiles_y * q.nb0 * q.nb1 * k_slices;
   int split = 1;
   if (q.partials != nullptr && q.tile_counters != nullptr && q.out_type != kOutS32 &&
       q.force_split_k != 1) {
@@ -509,7 +521,7 @@ int gemm_plan_build(const GemmProblem& q, GemmPlan* plan) {
   p.blocked_a = (swap && q.b_blocked) ? 1 : 0;
   p.blocked_b = (!swap && q.b_blocked) ? 1 : 0;
   plan->split_k = split;
-  plan->grid = dim3(tiles_x, tiles_y, q.nb0 * q.nb1 * split);
+  plan->grid = dim3(tiles_x, tiles_y, q.nb0 * q.nb1 * k_slices * split);
   if (plan->multi_wave_candidate && split == 1) {
     const void* persistent = nullptr;
     // GeGLU too has a kernel of its own here (FP8 out of an FP8 GEMM, bf16 out of a bf16 one)

@@ -26,6 +26,10 @@ struct GemmProblem {
   int op = kOpBf16;  // OperandType of both operands
   int M = 0, N = 0, K = 0;
   int nb0 = 1, nb1 = 1;  // batch extents
+  // > 1: the K range of ONE GEMM (nb0 = nb1 = 1) in that many runs of K blocks, run s writing
+  // its own product at out + s * out_sb0 (fp32 partial products for a row kernel to add). The
+  // runs hold ceil(blocks / k_slices) K blocks each; what the last one lacks reads as zero.
+  int k_slices = 1;
   GemmOperand a;         // activations [M, K]
   GemmOperand b;         // weights [N, K]; with b_mn_major: [K, N] row-major, rows = K
   bool b_mn_major = false;

@@ -66,6 +66,10 @@ struct GemmParams {
   int rows_b;   // valid rows of the BLOCK_N-side operand
   int num_kb;   // K blocks of 128 bytes
   int nb0;      // blockIdx.z = b0 + nb0 * b1
+  // > 0: K slices as a batch. Entry b0 covers K blocks [b0 * k_slice_kb, (b0 + 1) * k_slice_kb)
+  // of ONE pair of operands (num_kb = k_slice_kb; blocks past the end of K read as zero) and
+  // writes its own output at b0 * out_sb0.
+  int k_slice_kb;
   // logical output [M, N] (after un-swapping), element strides
   void* out;
   long long ldc, out_sb0, out_sb1;
@@ -783,6 +787,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       int issued = 0;
       const bool first_cta = (blockIdx.x | blockIdx.y | blockIdx.z) == 0;
+      // K slices as a batch: the batch index moves the K range, not the operand
+      const int kb_slice = p.k_slice_kb > 0 ? b0 * p.k_slice_kb : 0;
+      const int c_b0 = p.k_slice_kb > 0 ? 0 : b0;
       auto load_a = [&](int it) {
         if (first_cta && it == p.drop_load_kb) return;
         const int s = it % STAGES;
@@ -791,13 +798,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
                            kb_begin + it, 0);
         } else {
           ptx::tma_load_4d(smem + s * kStageBytes, &tmap_a, &full_bar[s],
-                           (kb_begin + it) * kBlockK, tile_a * kTileRowsA, b0, b1);
+                           (kb_slice + kb_begin + it) * kBlockK, tile_a * kTileRowsA, c_b0, b1);
         }
       };
       auto load_b = [&](int it) {
         const int s = it % STAGES;
         uint8_t* sb = smem + s * kStageBytes + kStageABytes;
-        const int kb = kb_begin + it;
+        const int kb = kb_slice + kb_begin + it;
         if constexpr (B_MN) {
           // MN-major B: 128-byte runs along N (kBlockK elements wide), kBlockK K-rows per chunk
 #pragma unroll
@@ -808,7 +815,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
         } else if (p.blocked_b) {
           ptx::tma_load_4d(sb, &tmap_b, &full_bar[s], 0, tile_b * BLOCK_N, kb, 0);
         } else {
-          ptx::tma_load_4d(sb, &tmap_b, &full_bar[s], kb * kBlockK, tile_b * BLOCK_N, b0, b1);
+          ptx::tma_load_4d(sb, &tmap_b, &full_bar[s], kb * kBlockK, tile_b * BLOCK_N, c_b0, b1);
         }
       };
       // First ring fill: static operands (weights) stream in while the producer of the

@@ -43,7 +43,7 @@ def gemm(a, b, out, *, op, mode=_lib.EPI_STORE, out_type=_lib.OUT_BF16, bias=Non
          out_inv_scale=1.0, b_mn_major=False, status=None, stream=None, force_swap=-1,
          force_block_n=0, partials=None, tile_counters=None, force_split_k=0,
          static_scratch=False, b_blocked=None, force_skinny=-1, prologue=0, style=None, eps=1e-6,
-         a_inv_scale=1.0, a_dynamic_rows=False, rope=None, dt=0.0):
+         a_inv_scale=1.0, a_dynamic_rows=False, rope=None, dt=0.0, k_slices=0):
     """out[.., M, N'] = epilogue(a[.., M, K] @ b[.., N, K]^T); see Pi05GemmArgs.
     `rope`: dict(q_out, k_cache, v_cache, cos, sin, tokens, q_heads, head_dim, position_offset,
     cache_rows) for mode EPI_ROPE."""
@@ -78,7 +78,8 @@ def gemm(a, b, out, *, op, mode=_lib.EPI_STORE, out_type=_lib.OUT_BF16, bias=Non
         max_tiles=(tile_counters.numel() if tile_counters is not None else 0),
         force_split_k=force_split_k,
         b_blocked=int(b_blocked is not None), force_skinny=force_skinny, prologue=prologue,
-        style=_ptr(style), eps=eps, a_inv_scale=a_inv_scale, a_dynamic_rows=int(a_dynamic_rows), dt=dt)
+        style=_ptr(style), eps=eps, a_inv_scale=a_inv_scale, a_dynamic_rows=int(a_dynamic_rows), dt=dt,
+        k_slices=k_slices)
     if rope is not None:
         args.rope_q_out, args.rope_k_cache, args.rope_v_cache = (_ptr(rope["q_out"]), _ptr(rope["k_cache"]),
                                                                  _ptr(rope["v_cache"]))

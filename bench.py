@@ -64,8 +64,8 @@ UNIT = "action chunks/s"
 # profiles/gemm_umma_persistent_e4m3_gate_up_batch64_dram_traffic.md, together with a digest
 # of the kernel and planner sources that were profiled: the bench line reports the traffic only while the
 # kernel source is still that one (null otherwise: a stale figure says nothing).
-GATE_UP_DRAM_BYTES_BATCH64 = 276.3e6 + 503.8e6
-GATE_UP_PROFILED_KERNEL_BLOB = "7b2e0904ec61"  # kernel_source_blob() of the profiled build
+GATE_UP_DRAM_BYTES_BATCH64 = 275.0e6 + 505.1e6
+GATE_UP_PROFILED_KERNEL_BLOB = "a069f6ec41f8"  # kernel_source_blob() of the profiled build
 
 
 def kernel_source_blob() -> str:

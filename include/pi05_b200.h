@@ -133,6 +133,12 @@ typedef struct Pi05GemmArgs {
   const float* rope_sin;
   int32_t rope_tokens, rope_q_heads, rope_head_dim, rope_position_offset, rope_cache_rows;
   float dt;                /* PI05_EPI_EULER */
+  /* > 1: the K range of one GEMM (nb0 = nb1 = 1, no split-K, K-major operands) in that many runs
+   * of 128-byte K blocks, run s writing its own product at out + s * out_sb0 elements: partial
+   * products (PI05_OUT_F32, PI05_EPI_STORE) for the caller to add. Used for a few hundred rows
+   * against a very long K (language.down at B=1), where whole tiles alone would leave most SMs
+   * idle. 0 and 1: off. */
+  int32_t k_slices;
 } Pi05GemmArgs;
 
 int pi05_gemm(const Pi05GemmArgs* args, void* cuda_stream);

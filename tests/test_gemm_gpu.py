@@ -418,3 +418,42 @@ def test_single_epilogue_kernels_give_the_general_kernel_bits(op, mode, M, N, Kd
         _tuning("single_epilogue_kernels", 1)
     assert torch.equal(single.view(torch.uint8), general.view(torch.uint8))
     assert single.view(torch.uint8).float().std().item() > 0  # not all one value
+
+
+@pytest.mark.parametrize("op", [0, 1, 2])
+@pytest.mark.parametrize("M,N,Kd,slices", [(522, 2048, 16384, 3), (300, 256, 1001 * 16, 4), (130, 200, 2048, 2),
+                                           (128, 128, 640, 3)])
+def test_gemm_k_slices_are_partial_products(op, M, N, Kd, slices):
+    """The K range of one GEMM as a batch of K-block runs, each writing its own fp32 product:
+    their sum is the whole product. Uneven runs (the last one shorter, or reaching past K, where
+    the operands read as zero) and a K that is no multiple of the K block are included."""
+    L, K = _lib()
+    if op != L.OP_BF16:
+        Kd = (Kd + 15) // 16 * 16
+    gen = torch.Generator().manual_seed(8100 + M + N + op)
+    if op == L.OP_S8:
+        a = torch.randint(-8, 9, (M, Kd), generator=gen, dtype=torch.int8)
+        b = torch.randint(-8, 9, (N, Kd), generator=gen, dtype=torch.int8)
+        af, bf = a.float(), b.float()
+    else:
+        a, af = make_operand(M, Kd, op, gen)
+        b, bf = make_operand(N, Kd, op, gen, 0.05)
+    want = (af.double() @ bf.double().t())
+    out = torch.full((slices, M, N), float("nan"), dtype=torch.float32, device="cuda")
+    st = K.gemm(a.cuda(), b.cuda(), out, op=op, out_type=L.OUT_F32, force_swap=0, k_slices=slices)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    parts = out.cpu().double()
+    assert torch.isfinite(parts).all()
+    block = 128 if op != L.OP_BF16 else 64
+    run = -(-(-(-Kd // block)) // slices) * block  # K elements per run
+    for s in range(slices):
+        lo, hi = min(Kd, s * run), min(Kd, (s + 1) * run)
+        part = af[:, lo:hi].double() @ bf[:, lo:hi].double().t()
+        scale = math.sqrt(max(hi - lo, 1)) * (16 if op == L.OP_E4M3 else 1) * 0.05
+        if op == L.OP_S8:
+            assert torch.equal(parts[s], part), f"run {s}"
+        else:
+            check_close(parts[s].float(), part.float(), 2e-3 * scale, 1e-3, f"run {s}")
+    if op == L.OP_S8:
+        assert torch.equal(parts.sum(0), want)
