@@ -508,6 +508,16 @@ int PreparedGraph::linear(const char* name, const Act& in, int rows, const Linea
       add_kernel((std::string(name) + ".sum").c_str(), [=](cudaStream_t s) {
         return launch_sum_partials(partials, slices, count, cols, residual, bias, out, s);
       });
+      if (!measuring_) {
+        pending_sum_.op_index = ops_.size() - 1;
+        pending_sum_.partials = partials;
+        pending_sum_.slices = slices;
+        pending_sum_.count = count;
+        pending_sum_.cols = cols;
+        pending_sum_.residual = residual;
+        pending_sum_.bias = bias;
+        pending_sum_.out = out;
+      }
       return kPi05Ok;
     }
   }
@@ -606,6 +616,21 @@ int PreparedGraph::norm_to_act(const char* name, const void* x, int rows, int co
           : prec == kPrecFp8 ? kRowE4m3
           : e_->static_int8() ? kRowInt8Static
                               : kRowInt8;
+  // the rows were just formed by the adding launch of a K-sliced GEMM: one launch does both
+  const PendingSum& ps = pending_sum_;
+  if (!measuring_ && !ops_.empty() && ps.op_index == ops_.size() - 1 && ps.out == x && ps.cols == cols &&
+      ps.count == (long long)rows * cols && kind == kNormRms && rows < 1024) {
+    a.sum_partials = ps.partials;
+    a.sum_splits = ps.slices;
+    a.sum_stride = ps.count;
+    a.sum_residual = ps.residual;
+    a.sum_bias = ps.bias;
+    Op& op = ops_.back();
+    op.name = op.name + "+" + name;
+    op.launch = [a](cudaStream_t s) { return launch_norm(a, s); };
+    pending_sum_ = PendingSum{};
+    return kPi05Ok;
+  }
   add_kernel(name, [a](cudaStream_t s) { return launch_norm(a, s); });
   return kPi05Ok;
 }

@@ -129,6 +129,18 @@ class PreparedGraph {
   int build(bool measuring);
   int build_styles();
   void add_kernel(const char* name, std::function<cudaError_t(cudaStream_t)> fn);
+  // The adding launch of a K-sliced GEMM, while it is the newest op: an RMSNorm of the rows it
+  // writes takes its place (one launch forms the rows and normalises them).
+  struct PendingSum {
+    size_t op_index = static_cast<size_t>(-1);
+    const float* partials = nullptr;
+    int slices = 0;
+    long long count = 0;
+    int cols = 0;
+    const void* residual = nullptr;
+    const void* bias = nullptr;
+    void* out = nullptr;
+  } pending_sum_;
   int add_gemm(const char* name, const GemmProblem& problem);
   int linear(const char* name, const Act& in, int rows, const Linear& w, int mode, void* out,
              long long ldc, int out_type, const void* residual, const void* gate,

@@ -63,7 +63,7 @@ __device__ __forceinline__ float block_reduce(float v, float* scratch) {
 }
 
 // One CTA per row, one 8-element vector per thread (cols <= 8 * blockDim.x).
-template <int KIND, int OUT>
+template <int KIND, int OUT, bool SUM = false>
 __global__ void norm_rows_kernel(NormArgs a) {
   pdl_launch_dependents();
   __shared__ float scratch[32];
@@ -90,7 +90,35 @@ __global__ void norm_rows_kernel(NormArgs a) {
   const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(a.input) + (long long)row * a.cols;
   float x[8];
   if (active) {
-    unpack8(reinterpret_cast<const uint4*>(in)[vec], x);
+    if constexpr (SUM) {
+      // the row itself comes first: partial products + residual (+ bias), rounded as the
+      // stand-alone adding kernel rounds them, stored, and normalised from the stored values
+      const long long base = (long long)row * a.cols + vec * 8;
+      float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+      for (int s = 0; s < a.sum_splits; ++s) {
+        const float4* src = reinterpret_cast<const float4*>(a.sum_partials + s * a.sum_stride + base);
+        const float4 lo = __ldcg(src);
+        const float4 hi = __ldcg(src + 1);
+        acc[0] += lo.x; acc[1] += lo.y; acc[2] += lo.z; acc[3] += lo.w;
+        acc[4] += hi.x; acc[5] += hi.y; acc[6] += hi.z; acc[7] += hi.w;
+      }
+      float r[8], bv[8];
+      unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.sum_residual) + base), r);
+      if (a.sum_bias != nullptr) {
+        unpack8(reinterpret_cast<const uint4*>(a.sum_bias)[vec], bv);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) bv[i] = 0.0f;
+      }
+      float y[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = (rb(acc[i]) + r[i]) + bv[i];
+      const uint4 packed = pack8(y);
+      reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(in))[vec] = packed;
+      unpack8(packed, x);
+    } else {
+      unpack8(reinterpret_cast<const uint4*>(in)[vec], x);
+    }
   } else {
 #pragma unroll
     for (int i = 0; i < 8; ++i) x[i] = 0.0f;
@@ -334,6 +362,25 @@ template <int KIND>
 cudaError_t launch_norm_kind(const NormArgs& a, int threads, cudaStream_t stream) {
   // a warp per row pays once there are rows enough to fill the SMs with such CTAs
   const bool by_warp = a.rows >= 1024 && (a.cols >> 3) <= 8 * 32;
+  if (a.sum_partials != nullptr) {
+    if constexpr (KIND == kNormRms) {
+      if (by_warp || a.sum_residual == nullptr || a.sum_splits <= 0) return cudaErrorInvalidValue;
+      switch (a.out) {
+        case kRowBf16:
+          return launch_pdl(norm_rows_kernel<KIND, kRowBf16, true>, dim3(a.rows), dim3(threads), 0, stream, a);
+        case kRowE4m3:
+          return launch_pdl(norm_rows_kernel<KIND, kRowE4m3, true>, dim3(a.rows), dim3(threads), 0, stream, a);
+        case kRowInt8:
+          return launch_pdl(norm_rows_kernel<KIND, kRowInt8, true>, dim3(a.rows), dim3(threads), 0, stream, a);
+        case kRowInt8Static:
+          return launch_pdl(norm_rows_kernel<KIND, kRowInt8Static, true>, dim3(a.rows), dim3(threads), 0, stream, a);
+        default:
+          return cudaErrorInvalidValue;
+      }
+    } else {
+      return cudaErrorInvalidValue;
+    }
+  }
   if (by_warp) {
     switch (a.out) {
       case kRowBf16: return launch_norm_warp<KIND, kRowBf16>(a, stream);

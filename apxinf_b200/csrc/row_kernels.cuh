@@ -37,6 +37,15 @@ struct NormArgs {
   // its style vectors once, outside the replayed launch list), so they are read ahead of the
   // programmatic-dependency wait and their round trip overlaps the predecessor's tail
   int static_params;
+  // != null (RMSNorm, fewer than 1024 rows): the rows are not read from `input` but formed
+  // first, as launch_sum_partials would form them, from `sum_splits` fp32 partial products
+  // (`sum_stride` elements apart), the bf16 residual and an optional bf16 bias; they are
+  // written to `input` (which may be the residual buffer) and normalised in the same pass.
+  const float* sum_partials;
+  int sum_splits;
+  long long sum_stride;
+  const void* sum_residual;
+  const void* sum_bias;
 };
 cudaError_t launch_norm(const NormArgs& args, cudaStream_t stream);
 
